@@ -1,0 +1,170 @@
+// Row-wise kernels: embedding gather, residual add + RMSNorm, SwiGLU, row gather, bias add.
+//
+// The residual stream is always float32; `A` is the activation type (float in the 32-bit path,
+// bfloat16 in the serving path).  Each row is reduced in an order that depends only on the
+// block size, so a row's result does not depend on which other rows are in the batch.
+//
+// Formulas (reference): RMSNorm x * rsqrt(mean(x^2) + eps) * w, normalise first, weight second
+// (src/iian/graph.cpp:105-114); SwiGLU silu(gate) * up with silu(z) = z / (1 + exp(-z))
+// (src/iian/graph.cpp:135, third_party/ggml/src/ggml-cpu/vec.h:1046-1048); embedding = row gather
+// (src/iian/graph.cpp:39-46); row selection = row gather (src/iian/graph.cpp:356-358).
+#include "common.cuh"
+
+namespace iian {
+
+template <typename W>
+__global__ void embedding_kernel(const W * __restrict__ table, const int * __restrict__ tokens,
+                                 float * __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    float * o = out + (size_t) t * H;
+    if (id < 0 || id >= V) {   // never read outside the table
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.0f;
+        return;
+    }
+    const W * row = table + (size_t) id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// residual (f32, in place) += delta (A, optional); out (A) = rmsnorm(residual) * weight (f32)
+template <typename A>
+__global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta,
+                                    const float * __restrict__ weight, A * __restrict__ out,
+                                    int H, float eps) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float * r = residual + base;
+    float ss = 0.0f;
+    if (delta != nullptr) {
+        const A * d = delta + base;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = r[i] + to_f32(d[i]);
+            r[i] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = r[i];
+            ss += v * v;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float) H + eps);
+    A * o = out + base;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<A>(r[i] * inv * weight[i]);
+}
+
+// x (A, read only) -> out (A) = rmsnorm(x) * weight; no residual
+template <typename A>
+__global__ void rms_norm_kernel(const A * __restrict__ x, const float * __restrict__ weight,
+                                A * __restrict__ out, int H, float eps) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32(x[base + i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float) H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[base + i] = from_f32<A>(to_f32(x[base + i]) * inv * weight[i]);
+}
+
+template <typename A>
+__global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t total) {
+    const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t row = idx / F;
+    const int col = (int) (idx - row * F);
+    const float g = to_f32(gate_up[row * 2 * F + col]);
+    const float u = to_f32(gate_up[row * 2 * F + F + col]);
+    const float s = g / (1.0f + expf(-g));
+    out[idx] = from_f32<A>(s * u);
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(const T * __restrict__ src, const int * __restrict__ rows,
+                                   T * __restrict__ out, int H, int n_src) {
+    const int r = rows[blockIdx.x];
+    T * o = out + (size_t) blockIdx.x * H;
+    if (r < 0 || r >= n_src) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(0.0f);
+        return;
+    }
+    const T * s = src + (size_t) r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = s[i];
+}
+
+template <typename A>
+__global__ void add_bias_kernel(A * __restrict__ x, const float * __restrict__ bias, int M, size_t total) {
+    const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    x[idx] = from_f32<A>(to_f32(x[idx]) + bias[idx % M]);
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+IIAN_API int iian_embedding(const void * table, int table_dtype, const int * tokens, float * out,
+                            int N, int H, int V, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == IIAN_F32) embedding_kernel<float><<<N, threads, 0, stream>>>((const float *) table, tokens, out, H, V);
+    else if (table_dtype == IIAN_BF16) embedding_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>((const __nv_bfloat16 *) table, tokens, out, H, V);
+    else return IIAN_ERR_DTYPE;
+    return iian_launch_status();
+}
+
+IIAN_API int iian_add_rms_norm(float * residual, const void * delta, const float * weight, void * out,
+                               int act_dtype, int N, int H, float eps, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    const int threads = 256;   // fixed: the reduction order must not depend on the batch
+    if (act_dtype == IIAN_F32) add_rms_norm_kernel<float><<<N, threads, 0, stream>>>(residual, (const float *) delta, weight, (float *) out, H, eps);
+    else if (act_dtype == IIAN_BF16) add_rms_norm_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>(residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
+    else return IIAN_ERR_DTYPE;
+    return iian_launch_status();
+}
+
+IIAN_API int iian_rms_norm(const void * x, const float * weight, void * out, int act_dtype, int N, int H,
+                           float eps, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    const int threads = H >= 512 ? 256 : 32;
+    if (act_dtype == IIAN_F32) rms_norm_kernel<float><<<N, threads, 0, stream>>>((const float *) x, weight, (float *) out, H, eps);
+    else if (act_dtype == IIAN_BF16) rms_norm_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>((const __nv_bfloat16 *) x, weight, (__nv_bfloat16 *) out, H, eps);
+    else return IIAN_ERR_DTYPE;
+    return iian_launch_status();
+}
+
+IIAN_API int iian_swiglu(const void * gate_up, void * out, int act_dtype, int N, int F, cudaStream_t stream) {
+    const size_t total = (size_t) N * F;
+    if (total == 0) return IIAN_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
+    if (act_dtype == IIAN_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float *) gate_up, (float *) out, F, total);
+    else if (act_dtype == IIAN_BF16) swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, total);
+    else return IIAN_ERR_DTYPE;
+    return iian_launch_status();
+}
+
+IIAN_API int iian_gather_rows(const void * src, const int * rows, void * out, int dtype, int R, int H,
+                              int n_src, cudaStream_t stream) {
+    if (R <= 0) return IIAN_OK;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == IIAN_F32) gather_rows_kernel<float><<<R, threads, 0, stream>>>((const float *) src, rows, (float *) out, H, n_src);
+    else if (dtype == IIAN_BF16) gather_rows_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>((const __nv_bfloat16 *) src, rows, (__nv_bfloat16 *) out, H, n_src);
+    else return IIAN_ERR_DTYPE;
+    return iian_launch_status();
+}
+
+IIAN_API int iian_add_bias(void * x, const float * bias, int act_dtype, int N, int M, cudaStream_t stream) {
+    const size_t total = (size_t) N * M;
+    if (total == 0) return IIAN_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
+    if (act_dtype == IIAN_F32) add_bias_kernel<float><<<blocks, threads, 0, stream>>>((float *) x, bias, M, total);
+    else if (act_dtype == IIAN_BF16) add_bias_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16 *) x, bias, M, total);
+    else return IIAN_ERR_DTYPE;
+    return iian_launch_status();
+}

@@ -1,0 +1,240 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step may hold portions of prompts beside single decoded tokens, cut anywhere.  It runs only the
+tokens it is given and returns float32 logits at the wanted places.  The reference builds the same
+thing per step from its scheduler's output (``UBatch``, include/iian/graph.h:22-38,
+src/iian/engine.cpp:491-535: tokens, positions, sequence index and cache cell per token, output row
+ids) and computes masks on the host; here causality and windows are decided inside the kernels from
+positions and context lengths, so a step uploads one packed integer buffer and nothing else.
+
+``ModelRunner`` owns the model, the cache manager (page numbers) and the cache storage (device
+memory).  The scheduler-driven engine and the trace replay both drive this class; there is no other
+forward pass.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager, RequestCache
+from ..cache.storage import CacheStorage, plan_groups
+from ..parts.base import KVNeed, StateNeed
+from .model import Model
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: ``tokens`` follow the ``start`` tokens already in its cache;
+    ``want`` lists indices into ``tokens`` whose logits are returned."""
+
+    cache: RequestCache
+    tokens: Sequence[int]
+    start: int
+    want: Sequence[int] = ()
+
+
+class Workspace:
+    """Activation buffers by name, grown on demand and reused from step to step."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.frozen = False          # set while a CUDA graph that uses these buffers is alive
+
+    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        t = self._bufs.get(key)
+        if t is None or t.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer '{name}' would have to grow while a captured graph uses it")
+            cap = max(n, 1)
+            t = torch.empty(cap, dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t[:n].view(*shape)
+
+
+@dataclass
+class AttentionMeta:
+    """What the attention kernels need for one page group."""
+
+    positions: torch.Tensor        # i32 [N]
+    seq_of_token: torch.Tensor     # i32 [N]   (-1: padding token)
+    cu_q: torch.Tensor             # i32 [S + 1]
+    ctx_len: torch.Tensor          # i32 [S]   tokens in the cache after this step
+    block_table: torch.Tensor      # i32 [S, max_blocks]
+    slots: torch.Tensor            # i32 [N]   cache cell of each token (-1: store nothing)
+    num_seqs: int
+    num_tokens: int
+    max_q_len: int
+    max_ctx: int
+    decode_only: bool
+    h_q_len: Sequence[int] = ()
+    h_ctx_len: Sequence[int] = ()
+
+
+class StepContext:
+    def __init__(self, workspace: Workspace):
+        self.workspace = workspace
+        self.tokens = self.positions = self.seq_of_token = self.cu_q = self.ctx_len = None
+        self.state_slots = self.out_rows = None
+        self.metas: List[AttentionMeta] = []
+        self.num_tokens = self.num_seqs = 0
+        self.h_q_start: List[int] = []
+        self.h_q_len: List[int] = []
+        self.h_ctx_len: List[int] = []
+        self.h_state_slots: List[int] = []
+        self.decode_only = False
+        self.max_q_len = 0
+        self.max_ctx = 0
+
+    def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype)
+
+    def attention_meta(self, group: int) -> AttentionMeta:
+        return self.metas[group]
+
+
+class ModelRunner:
+    def __init__(self, model: Model, *, block_size: int = 16, capacity_tokens: int, max_num_seqs: int = 4,
+                 enable_prefix_caching: bool = False, window_capacity_tokens: Optional[int] = None):
+        self.model = model
+        self.device = model.device
+        self.block_size = block_size
+        self.max_num_seqs = max_num_seqs
+        needs = model.cache_needs()
+        groups, kinds = plan_groups(needs, capacity_tokens, block_size, window_capacity_tokens)
+        has_state = any(isinstance(n, StateNeed) for n in needs.values())
+        self.manager = CacheManager(groups, block_size, enable_prefix_caching, num_state_slots=max_num_seqs)
+        self.storage = CacheStorage(needs, groups, kinds, block_size, max_num_seqs if has_state else 0,
+                                    model.dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self._pinned: Optional[torch.Tensor] = None
+        self._staging_dev: Optional[torch.Tensor] = None
+        self._copy_done = None
+        if self.device.type == "cuda":
+            ops.kernels().prepare(model.dtype) if hasattr(ops.kernels(), "prepare") else None
+
+    # ---- batch building ---------------------------------------------------------------------
+    def _stage(self, n_ints: int) -> Tuple[np.ndarray, torch.Tensor]:
+        """Host array (pinned on CUDA) and device tensor of at least ``n_ints`` int32."""
+        if self._staging_dev is None or self._staging_dev.numel() < n_ints:
+            cap = max(4096, 2 * n_ints)
+            self._staging_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        if self._copy_done is not None:
+            self._copy_done.synchronize()       # the last step's upload has left the host buffer
+        return self._pinned.numpy(), self._staging_dev
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        mgr = self.manager
+        bs = self.block_size
+        S = len(entries)
+        N = sum(len(e.tokens) for e in entries)
+        R = sum(len(e.want) for e in entries)
+        n_groups = len(mgr.groups)
+        max_blocks = []
+        for g in range(n_groups):
+            mb = 1
+            for e in entries:
+                mb = max(mb, mgr.blocks_for(e.start + len(e.tokens)))
+            max_blocks.append(mb)
+        total = 3 * N + (S + 1) + 2 * S + R + sum(N + S * mb for mb in max_blocks)
+        host, dev = self._stage(total)
+        off = 0
+
+        def take(n):
+            nonlocal off
+            a = (off, off + n)
+            off += n
+            return a
+
+        r_tok, r_pos, r_seq = take(N), take(N), take(N)
+        r_cu, r_ctx, r_slot_state, r_rows = take(S + 1), take(S), take(S), take(R)
+        r_slots = [take(N) for _ in range(n_groups)]
+        r_bt = [take(S * mb) for mb in max_blocks]
+
+        ctx = StepContext(self.workspace)
+        t0 = 0
+        rows: List[int] = []
+        fresh: List[int] = []
+        host[r_cu[0]] = 0
+        for s, e in enumerate(entries):
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError("a step entry must bring at least one token")
+            host[r_tok[0] + t0: r_tok[0] + t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+            host[r_pos[0] + t0: r_pos[0] + t0 + n] = np.arange(e.start, e.start + n, dtype=np.int32)
+            host[r_seq[0] + t0: r_seq[0] + t0 + n] = s
+            host[r_cu[0] + s + 1] = t0 + n
+            host[r_ctx[0] + s] = e.start + n
+            host[r_slot_state[0] + s] = e.cache.state_slot
+            if e.cache.state_fresh:
+                fresh.append(e.cache.state_slot)
+                e.cache.state_fresh = False
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"wanted place {w} is outside this step's {n} tokens")
+                rows.append(t0 + w)
+            for g in range(n_groups):
+                table = e.cache.tables[g]
+                need_blocks = mgr.blocks_for(e.start + n)
+                if len(table) < need_blocks:
+                    raise ValueError(f"request holds {len(table)} pages in group {g}, needs {need_blocks}")
+                mb = max_blocks[g]
+                row = host[r_bt[g][0] + s * mb: r_bt[g][0] + (s + 1) * mb]
+                row[:] = -1
+                row[:need_blocks] = np.asarray(table[:need_blocks], dtype=np.int32)
+                pos = np.arange(e.start, e.start + n)
+                pages = row[pos // bs]
+                if (pages < 0).any():
+                    raise ValueError("a token of this step lies in a page that was given back")
+                host[r_slots[g][0] + t0: r_slots[g][0] + t0 + n] = pages * bs + (pos % bs)
+            ctx.h_q_start.append(t0)
+            ctx.h_q_len.append(n)
+            ctx.h_ctx_len.append(e.start + n)
+            ctx.h_state_slots.append(e.cache.state_slot)
+            t0 += n
+        host[r_rows[0]: r_rows[1]] = np.asarray(rows, dtype=np.int32) if rows else 0
+
+        dev[:total].copy_(self._pinned[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._copy_done is None:
+                self._copy_done = torch.cuda.Event()
+            self._copy_done.record()
+        self.storage.zero_state(fresh)
+
+        def view(r, shape=None):
+            t = dev[r[0]: r[1]]
+            return t.view(*shape) if shape is not None else t
+
+        ctx.tokens, ctx.positions, ctx.seq_of_token = view(r_tok), view(r_pos), view(r_seq)
+        ctx.cu_q, ctx.ctx_len, ctx.state_slots, ctx.out_rows = view(r_cu), view(r_ctx), view(r_slot_state), view(r_rows)
+        ctx.num_tokens, ctx.num_seqs = N, S
+        ctx.max_q_len = max(ctx.h_q_len) if S else 0
+        ctx.max_ctx = max(ctx.h_ctx_len) if S else 0
+        ctx.decode_only = ctx.max_q_len == 1
+        for g in range(n_groups):
+            ctx.metas.append(AttentionMeta(
+                positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
+                block_table=view(r_bt[g], (S, max_blocks[g])), slots=view(r_slots[g]),
+                num_seqs=S, num_tokens=N, max_q_len=ctx.max_q_len, max_ctx=ctx.max_ctx,
+                decode_only=ctx.decode_only, h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len))
+        return ctx
+
+    # ---- the step -----------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Logits ``[sum(len(want)), vocab]`` in the order of the entries and of their ``want`` lists
+        (None if nothing is wanted).  Pages for every entry's tokens must already be allocated."""
+        if not entries:
+            return None
+        if len(entries) > self.max_num_seqs:
+            raise ValueError(f"{len(entries)} requests in one step, the runner was built for {self.max_num_seqs}")
+        ctx = self.build_context(entries)
+        return self.model.forward(ctx, self.storage)

@@ -1,0 +1,249 @@
+"""The engine's kernels as Python functions on torch CUDA tensors.
+
+Every function validates its tensors (device, dtype, contiguity, shapes), then launches a
+hand-written kernel from ``iian_b200/csrc`` on the current CUDA stream through ``ctypes``.
+Nothing here computes with torch ops; a tensor that is not on a CUDA device is an error, there
+is no CPU path.  Large bfloat16 matrix products may go to the library GEMM, as in the reference
+(third_party/ggml/src/ggml-cuda/ggml-cuda.cu:1548-1608 calls cuBLAS for batches its own
+mat-vec kernels do not cover).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_ERRS = {1: "element types not supported by this kernel", 2: "a size this kernel refuses",
+         3: "a pointer or stride is not aligned as the kernel requires", 4: "beyond the kernel's stated maximum"}
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code >= 1000:
+        raise KernelError(f"{what}: CUDA launch failed with error {code - 1000}")
+    raise KernelError(f"{what}: {_ERRS.get(code, f'error {code}')}")
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _cuda(t: Optional[torch.Tensor], what: str, dtype=None) -> int:
+    """Pointer of a contiguous CUDA tensor (0 for None)."""
+    if t is None:
+        return 0
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}; the engine's kernels run on CUDA only")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_sigs_done = set()
+
+
+def _fn(lib_name: str, fn_name: str, argtypes):
+    lib = _build.load(lib_name)
+    fn = getattr(lib, fn_name)
+    key = (lib_name, fn_name)
+    if key not in _sigs_done:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _sigs_done.add(key)
+    return fn
+
+
+class CudaKernels:
+    """The kernel set the product path uses."""
+
+    name = "cuda"
+
+    # ---- libraries a model needs (compiled together on first use) ----------------------
+    def prepare(self, dtype: torch.dtype) -> None:
+        names = ["elementwise", "rope_kv", "attention_generic", "gemm_simt", "sampling"]
+        if dtype == torch.bfloat16:
+            names += [n for n in _build.SOURCES if n not in names and n in _build.BF16_SOURCES]
+        _build.preload(names)
+
+    # ---- row-wise ------------------------------------------------------------------------
+    def embedding(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+        n, h = out.shape
+        fn = _fn("elementwise", "iian_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(table, "embedding table"), _code(table, "embedding table"),
+                  _cuda(tokens, "tokens", torch.int32), _cuda(out, "embedding out", torch.float32),
+                  n, h, table.shape[0], _stream()), "embedding")
+
+    def add_rms_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                     eps: float, out: torch.Tensor) -> None:
+        n, h = residual.shape
+        if delta is not None and (delta.shape != residual.shape or delta.dtype != out.dtype):
+            raise KernelError(f"add_rms_norm: delta {tuple(delta.shape)} {delta.dtype} does not match "
+                              f"residual {tuple(residual.shape)} / out {out.dtype}")
+        if out.shape != residual.shape or weight.numel() != h:
+            raise KernelError("add_rms_norm: shapes of out / weight do not match the residual")
+        fn = _fn("elementwise", "iian_add_rms_norm",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(residual, "residual", torch.float32), _cuda(delta, "delta"),
+                  _cuda(weight, "norm weight", torch.float32), _cuda(out, "norm out"), _code(out, "norm out"),
+                  n, h, eps, _stream()), "add_rms_norm")
+
+    def rms_norm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        n, h = x.shape
+        if out.shape != x.shape or out.dtype != x.dtype or weight.numel() != h:
+            raise KernelError("rms_norm: out / weight do not match the input")
+        fn = _fn("elementwise", "iian_rms_norm", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(x, "rms_norm in"), _cuda(weight, "norm weight", torch.float32), _cuda(out, "rms_norm out"),
+                  _code(x, "rms_norm in"), n, h, eps, _stream()), "rms_norm")
+
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        n, f2 = gate_up.shape
+        if out.shape != (n, f2 // 2) or f2 % 2 or out.dtype != gate_up.dtype:
+            raise KernelError("swiglu: out must be [N, F] for gate_up [N, 2F] of the same dtype")
+        fn = _fn("elementwise", "iian_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(gate_up, "gate_up"), _cuda(out, "swiglu out"), _code(out, "swiglu out"), n, f2 // 2, _stream()),
+               "swiglu")
+
+    def gather_rows(self, src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+        r, h = out.shape
+        if src.shape[1] != h or src.dtype != out.dtype or rows.numel() != r:
+            raise KernelError("gather_rows: shapes or dtypes do not match")
+        fn = _fn("elementwise", "iian_gather_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(src, "gather src"), _cuda(rows, "rows", torch.int32), _cuda(out, "gather out"),
+                  _code(src, "gather src"), r, h, src.shape[0], _stream()), "gather_rows")
+
+    def add_bias(self, x: torch.Tensor, bias: torch.Tensor) -> None:
+        n, m = x.shape
+        if bias.numel() != m:
+            raise KernelError("add_bias: bias length does not match")
+        fn = _fn("elementwise", "iian_add_bias", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(x, "add_bias x"), _cuda(bias, "bias", torch.float32), _code(x, "add_bias x"), n, m, _stream()),
+               "add_bias")
+
+    # ---- matrix products -----------------------------------------------------------------
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        """out[n, m] = sum_k x[n, k] * w[m, k]."""
+        n, k = x.shape
+        m = w.shape[0]
+        if w.shape[1] != k or out.shape != (n, m):
+            raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+        if n == 0:
+            return
+        self._linear_dispatch(x, w, out, n, m, k)
+
+    def _linear_dispatch(self, x, w, out, n, m, k) -> None:
+        self.gemm_simt(x, w, out)
+
+    def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        n, k = x.shape
+        m = w.shape[0]
+        fn = _fn("gemm_simt", "iian_gemm_simt",
+                 [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(x, "linear x"), _code(x, "linear x"), _cuda(w, "linear w"), _code(w, "linear w"),
+                  _cuda(out, "linear out"), _code(out, "linear out"), n, m, k, _stream()), "gemm_simt")
+
+    # ---- attention -----------------------------------------------------------------------
+    def qk_norm_rope_store(self, qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                           v_cache: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int, head_dim: int,
+                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                           inv_freq: Optional[torch.Tensor], rot_dim: int, rope_style: int,
+                           positions: torch.Tensor, slots: Optional[torch.Tensor], write_kv: bool,
+                           bias: Optional[torch.Tensor] = None) -> None:
+        n = qkv.shape[0]
+        width = (num_heads + 2 * num_kv_heads) * head_dim
+        if qkv.shape[1] != width or q_out.numel() != n * num_heads * head_dim or q_out.dtype != qkv.dtype:
+            raise KernelError(f"qk_norm_rope_store: qkv {tuple(qkv.shape)} does not match {num_heads}+2*{num_kv_heads} "
+                              f"heads of {head_dim}")
+        page_size = num_pages = 0
+        if write_kv:
+            if k_cache is None or v_cache is None or slots is None:
+                raise KernelError("qk_norm_rope_store: a cache and slots are needed to store K and V")
+            if k_cache.dtype != qkv.dtype or k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads \
+                    or k_cache.shape[3] != head_dim:
+                raise KernelError(f"qk_norm_rope_store: cache {tuple(k_cache.shape)} {k_cache.dtype} does not match")
+            num_pages, page_size = k_cache.shape[0], k_cache.shape[2]
+        if inv_freq is not None and inv_freq.numel() < rot_dim // 2:
+            raise KernelError("qk_norm_rope_store: inv_freq is shorter than rot_dim / 2")
+        fn = _fn("rope_kv", "iian_qk_norm_rope_store",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(qkv, "qkv"), _cuda(bias, "qkv bias", torch.float32), _cuda(q_out, "q out"),
+                  _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"),
+                  _cuda(q_weight, "q norm weight", torch.float32), _cuda(k_weight, "k norm weight", torch.float32),
+                  _cuda(inv_freq, "inv_freq", torch.float32), _cuda(positions, "positions", torch.int32),
+                  _cuda(slots, "slots", torch.int32), _code(qkv, "qkv"), n, num_heads, num_kv_heads, head_dim,
+                  rot_dim if inv_freq is not None else 0, rope_style, eps, page_size, num_pages, 1 if write_kv else 0,
+                  _stream()), "qk_norm_rope_store")
+
+    def paged_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                        meta, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                        window: Optional[int]) -> None:
+        """``meta``: an object with ``positions``, ``seq_of_token``, ``block_table`` [S, max_blocks],
+        ``ctx_len`` [S] (int32 CUDA tensors) and host-side hints (``num_seqs``, ``max_q_len``, ``max_ctx``,
+        ``decode_only``)."""
+        self._attention_dispatch(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale, window)
+
+    def _attention_dispatch(self, q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, window) -> None:
+        self.paged_attention_generic(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                                     scale=scale, window=window)
+
+    def paged_attention_generic(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale,
+                                window) -> None:
+        n = q.shape[0]
+        if k_cache.dtype != q.dtype or out.dtype != q.dtype or k_cache.shape != v_cache.shape:
+            raise KernelError("paged_attention: q, caches and out must share one dtype and the caches one shape")
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or q.numel() != n * num_heads * head_dim:
+            raise KernelError(f"paged_attention: cache {tuple(k_cache.shape)} / q {tuple(q.shape)} do not match "
+                              f"{num_heads}/{num_kv_heads} heads of {head_dim}")
+        fn = _fn("attention_generic", "iian_paged_attention_generic",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+        bt = meta.block_table
+        _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
+                  _cuda(meta.positions, "positions", torch.int32), _cuda(meta.seq_of_token, "seq_of_token", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _code(q, "q"), n, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+                  scale, window or 0, _stream()), "paged_attention_generic")
+
+    # ---- sampling ------------------------------------------------------------------------
+    def argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:
+        r, v = logits.shape
+        if logits.stride(1) != 1:
+            raise KernelError("argmax: logits rows must be contiguous")
+        if not logits.is_cuda or logits.dtype != torch.float32:
+            raise KernelError("argmax: logits must be float32 on CUDA")
+        fn = _fn("sampling", "iian_argmax", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p])
+        _check(fn(logits.data_ptr(), r, v, logits.stride(0), _cuda(out, "argmax out", torch.int32), _stream()), "argmax")
+
+    def sample(self, logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+               min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+        r, v = logits.shape
+        if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
+            raise KernelError("sample: logits must be float32 on CUDA with contiguous rows")
+        fn = _fn("sampling", "iian_sample", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_void_p])
+        _check(fn(logits.data_ptr(), r, v, logits.stride(0), _cuda(temperature, "temperature", torch.float32),
+                  _cuda(top_k, "top_k", torch.int32), _cuda(top_p, "top_p", torch.float32),
+                  _cuda(min_p, "min_p", torch.float32), _cuda(uniform, "uniform", torch.float32),
+                  _cuda(out, "sample out", torch.int32), _stream()), "sample")

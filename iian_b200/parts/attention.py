@@ -1,0 +1,121 @@
+"""The attention mixer: projections, optional per-head RMSNorm of Q and K, position encoding, paged
+cache write, attention over the cache, output projection.
+
+Formulas in the reference's order (src/iian/arch/qwen3.cpp:80-89, src/iian/graph.cpp:215-244,
+:308-354): ``q = Wq h``, ``k = Wk h``, ``v = Wv h`` (biases only where the file has them); Q and K
+normalised over the head axis with one weight per projection; rotation; K and V stored at the token's
+cache cell; head ``h`` attends with KV head ``h // (num_heads / num_kv_heads)``, scores times
+``scale``, causal, optionally only the last ``window`` keys (src/iian/paged_attn.cpp:124), softmax in
+float32; ``y = Wo concat(o)``.
+
+The three projections run as one matrix product over the rows ``Wq | Wk | Wv`` stacked at load time.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import KVNeed, Mixer, POSITIONS, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``qk_norm``
+    (bool), ``qk_norm_eps``, ``window`` (None or keys visible), ``position`` (a PartSpec)."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.hd = int(p["head_dim"])
+        if self.nkv <= 0 or self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads cannot share {self.nkv} KV heads")
+        self.scale = float(p["scale"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("qk_norm_eps", 0.0))
+        self.window = p.get("window")
+        if self.window is not None and int(self.window) <= 0:
+            raise ValueError("attention: window must be positive or None")
+        self.position = POSITIONS.build(p["position"], dtype, device)
+        if getattr(self.position, "dim", 0) > self.hd:
+            raise ValueError(f"attention: position encoding rotates {self.position.dim} dims of a head of {self.hd}")
+        self.q_size = self.nh * self.hd
+        self.kv_size = self.nkv * self.hd
+        self.w_qkv = self.w_o = self.b_qkv = self.b_o = self.q_norm_w = self.k_norm_w = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        t = {
+            "q_proj.weight": TensorSpec((self.q_size, self.hidden)),
+            "k_proj.weight": TensorSpec((self.kv_size, self.hidden)),
+            "v_proj.weight": TensorSpec((self.kv_size, self.hidden)),
+            "o_proj.weight": TensorSpec((self.hidden, self.q_size)),
+            "q_proj.bias": TensorSpec((self.q_size,), optional=True, init="zeros"),
+            "k_proj.bias": TensorSpec((self.kv_size,), optional=True, init="zeros"),
+            "v_proj.bias": TensorSpec((self.kv_size,), optional=True, init="zeros"),
+            "o_proj.bias": TensorSpec((self.hidden,), optional=True, init="zeros"),
+        }
+        if self.qk_norm:
+            t["q_norm.weight"] = TensorSpec((self.hd,), init="ones_jitter")
+            t["k_norm.weight"] = TensorSpec((self.hd,), init="ones_jitter")
+        return t
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        ws = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.to(torch.float32) for w in ws]
+        self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if any(f"{n}_proj.bias" in tensors for n in "qkv"):
+            parts = []
+            for n, size in (("q", self.q_size), ("k", self.kv_size), ("v", self.kv_size)):
+                b = tensors.get(f"{n}_proj.bias")
+                parts.append(b.to(torch.float32) if b is not None else torch.zeros(size, dtype=torch.float32, device=self.device))
+            self.b_qkv = torch.cat(parts).contiguous()
+        if "o_proj.bias" in tensors:
+            self.b_o = tensors["o_proj.bias"].to(torch.float32).contiguous()
+        if self.qk_norm:
+            self.q_norm_w = tensors["q_norm.weight"].to(torch.float32).contiguous()
+            self.k_norm_w = tensors["k_norm.weight"].to(torch.float32).contiguous()
+
+    def cache_need(self) -> KVNeed:
+        return KVNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
+
+    def kernel_libraries(self):
+        return ("rope_kv", "attention_generic", "gemm_simt")
+
+    def forward(self, x: torch.Tensor, ctx, cache, writes_cache: bool) -> torch.Tensor:
+        k = ops.kernels()
+        n = x.shape[0]
+        pos = self.position
+        if writes_cache:
+            w, bias, nkv = self.w_qkv, self.b_qkv, self.nkv
+        else:   # reads a cache another call filled: only Q is needed
+            w, nkv = self.w_qkv[: self.q_size], 0
+            bias = self.b_qkv[: self.q_size] if self.b_qkv is not None else None
+        width = self.q_size + 2 * nkv * self.hd
+        qkv = ctx.buf("qkv", (n, width), self.dtype)
+        k.linear(x, w, qkv)
+        if not pos.fused:
+            pos.apply(qkv, self.nh, nkv, self.hd, ctx)
+        q = ctx.buf("q", (n, self.nh, self.hd), self.dtype)
+        meta = ctx.attention_meta(cache.group)
+        k.qk_norm_rope_store(
+            qkv, q, cache.k if writes_cache else None, cache.v if writes_cache else None,
+            num_heads=self.nh, num_kv_heads=nkv, head_dim=self.hd,
+            q_weight=self.q_norm_w, k_weight=self.k_norm_w, eps=self.eps,
+            inv_freq=pos.inv_freq if pos.fused else None, rot_dim=pos.dim if pos.fused else 0,
+            rope_style=pos.style if pos.fused else 0,
+            positions=ctx.positions, slots=meta.slots if writes_cache else None, write_kv=writes_cache, bias=bias)
+        attn = ctx.buf("attn", (n, self.q_size), self.dtype)
+        k.paged_attention(q, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
+                          head_dim=self.hd, scale=self.scale, window=self.window)
+        out = ctx.buf("mixer_out", (n, self.hidden), self.dtype)
+        k.linear(attn, self.w_o, out)
+        if self.b_o is not None:
+            k.add_bias(out, self.b_o)
+        return out

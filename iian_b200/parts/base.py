@@ -1,0 +1,153 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part is built from a :class:`~iian_b200.config.spec.PartSpec` (its sizes and constants), the
+activation dtype and the device.  It declares the tensors it needs under names local to itself
+(:meth:`Part.tensors`), receives them (:meth:`Part.bind`), and computes through
+``iian_b200.ops.kernels()``.  It never sees the model's configuration.
+
+The reference has the same inventory as methods of one ``GraphContext`` (include/iian/graph.h:60-150:
+``build_norm``, ``build_qkv``, ``build_rope``, ``build_attn``, ``build_ffn``, ``build_lm_head``) that
+read several constants from a shared hyper-parameter struct (src/iian/graph.cpp:25-30, :107); here
+each kind is a class chosen by name, layer by layer.
+
+Interfaces
+----------
+``Norm.forward(residual, delta, ctx) -> normed``
+    ``residual`` is the float32 residual stream ``[N, H]``; if ``delta`` is given it is first added
+    into ``residual`` in place (the residual sum is always float32).  Returns the normalised rows in
+    the activation dtype.
+``Mixer.forward(x, ctx, cache, writes_cache) -> y``
+    ``x``: normalised rows ``[N, H]``; ``cache``: what :meth:`Mixer.cache_need` asked for (a
+    :class:`~iian_b200.cache.storage.KVView`, a :class:`~iian_b200.cache.storage.StateView` or
+    None); ``writes_cache`` is False when the run order lets this call read another call's cache.
+    Returns ``[N, H]`` in the activation dtype.
+``FeedForward.forward(x, ctx) -> y``
+    rows in, rows out, ``[N, H]``.
+``PositionEncoding``
+    owned by the mixer that needs positions; the attention mixer asks it for the rotation table.
+``Embedding.forward(tokens, ctx) -> residual`` and ``Head.forward(x, ctx) -> logits`` (float32).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional, Tuple, Type
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.loader import TensorSpec
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Per-token entries: keys and values of ``num_kv_heads`` heads of ``head_dim``; ``window`` = how
+    many of the latest keys stay needed (None: all)."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A fixed-size state per request: one tensor of ``shape`` and ``dtype`` per slot."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    def __init__(self, spec: PartSpec, dtype: torch.dtype, device: torch.device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        """Names of the CUDA libraries this part launches (compiled together before the first step)."""
+        return ()
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache, writes_cache: bool) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Embedding(Part):
+    def forward(self, tokens: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: Dict[str, Type[Part]] = {}
+
+    def register(self, kind: str) -> Callable[[Type[Part]], Type[Part]]:
+        def deco(cls: Type[Part]) -> Type[Part]:
+            self._kinds[kind] = cls
+            return cls
+        return deco
+
+    def unregister(self, kind: str) -> None:
+        self._kinds.pop(kind, None)
+
+    def build(self, spec: PartSpec, dtype: torch.dtype, device: torch.device) -> Part:
+        try:
+            cls = self._kinds[spec.kind]
+        except KeyError:
+            raise KeyError(f"unknown {self.what} '{spec.kind}'; registered: {', '.join(sorted(self._kinds))}") from None
+        return cls(spec, dtype, device)
+
+    def kinds(self):
+        return sorted(self._kinds)
+
+
+NORMS = Registry("norm")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+POSITIONS = Registry("position encoding")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+BLOCKS: Dict[str, type] = {}
+
+register_norm = NORMS.register
+register_mixer = MIXERS.register
+register_feed_forward = FEED_FORWARDS.register
+register_position = POSITIONS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
+
+
+def register_block(kind: str):
+    def deco(cls):
+        BLOCKS[kind] = cls
+        return cls
+    return deco

@@ -1,0 +1,57 @@
+"""Dense gated feed-forward: ``y = Wdown (act(Wgate h) * (Wup h))``, parallel gate, no biases
+(src/iian/graph.cpp:116-163 with ``FfnOp::SILU`` / ``FfnGate::PAR``, src/iian/arch/qwen3.cpp:97).
+``silu(z) = z / (1 + exp(-z))`` (third_party/ggml/src/ggml-cpu/vec.h:1046-1048).
+
+Gate and up projections run as one matrix product over the rows ``Wgate | Wup`` stacked at load time.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    """params: ``hidden_size``, ``intermediate_size``, ``activation`` (``silu``)."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        act = spec.params.get("activation", "silu")
+        if act != "silu":
+            raise ValueError(f"gated_mlp: activation '{act}' has no kernel (silu only)")
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {
+            "gate_proj.weight": TensorSpec((self.inter, self.hidden)),
+            "up_proj.weight": TensorSpec((self.inter, self.hidden)),
+            "down_proj.weight": TensorSpec((self.hidden, self.inter)),
+        }
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        if g.dtype != u.dtype:
+            g, u = g.to(torch.float32), u.to(torch.float32)
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"].contiguous()
+
+    def kernel_libraries(self):
+        return ("elementwise", "gemm_simt")
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        k = ops.kernels()
+        n = x.shape[0]
+        gate_up = ctx.buf("gate_up", (n, 2 * self.inter), self.dtype)
+        k.linear(x, self.w_gate_up, gate_up)
+        act = ctx.buf("ffn_act", (n, self.inter), self.dtype)
+        k.swiglu(gate_up, act)
+        out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
+        k.linear(act, self.w_down, out)
+        return out
