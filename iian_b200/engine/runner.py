@@ -119,7 +119,8 @@ class ModelRunner:
         self._staging_dev: Optional[torch.Tensor] = None
         self._copy_done = None
         if self.device.type == "cuda":
-            ops.kernels().prepare(model.dtype) if hasattr(ops.kernels(), "prepare") else None
+            from ..csrc import build
+            build.preload(model.kernel_libraries())      # compile what this model needs, together
 
     # ---- batch building ---------------------------------------------------------------------
     def _stage(self, n_ints: int) -> Tuple[np.ndarray, torch.Tensor]:

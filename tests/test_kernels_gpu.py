@@ -1,0 +1,291 @@
+"""Each CUDA kernel alone against a plain float64 reference, at sizes other than the engine's
+(odd widths, head sizes in steps of 16, page sizes that are no power of two)."""
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from iian_b200.ops.cuda_backend import CudaKernels
+    return CudaKernels()
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embedding(dtype):
+    table = rnd(77, 50, dtype=dtype)
+    tokens = torch.tensor([0, 76, 5, 5, 33], dtype=torch.int32).cuda()
+    out = torch.empty(5, 50, dtype=torch.float32).cuda()
+    K().embedding(table, tokens, out)
+    assert torch.equal(out.cpu(), table.float().cpu()[tokens.long().cpu()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("H", [203, 1024, 4100])
+def test_add_rms_norm(dtype, H):
+    res = rnd(5, H, seed=1)
+    delta = rnd(5, H, dtype=dtype, seed=2)
+    w = rnd(H, seed=3) * 0.1 + 1
+    out = torch.empty(5, H, dtype=dtype).cuda()
+    res0 = res.clone()
+    K().add_rms_norm(res, delta, w, 1e-5, out)
+    want_res = res0.double().cpu() + delta.double().cpu()
+    assert (res.double().cpu() - want_res).abs().max() < 1e-6
+    want = plain.rms_norm(want_res, w.double().cpu(), 1e-5)
+    assert (out.double().cpu() - want).abs().max() < tol(dtype, want.abs().max().item())
+    # without delta the residual is left alone
+    res1 = res.clone()
+    K().add_rms_norm(res, None, w, 1e-5, out)
+    assert torch.equal(res, res1)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_rms_norm_and_swiglu_and_gather_and_bias(dtype):
+    x = rnd(7, 130, dtype=dtype, seed=4)
+    w = rnd(130, seed=5) * 0.1 + 1
+    out = torch.empty_like(x)
+    K().rms_norm(x, w, 1e-6, out)
+    want = plain.rms_norm(x.double().cpu(), w.double().cpu(), 1e-6)
+    assert (out.double().cpu() - want).abs().max() < tol(dtype, want.abs().max().item())
+
+    gu = rnd(3, 2 * 77, dtype=dtype, seed=6, std=2.0)
+    act = torch.empty(3, 77, dtype=dtype).cuda()
+    K().swiglu(gu, act)
+    g, u = gu.double().cpu()[:, :77], gu.double().cpu()[:, 77:]
+    want = plain.silu(g) * u
+    assert (act.double().cpu() - want).abs().max() < tol(dtype, want.abs().max().item())
+
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32).cuda()
+    sel = torch.empty(3, 130, dtype=dtype).cuda()
+    K().gather_rows(x, rows, sel)
+    assert torch.equal(sel, x[rows.long()])
+
+    b = rnd(130, seed=7)
+    y = x.clone()
+    K().add_bias(y, b)
+    assert (y.double().cpu() - (x.double().cpu() + b.double().cpu())).abs().max() < tol(dtype, 4.0)
+
+
+@pytest.mark.parametrize("xd,wd,od", [(torch.float32, torch.float32, torch.float32),
+                                       (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                       (torch.bfloat16, torch.bfloat16, torch.float32),
+                                       (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("N,M,K_", [(1, 70, 45), (37, 70, 45), (130, 257, 96)])
+def test_gemm_simt(xd, wd, od, N, M, K_):
+    x = rnd(N, K_, dtype=xd, seed=8)
+    w = rnd(M, K_, dtype=wd, seed=9)
+    out = torch.empty(N, M, dtype=od).cuda()
+    K().gemm_simt(x, w, out)
+    want = x.double().cpu() @ w.double().cpu().T
+    assert (out.double().cpu() - want).abs().max() < tol(od, want.abs().max().item())
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    x = rnd(40, 333, seed=10)
+    w = rnd(90, 333, seed=11)
+    full = torch.empty(40, 90).cuda()
+    K().gemm_simt(x, w, full)
+    one = torch.empty(1, 90).cuda()
+    for r in (0, 17, 39):
+        K().gemm_simt(x[r:r + 1].contiguous(), w, one)
+        assert torch.equal(one[0], full[r])
+
+
+def _fill_cache(k_all, v_all, tables, ps, nkv, hd, n_pages, dtype):
+    k_cache = torch.zeros(n_pages, nkv, ps, hd, dtype=dtype)
+    v_cache = torch.zeros(n_pages, nkv, ps, hd, dtype=dtype)
+    for s, table in enumerate(tables):
+        for j in range(k_all[s].shape[0]):
+            pg = table[j // ps]
+            if pg < 0:
+                continue
+            k_cache[pg, :, j % ps] = k_all[s][j].to(dtype)
+            v_cache[pg, :, j % ps] = v_all[s][j].to(dtype)
+    return k_cache.cuda(), v_cache.cuda()
+
+
+class Meta:
+    pass
+
+
+def attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=0, standout=False):
+    """Random sequences in a shuffled paged cache; returns what the kernel needs and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(ctx_lens)
+    n_blocks = [math.ceil(c / ps) for c in ctx_lens]
+    n_pages = sum(n_blocks) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    tables, at = [], 0
+    for nb in n_blocks:
+        tables.append(perm[at:at + nb])
+        at += nb
+    ks = [torch.randn(c, nkv, hd, generator=g) for c in ctx_lens]
+    vs = [torch.randn(c, nkv, hd, generator=g) for c in ctx_lens]
+    qs = [torch.randn(c, nh, hd, generator=g) for c in ctx_lens]
+    if standout:        # one far key among hundreds decides the output of the last query
+        for s in range(S):
+            far = min(3, ctx_lens[s] - 1) if not window else max(0, ctx_lens[s] - window)      # window: the oldest key still visible
+            qs[s][-1] *= 4.0
+            ks[s][far] = qs[s][-1][::nh // nkv][:nkv] * 1.0
+    ks = [k.to(dtype).float() for k in ks]
+    vs = [v.to(dtype).float() for v in vs]
+    qs = [q.to(dtype).float() for q in qs]
+    k_cache, v_cache = _fill_cache(ks, vs, tables, ps, nkv, hd, n_pages, dtype)
+    scale = 1.0 / math.sqrt(hd)
+    q_rows, pos, seq, want = [], [], [], []
+    for s in range(S):
+        full = plain.attention(qs[s].double(), ks[s].double(), vs[s].double(), scale, window)
+        first = ctx_lens[s] - q_lens[s]
+        q_rows.append(qs[s][first:])
+        want.append(full[first:].reshape(q_lens[s], nh * hd))
+        pos += list(range(first, ctx_lens[s]))
+        seq += [s] * q_lens[s]
+    maxb = max(n_blocks)
+    bt = torch.full((S, maxb), -1, dtype=torch.int32)
+    for s, t in enumerate(tables):
+        bt[s, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    m = Meta()
+    m.positions = torch.tensor(pos, dtype=torch.int32).cuda()
+    m.seq_of_token = torch.tensor(seq, dtype=torch.int32).cuda()
+    m.block_table = bt.cuda()
+    m.ctx_len = torch.tensor(ctx_lens, dtype=torch.int32).cuda()
+    cu = [0]
+    for ql in q_lens:
+        cu.append(cu[-1] + ql)
+    m.cu_q = torch.tensor(cu, dtype=torch.int32).cuda()
+    m.num_seqs, m.num_tokens = S, len(pos)
+    m.max_q_len, m.max_ctx = max(q_lens), max(ctx_lens)
+    m.decode_only = max(q_lens) == 1
+    m.h_q_len, m.h_ctx_len = list(q_lens), list(ctx_lens)
+    q = torch.cat(q_rows).to(dtype).cuda().contiguous()
+    return q, k_cache, v_cache, m, torch.cat(want), scale
+
+
+ATT_CASES = [
+    # nh, nkv, hd, page, ctx_lens, q_lens, window
+    (6, 3, 80, 8, [37, 5, 64], [37, 1, 20], None),
+    (4, 4, 16, 16, [33, 1], [2, 1], None),
+    (8, 2, 128, 16, [300, 257, 31], [1, 1, 1], None),
+    (6, 2, 48, 12, [90, 41], [13, 41], 20),
+    (5, 1, 96, 16, [130], [130], 33),
+    (8, 2, 64, 16, [200, 77], [64, 77], None),
+]
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("case", ATT_CASES)
+@pytest.mark.parametrize("standout", [False, True])
+def test_paged_attention_generic(dtype, case, standout):
+    nh, nkv, hd, ps, ctx_lens, q_lens, window = case
+    q, kc, vc, m, want, scale = attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=3, standout=standout)
+    out = torch.empty(q.shape[0], nh * hd, dtype=dtype).cuda()
+    K().paged_attention_generic(q, kc, vc, out, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale, window=window)
+    err = (out.double().cpu() - want).abs().max().item()
+    assert err < tol(dtype, max(1.0, want.abs().max().item())), err
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,rot,style,ps", [(6, 2, 48, 48, 0, 8), (4, 4, 16, 8, 0, 16), (3, 1, 80, 80, 1, 12),
+                                                      (8, 2, 128, 128, 0, 16)])
+def test_qk_norm_rope_store(dtype, nh, nkv, hd, rot, style, ps):
+    N, n_pages = 11, 9
+    width = (nh + 2 * nkv) * hd
+    qkv = rnd(N, width, dtype=dtype, seed=12)
+    qw, kw = rnd(hd, seed=13) * 0.1 + 1, rnd(hd, seed=14) * 0.1 + 1
+    base = 10000.0
+    inv_freq = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).float().cuda()
+    positions = torch.tensor([0, 1, 2, 3, 100, 101, 7, 8, 9, 4000, 17], dtype=torch.int32).cuda()
+    g = torch.Generator().manual_seed(15)
+    slots_l = torch.randperm(n_pages * ps, generator=g)[:N].tolist()
+    slots_l[5] = -1                                   # a padding token stores nothing
+    slots = torch.tensor(slots_l, dtype=torch.int32).cuda()
+    kc = torch.zeros(n_pages, nkv, ps, hd, dtype=dtype).cuda()
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(N, nh, hd, dtype=dtype).cuda()
+    eps = 1e-5
+    K().qk_norm_rope_store(qkv, q_out, kc, vc, num_heads=nh, num_kv_heads=nkv, head_dim=hd, q_weight=qw, k_weight=kw,
+                           eps=eps, inv_freq=inv_freq, rot_dim=rot, rope_style=style, positions=positions, slots=slots,
+                           write_kv=True)
+    x = qkv.double().cpu().view(N, nh + 2 * nkv, hd)
+    q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+    q = plain.rms_norm(q, qw.double().cpu(), eps)
+    k = plain.rms_norm(k, kw.double().cpu(), eps)
+    pos = positions.cpu()
+    if style == 0:
+        q, k = plain.rope_neox(q, pos, base, rot), plain.rope_neox(k, pos, base, rot)
+    else:   # interleaved pairs (2j, 2j+1): permute into NEOX order, rotate, permute back
+        idx = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2)])
+        inv = torch.argsort(idx)
+        def inter(t):
+            r = plain.rope_neox(t[..., idx].contiguous(), pos, base, rot)
+            return r[..., inv]
+        q, k = inter(q), inter(k)
+    t = tol(dtype, 4.0)
+    assert (q_out.double().cpu() - q).abs().max() < t
+    for i in range(N):
+        s = slots_l[i]
+        if s < 0:
+            continue
+        assert (kc[s // ps, :, s % ps].double().cpu() - k[i]).abs().max() < t
+        assert (vc[s // ps, :, s % ps].double().cpu() - v[i]).abs().max() < t
+    used = {s for s in slots_l if s >= 0}
+    flat_k = kc.float().cpu().permute(0, 2, 1, 3).reshape(n_pages * ps, -1)
+    for cell in range(n_pages * ps):
+        if cell not in used:
+            assert flat_k[cell].abs().max() == 0, "a cell no token owns was written"
+
+
+def test_argmax_ties_go_to_the_lowest_id():
+    logits = torch.full((3, 1001), -1.0)
+    logits[0, [7, 500, 999]] = 5.0
+    logits[1, 1000] = 2.0
+    logits[2] = 0.0
+    out = torch.empty(3, dtype=torch.int32).cuda()
+    K().argmax(logits.cuda(), out)
+    assert out.tolist() == [7, 1000, 0]
+
+
+@pytest.mark.parametrize("V", [503, 151936])
+@pytest.mark.parametrize("params", [(0.7, 0, 1.0, 0.0), (1.3, 5, 1.0, 0.0), (1.0, 0, 0.9, 0.0), (0.8, 0, 1.0, 0.05),
+                                    (1.0, 50, 0.8, 0.01), (0.0, 0, 1.0, 0.0)])
+def test_sample_matches_the_plain_walk(V, params):
+    T, top_k, top_p, min_p = params
+    R = 6
+    g = torch.Generator().manual_seed(V + int(T * 10) + top_k)
+    logits = torch.randn(R, V, generator=g) * 2.5
+    logits[2, 10] = logits[2, 400] = logits[2].max() + 0.5          # a tie at the top
+    u = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32).cuda()
+    f = lambda v, dt: torch.full((R,), v, dtype=dt).cuda()
+    K().sample(logits.cuda(), f(T, torch.float32), f(top_k, torch.int32), f(top_p, torch.float32),
+               f(min_p, torch.float32), u.cuda(), out)
+    got = out.tolist()
+    for r in range(R):
+        if T < 1e-5:
+            assert got[r] == plain.argmax(logits[r])
+            continue
+        probs = plain.candidate_probs(logits[r], T, top_k, top_p, min_p)
+        assert probs[got[r]] > 0, f"row {r}: token {got[r]} is outside the candidate set"
+        # the token's interval of the running mass must contain u * total (up to float32 rounding of the sums)
+        cum = torch.cumsum(probs, 0)
+        total = cum[-1].item()
+        lo = cum[got[r]].item() - probs[got[r]].item()
+        hi = cum[got[r]].item()
+        target = u[r].item() * total
+        slack = 1e-5 * total
+        assert lo - slack <= target <= hi + slack, f"row {r}: u*total={target} not in [{lo}, {hi}]"
