@@ -1,0 +1,370 @@
+// Paged flash attention on tensor cores (bf16 in, float32 softmax and accumulation) for prefill
+// portions and for decode, over block tables.
+//
+// One CTA works on a tile of rows of one (sequence, KV head): the rows are the (token, head) pairs of
+// the query heads that share this KV head ("GQA packing": row r = token r / G, head kvh * G + r % G),
+// so a K/V tile fetched once serves all G heads -- in decode, where a sequence has one token, the G
+// heads are the rows.  Keys are walked in tiles of 64; K and V tiles are gathered page by page through
+// the block table with 16-byte cp.async into swizzled shared memory (two stages), read back with
+// ldmatrix, multiplied with mma.sync m16n8k16.  With n_split > 1 the key range is cut into n_split
+// parts handled by different CTAs that write (normalised partial output, log-sum-exp) to scratch
+// memory, and a second kernel merges them: this is how a single long sequence fills the GPU in decode.
+//
+// Formula (reference, src/iian/paged_attn.cpp:112-145): scores q.k * scale; key j visible to the token
+// at position p iff j <= p and (window == 0 or p - j < window); softmax in float32; o = sum p_j v_j; a
+// row that sees no key yields zeros.  The reference's GPU path reaches the same result by gathering
+// each sequence's cells into a contiguous buffer and calling a dense flash-attention kernel
+// (src/iian/graph.cpp:474-518); here the gather happens inside the kernel.
+#include "common.cuh"
+
+namespace iian {
+
+constexpr int BN = 64;   // keys per tile
+
+struct AttnParams {
+    const __nv_bfloat16 * q;        // [N, nh, HD]
+    const __nv_bfloat16 * k_cache;  // [pages, nkv, page_size, HD]
+    const __nv_bfloat16 * v_cache;
+    __nv_bfloat16 * out;            // [N, nh * HD]
+    float * part_o;                 // [N * nh, n_split, HD]   (n_split > 1)
+    float * part_lse;               // [N * nh, n_split]
+    const int * cu_q;               // [S + 1]
+    const int * ctx_len;            // [S]
+    const int * block_table;        // [S, max_blocks]
+    int max_blocks, nh, nkv, page_size, num_pages, window, n_split;
+    float scale_log2;               // scale * log2(e)
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(unsigned dst, const void * src, bool valid) {
+    const int n = valid ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned & r0, unsigned & r1, unsigned & r2, unsigned & r3, unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned & r0, unsigned & r1, unsigned & r2, unsigned & r3, unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float * c, const unsigned * a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned *>(&v);
+}
+
+// byte offset of 16-byte chunk `chunk` of row `row` in a tile with rows of HD bf16, XOR-swizzled so that
+// the 8 rows an ldmatrix touches fall into different banks
+template <int HD> __device__ __forceinline__ unsigned swz(int row, int chunk) {
+    return (unsigned) (row * HD * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams p) {
+    constexpr int BM = 16 * NW;
+    constexpr int CH = HD / 8;                 // 16-byte chunks per row
+    constexpr int KS = HD / 16;                // k-steps of QK^T
+    constexpr int DT = HD / 8;                 // d-tiles of the output
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char * sQ = smem;
+    unsigned char * sK = sQ + BM * HD * 2;                 // [2][BN][HD]
+    unsigned char * sV = sK + 2 * BN * HD * 2;             // [2][BN][HD]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g_ = lane >> 2, t_ = lane & 3;
+    const int kvh = blockIdx.y;
+    const int s = blockIdx.z / p.n_split, split = blockIdx.z % p.n_split;
+    const int G = p.nh / p.nkv;
+    const int q0 = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - q0;
+    const int ctx = p.ctx_len[s];
+    const int pos0 = ctx - q_len;
+    const int rows_total = q_len * G;
+    const int row0 = blockIdx.x * BM;
+    if (row0 >= rows_total) return;
+
+    const int tok_min = row0 / G;
+    const int tok_max = min(rows_total - 1, row0 + BM - 1) / G;
+    const int k_hi = pos0 + tok_max;
+    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : 0;
+    const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
+    const int n_tiles = tile_hi - tile_lo + 1;
+    const int per = (n_tiles + p.n_split - 1) / p.n_split;
+    const int tile_begin = tile_lo + split * per;
+    const int tile_end = min(tile_hi + 1, tile_begin + per);
+
+    const int * bt = p.block_table + (size_t) s * p.max_blocks;
+
+    // ---- loaders ---------------------------------------------------------------------------
+    auto load_q = [&]() {
+        for (int c = tid; c < BM * CH; c += NW * 32) {
+            const int r = c / CH, ch = c % CH;
+            const int R = row0 + r;
+            const bool valid = R < rows_total;
+            const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
+            const __nv_bfloat16 * src = p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8;
+            cp_async16(smem_u32(sQ + swz<HD>(r, ch)), src, valid);
+        }
+    };
+    auto load_kv = [&](int tile, int stage) {
+        unsigned char * dK = sK + stage * BN * HD * 2;
+        unsigned char * dV = sV + stage * BN * HD * 2;
+        for (int c = tid; c < BN * CH; c += NW * 32) {
+            const int r = c / CH, ch = c % CH;
+            const int j = tile * BN + r;
+            bool valid = j <= k_hi && j >= 0;
+            size_t cell = 0;
+            if (valid) {
+                const int page = bt[j / p.page_size];
+                if (page < 0 || page >= p.num_pages) valid = false;
+                else cell = (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD + ch * 8;
+            }
+            cp_async16(smem_u32(dK + swz<HD>(r, ch)), p.k_cache + cell, valid);
+            cp_async16(smem_u32(dV + swz<HD>(r, ch)), p.v_cache + cell, valid);
+        }
+    };
+
+    float o[DT][4];
+#pragma unroll
+    for (int i = 0; i < DT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+    // rows of this thread: warp * 16 + g_ and + 8
+    int row_tok[2], row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int R = row0 + warp * 16 + g_ + 8 * h;
+        row_ok[h] = R < rows_total;
+        row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);       // position of the row's token
+    }
+
+    if (tile_begin < tile_end) {
+        load_q();
+        load_kv(tile_begin, 0);
+        cp_async_commit();
+
+        unsigned qf[KS][4];
+        bool q_loaded = false;
+
+        for (int tile = tile_begin; tile < tile_end; tile++) {
+            const int stage = (tile - tile_begin) & 1;
+            if (tile + 1 < tile_end) {
+                load_kv(tile + 1, stage ^ 1);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (!q_loaded) {
+#pragma unroll
+                for (int ks = 0; ks < KS; ks++) {
+                    const int r = warp * 16 + (lane & 15);
+                    const int ch = ks * 2 + (lane >> 4);
+                    ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], smem_u32(sQ + swz<HD>(r, ch)));
+                }
+                q_loaded = true;
+            }
+            const unsigned char * tK = sK + stage * BN * HD * 2;
+            const unsigned char * tV = sV + stage * BN * HD * 2;
+
+            // ---- S = Q K^T -------------------------------------------------------------------
+            float sc[BN / 8][4];
+#pragma unroll
+            for (int i = 0; i < BN / 8; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+                for (int np = 0; np < BN / 16; np++) {
+                    unsigned b0, b1, b2, b3;
+                    const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int ch = ks * 2 + ((lane >> 3) & 1);
+                    ldmatrix_x4(b0, b1, b2, b3, smem_u32(tK + swz<HD>(r, ch)));
+                    mma16816(sc[2 * np], qf[ks], b0, b1);
+                    mma16816(sc[2 * np + 1], qf[ks], b2, b3);
+                }
+            }
+            // ---- mask, online softmax ---------------------------------------------------------
+            const int key0 = tile * BN;
+            float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; nt++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int h = e >> 1;
+                    const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
+                    const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
+                    const float v = vis ? sc[nt][e] * p.scale_log2 : -INFINITY;
+                    sc[nt][e] = v;
+                    m_new[h] = fmaxf(m_new[h], v);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+            }
+            float corr[2], sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f(m_run[h] - m_new[h]);   // m_run = -inf gives 0
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; nt++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int h = e >> 1;
+                    const float pv = (m_new[h] == -INFINITY) ? 0.0f : exp2f(sc[nt][e] - m_new[h]);
+                    sc[nt][e] = pv;
+                    sum[h] += pv;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                l_run[h] = l_run[h] * corr[h] + sum[h];     // per-thread partial; reduced over the quad at the end
+                m_run[h] = m_new[h];
+            }
+#pragma unroll
+            for (int dt = 0; dt < DT; dt++) {
+                o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+                o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+            }
+            // ---- O += P V ------------------------------------------------------------------------
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; kk++) {
+                unsigned a[4];
+                a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+                a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+                a[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                a[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < DT / 2; dp++) {
+                    unsigned b0, b1, b2, b3;
+                    const int r = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                    const int ch = dp * 2 + (lane >> 4);
+                    ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(tV + swz<HD>(r, ch)));
+                    mma16816(o[2 * dp], a, b0, b1);
+                    mma16816(o[2 * dp + 1], a, b2, b3);
+                }
+            }
+            __syncthreads();      // everyone is done with this stage before it is refilled
+        }
+    }
+
+    // ---- finish --------------------------------------------------------------------------------
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int R = row0 + warp * 16 + g_ + 8 * h;
+        if (R >= rows_total) continue;
+        const int tok = R / G, head = kvh * G + R % G;
+        const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+        const size_t row_idx = (size_t) (q0 + tok) * p.nh + head;
+        if (p.n_split == 1) {
+            __nv_bfloat16 * dst = p.out + row_idx * HD;
+#pragma unroll
+            for (int dt = 0; dt < DT; dt++) {
+                const int d = dt * 8 + 2 * t_;
+                *reinterpret_cast<__nv_bfloat162 *>(dst + d) = __floats2bfloat162_rn(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+            }
+        } else {
+            float * dst = p.part_o + (row_idx * p.n_split + split) * HD;
+#pragma unroll
+            for (int dt = 0; dt < DT; dt++) {
+                const int d = dt * 8 + 2 * t_;
+                *reinterpret_cast<float2 *>(dst + d) = make_float2(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+            }
+            if (t_ == 0)    // log-sum-exp in base 2; -inf marks a part that saw no key
+                p.part_lse[row_idx * p.n_split + split] = l_run[h] > 0.0f ? m_run[h] + log2f(l_run[h]) : -INFINITY;
+        }
+    }
+}
+
+// merge the n_split partial results of every (token, head): one warp per row
+template <int HD>
+__global__ void attention_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_lse,
+                                         __nv_bfloat16 * __restrict__ out, int rows, int n_split) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float * lse = part_lse + (size_t) row * n_split;
+    float mx = -INFINITY;
+    for (int i = 0; i < n_split; i++) mx = fmaxf(mx, lse[i]);
+    float acc[HD / 32];
+#pragma unroll
+    for (int i = 0; i < HD / 32; i++) acc[i] = 0.0f;
+    float wsum = 0.0f;
+    if (mx != -INFINITY) {
+        for (int i = 0; i < n_split; i++) {
+            const float w = exp2f(lse[i] - mx);      // 0 for a part that saw no key
+            if (w == 0.0f) continue;
+            wsum += w;
+            const float * po = part_o + ((size_t) row * n_split + i) * HD;
+#pragma unroll
+            for (int k = 0; k < HD / 32; k++) acc[k] += w * po[lane + 32 * k];
+        }
+    }
+    const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+#pragma unroll
+    for (int k = 0; k < HD / 32; k++) out[(size_t) row * HD + lane + 32 * k] = __float2bfloat16_rn(acc[k] * inv);
+}
+
+template <int HD, int NW>
+static int launch_attention(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
+    constexpr int BM = 16 * NW;
+    const size_t smem = (size_t) BM * HD * 2 + 4 * BN * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        if (e != cudaSuccess) return 1000 + (int) e;
+        configured = true;
+    }
+    dim3 grid((max_rows + BM - 1) / BM, p.nkv, S * p.n_split);
+    attention_mma_kernel<HD, NW><<<grid, NW * 32, smem, stream>>>(p);
+    return iian_launch_status();
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+// Scratch needed for n_split > 1: part_o = N * nh * n_split * hd floats, part_lse = N * nh * n_split floats.
+IIAN_API int iian_attention_mma(
+    const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int n_split, int small_tiles, cudaStream_t stream) {
+    if (N <= 0 || S <= 0) return IIAN_OK;
+    if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
+    if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
+    if (n_split > 1 && (part_o == nullptr || part_lse == nullptr)) return IIAN_ERR_SHAPE;
+    if ((long long) S * n_split > 65535 || nkv > 65535) return IIAN_ERR_LIMIT;
+    AttnParams p;
+    p.q = (const __nv_bfloat16 *) q; p.k_cache = (const __nv_bfloat16 *) k_cache; p.v_cache = (const __nv_bfloat16 *) v_cache;
+    p.out = (__nv_bfloat16 *) out; p.part_o = part_o; p.part_lse = part_lse;
+    p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.n_split = n_split;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    const int max_rows = max_q_len * (nh / nkv);
+    int rc;
+    if (hd == 128) rc = small_tiles ? launch_attention<128, 1>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
+    else rc = small_tiles ? launch_attention<64, 1>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
+    if (rc != IIAN_OK || n_split == 1) return rc;
+    const int rows = N * nh;
+    const int warps = 4;
+    if (hd == 128) attention_combine_kernel<128><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(part_o, part_lse, (__nv_bfloat16 *) out, rows, n_split);
+    else attention_combine_kernel<64><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(part_o, part_lse, (__nv_bfloat16 *) out, rows, n_split);
+    return iian_launch_status();
+}

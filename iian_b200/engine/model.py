@@ -150,6 +150,9 @@ class Model:
         for blk in self.blocks:
             for _, part in blk.parts():
                 libs.update(part.kernel_libraries())
+        if self.dtype == torch.bfloat16:
+            from ..csrc import build
+            libs.update(build.BF16_SOURCES)
         return sorted(libs)
 
     # ---- one step ----------------------------------------------------------------------------

@@ -77,6 +77,7 @@ class AttentionMeta:
     decode_only: bool
     h_q_len: Sequence[int] = ()
     h_ctx_len: Sequence[int] = ()
+    n_split: Optional[int] = None  # fixed number of key splits (captured decode graphs); None: the kernel layer decides
 
 
 class StepContext:
@@ -103,8 +104,13 @@ class StepContext:
 
 class ModelRunner:
     def __init__(self, model: Model, *, block_size: int = 16, capacity_tokens: int, max_num_seqs: int = 4,
-                 enable_prefix_caching: bool = False, window_capacity_tokens: Optional[int] = None):
+                 enable_prefix_caching: bool = False, window_capacity_tokens: Optional[int] = None,
+                 cuda_graphs: bool = False, max_model_len: Optional[int] = None):
         self.model = model
+        self.cuda_graphs = cuda_graphs and model.device.type == "cuda"
+        self.max_model_len = max_model_len or capacity_tokens
+        self._graphs: Dict[Tuple[int, int], "_GraphSlot"] = {}
+        self.launches = 0                 # kernel launches issued through this runner (graph replays included)
         self.device = model.device
         self.block_size = block_size
         self.max_num_seqs = max_num_seqs
@@ -118,6 +124,7 @@ class ModelRunner:
         self._pinned: Optional[torch.Tensor] = None
         self._staging_dev: Optional[torch.Tensor] = None
         self._copy_done = None
+        self.last_upload_bytes = 0
         if self.device.type == "cuda":
             from ..csrc import build
             build.preload(model.kernel_libraries())      # compile what this model needs, together
@@ -133,21 +140,35 @@ class ModelRunner:
             self._copy_done.synchronize()       # the last step's upload has left the host buffer
         return self._pinned.numpy(), self._staging_dev
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def build_context(self, entries: Sequence[StepEntry], slot: Optional["_GraphSlot"] = None) -> StepContext:
+        """Pack the step's integers on the host and upload them with one copy.  With ``slot`` (a
+        captured decode graph) the batch is padded to the slot's fixed shape and written into the
+        slot's own buffers: padding sequences bring one token that is stored nowhere (cell -1)."""
         mgr = self.manager
         bs = self.block_size
-        S = len(entries)
-        N = sum(len(e.tokens) for e in entries)
-        R = sum(len(e.want) for e in entries)
+        n_real = len(entries)
         n_groups = len(mgr.groups)
-        max_blocks = []
-        for g in range(n_groups):
-            mb = 1
-            for e in entries:
-                mb = max(mb, mgr.blocks_for(e.start + len(e.tokens)))
-            max_blocks.append(mb)
+        if slot is None:
+            S = n_real
+            N = sum(len(e.tokens) for e in entries)
+            R = sum(len(e.want) for e in entries)
+            max_blocks = []
+            for g in range(n_groups):
+                mb = 1
+                for e in entries:
+                    mb = max(mb, mgr.blocks_for(e.start + len(e.tokens)))
+                max_blocks.append(mb)
+        else:
+            S = N = R = slot.num_seqs
+            max_blocks = [slot.max_blocks] * n_groups
         total = 3 * N + (S + 1) + 2 * S + R + sum(N + S * mb for mb in max_blocks)
-        host, dev = self._stage(total)
+        if slot is None:
+            host, dev = self._stage(total)
+            pinned = self._pinned
+        else:
+            if slot.copy_done is not None:
+                slot.copy_done.synchronize()
+            host, dev, pinned = slot.pinned.numpy(), slot.staging, slot.pinned
         off = 0
 
         def take(n):
@@ -161,7 +182,18 @@ class ModelRunner:
         r_slots = [take(N) for _ in range(n_groups)]
         r_bt = [take(S * mb) for mb in max_blocks]
 
-        ctx = StepContext(self.workspace)
+        ctx = StepContext(self.workspace if slot is None else slot.workspace)
+        if slot is not None:       # padding first; real sequences overwrite the front
+            host[r_tok[0]: r_tok[1]] = 0
+            host[r_pos[0]: r_pos[1]] = 0
+            host[r_seq[0]: r_seq[1]] = -1
+            host[r_cu[0]: r_cu[1]] = np.arange(S + 1, dtype=np.int32)
+            host[r_ctx[0]: r_ctx[1]] = 1
+            host[r_slot_state[0]: r_slot_state[1]] = -1
+            host[r_rows[0]: r_rows[1]] = np.arange(R, dtype=np.int32)
+            for g in range(n_groups):
+                host[r_slots[g][0]: r_slots[g][1]] = -1
+                host[r_bt[g][0]: r_bt[g][1]] = 0
         t0 = 0
         rows: List[int] = []
         fresh: List[int] = []
@@ -202,13 +234,19 @@ class ModelRunner:
             ctx.h_ctx_len.append(e.start + n)
             ctx.h_state_slots.append(e.cache.state_slot)
             t0 += n
-        host[r_rows[0]: r_rows[1]] = np.asarray(rows, dtype=np.int32) if rows else 0
+        if slot is None:
+            host[r_rows[0]: r_rows[1]] = np.asarray(rows, dtype=np.int32) if rows else 0
 
-        dev[:total].copy_(self._pinned[:total], non_blocking=True)
+        dev[:total].copy_(pinned[:total], non_blocking=True)
         if self.device.type == "cuda":
-            if self._copy_done is None:
-                self._copy_done = torch.cuda.Event()
-            self._copy_done.record()
+            if slot is None:
+                if self._copy_done is None:
+                    self._copy_done = torch.cuda.Event()
+                self._copy_done.record()
+            else:
+                if slot.copy_done is None:
+                    slot.copy_done = torch.cuda.Event()
+                slot.copy_done.record()
         self.storage.zero_state(fresh)
 
         def view(r, shape=None):
@@ -218,15 +256,19 @@ class ModelRunner:
         ctx.tokens, ctx.positions, ctx.seq_of_token = view(r_tok), view(r_pos), view(r_seq)
         ctx.cu_q, ctx.ctx_len, ctx.state_slots, ctx.out_rows = view(r_cu), view(r_ctx), view(r_slot_state), view(r_rows)
         ctx.num_tokens, ctx.num_seqs = N, S
-        ctx.max_q_len = max(ctx.h_q_len) if S else 0
-        ctx.max_ctx = max(ctx.h_ctx_len) if S else 0
+        ctx.max_q_len = max(ctx.h_q_len) if ctx.h_q_len else 0
+        ctx.max_ctx = max(ctx.h_ctx_len) if ctx.h_ctx_len else 0
+        if slot is not None:
+            ctx.max_q_len, ctx.max_ctx = 1, slot.ctx_bucket
         ctx.decode_only = ctx.max_q_len == 1
+        ctx.upload_bytes = total * 4
         for g in range(n_groups):
             ctx.metas.append(AttentionMeta(
                 positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
                 block_table=view(r_bt[g], (S, max_blocks[g])), slots=view(r_slots[g]),
                 num_seqs=S, num_tokens=N, max_q_len=ctx.max_q_len, max_ctx=ctx.max_ctx,
-                decode_only=ctx.decode_only, h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len))
+                decode_only=ctx.decode_only, h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len,
+                n_split=slot.n_split if slot is not None else None))
         return ctx
 
     # ---- the step -----------------------------------------------------------------------------
@@ -237,5 +279,76 @@ class ModelRunner:
             return None
         if len(entries) > self.max_num_seqs:
             raise ValueError(f"{len(entries)} requests in one step, the runner was built for {self.max_num_seqs}")
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._step_graph(entries)
         ctx = self.build_context(entries)
-        return self.model.forward(ctx, self.storage)
+        before = _launch_count()
+        out = self.model.forward(ctx, self.storage)
+        self.launches += _launch_count() - before
+        self.last_upload_bytes = ctx.upload_bytes
+        return out
+
+    # ---- decode-only steps replayed from captured CUDA graphs ------------------------------------
+    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """The reference replays whole steps from CUDA graphs keyed by the batch's shape
+        (src/iian/engine.cpp:553-574, CMakeLists.txt:32-37).  Here a graph is keyed by (padded number of
+        sequences, context bucket); its kernels read the step's integers from fixed device buffers, so a
+        replay needs one upload and one launch."""
+        n = len(entries)
+        bucket = 1
+        while bucket < n:
+            bucket *= 2
+        bucket = min(bucket, max(self.max_num_seqs, n))
+        max_ctx = max(e.start + 1 for e in entries)
+        ctx_bucket = 256
+        while ctx_bucket < max_ctx:
+            ctx_bucket *= 2
+        key = (bucket, ctx_bucket)
+        slot = self._graphs.get(key)
+        if slot is None:
+            slot = self._capture(bucket, ctx_bucket, entries)
+            self._graphs[key] = slot
+        ctx = self.build_context(entries, slot)
+        slot.graph.replay()
+        self.launches += slot.launches
+        self.last_upload_bytes = ctx.upload_bytes
+        return slot.logits[:n]
+
+    def _capture(self, num_seqs: int, ctx_bucket: int, entries: Sequence[StepEntry]) -> "_GraphSlot":
+        mgr = self.manager
+        n_groups = len(mgr.groups)
+        max_blocks = max(1, mgr.blocks_for(max(self.max_model_len, ctx_bucket)))
+        total = 3 * num_seqs + (num_seqs + 1) + 3 * num_seqs + n_groups * (num_seqs + num_seqs * max_blocks)
+        slot = _GraphSlot()
+        slot.num_seqs, slot.ctx_bucket, slot.max_blocks = num_seqs, ctx_bucket, max_blocks
+        slot.staging = torch.empty(total, dtype=torch.int32, device=self.device)
+        slot.pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        slot.workspace = Workspace(self.device)
+        slot.copy_done = None
+        kv_heads = [n.num_kv_heads for n in self.model.cache_needs().values() if isinstance(n, KVNeed)]
+        k = ops.kernels()
+        slot.n_split = k.attention_splits(num_seqs, min(kv_heads), ctx_bucket) if kv_heads and hasattr(k, "attention_splits") else 1
+        # run once eagerly (loads kernels, sizes every buffer), then capture the same launches
+        ctx = self.build_context(entries, slot)
+        self.model.forward(ctx, self.storage)
+        torch.cuda.synchronize(self.device)
+        slot.workspace.frozen = True
+        before = _launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            slot.logits = self.model.forward(ctx, self.storage)
+        slot.launches = _launch_count() - before
+        slot.graph = graph
+        return slot
+
+
+class _GraphSlot:
+    """Everything a captured decode graph owns: fixed-shape integer buffers, workspace, output."""
+
+    num_seqs = ctx_bucket = max_blocks = n_split = launches = 0
+    staging = pinned = workspace = copy_done = graph = logits = None
+
+
+def _launch_count() -> int:
+    from ..ops import cuda_backend
+    return cuda_backend.LAUNCHES[0]

@@ -69,6 +69,7 @@ class Qwen3Config:
     sliding_window: Optional[int] = None        # keys visible to a windowed layer (incl. the query's own)
     layer_types: Tuple[str, ...] = ()            # "full_attention" | "sliding_attention" per layer
     hidden_act: str = "silu"
+    eos_token_ids: Tuple[int, ...] = ()          # config.json "eos_token_id": one id or a list
 
     @property
     def q_size(self) -> int:
@@ -139,6 +140,15 @@ def qwen3_config_from_dict(raw: Mapping[str, Any]) -> Qwen3Config:
             raise ConfigError("config.json: a layer is 'sliding_attention' but 'sliding_window' is not a positive integer")
     else:
         window = None
+    eos = raw.get("eos_token_id")
+    if eos is None:
+        eos_ids: Tuple[int, ...] = ()
+    elif isinstance(eos, int) and not isinstance(eos, bool):
+        eos_ids = (eos,)
+    elif isinstance(eos, list) and all(isinstance(e, int) and not isinstance(e, bool) for e in eos):
+        eos_ids = tuple(eos)
+    else:
+        raise ConfigError(f"config.json: 'eos_token_id' must be an integer or a list of integers, got {eos!r}")
     return Qwen3Config(
         vocab_size=_need(raw, "vocab_size"),
         hidden_size=hidden,
@@ -154,6 +164,7 @@ def qwen3_config_from_dict(raw: Mapping[str, Any]) -> Qwen3Config:
         sliding_window=window,
         layer_types=layer_types,
         hidden_act=act,
+        eos_token_ids=eos_ids,
     )
 
 
@@ -188,6 +199,8 @@ class Qwen3(Architecture):
         }
         if windowed:
             d["layer_types"] = list(c.layer_types)
+        if c.eos_token_ids:
+            d["eos_token_id"] = c.eos_token_ids[0] if len(c.eos_token_ids) == 1 else list(c.eos_token_ids)
         return d
 
     def build_spec(self, c: Qwen3Config) -> ModelSpec:

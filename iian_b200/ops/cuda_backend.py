@@ -29,8 +29,12 @@ _ERRS = {1: "element types not supported by this kernel", 2: "a size this kernel
          3: "a pointer or stride is not aligned as the kernel requires", 4: "beyond the kernel's stated maximum"}
 
 
+LAUNCHES = [0]        # kernel launches issued by this module (a split attention counts its merge kernel too)
+
+
 def _check(code: int, what: str) -> None:
     if code == 0:
+        LAUNCHES[0] += 1
         return
     if code >= 1000:
         raise KernelError(f"{what}: CUDA launch failed with error {code - 1000}")
@@ -152,8 +156,41 @@ class CudaKernels:
             return
         self._linear_dispatch(x, w, out, n, m, k)
 
+    # rows up to which the weight-streaming kernel is used; above it the library GEMM takes over
+    SKINNY_MAX_ROWS = 64
+
     def _linear_dispatch(self, x, w, out, n, m, k) -> None:
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+                self.gemm_skinny(x, w, out)
+                return
+            if n > 16 and self._library_gemm(x, w, out):
+                return
         self.gemm_simt(x, w, out)
+
+    _library_f32_out = True
+
+    def _library_gemm(self, x, w, out) -> bool:
+        """cuBLAS through torch.mm, for large bfloat16 products (as the reference does for large batches)."""
+        if out.dtype == torch.bfloat16:
+            torch.mm(x, w.t(), out=out)
+            return True
+        if out.dtype == torch.float32 and self._library_f32_out:
+            try:
+                torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+                return True
+            except (TypeError, RuntimeError):
+                type(self)._library_f32_out = False
+        return False
+
+    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        n, k = x.shape
+        m = w.shape[0]
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise KernelError("gemm_skinny: x and w must be bfloat16")
+        fn = _fn("gemm_skinny", "iian_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
+                  n, m, k, _stream()), "gemm_skinny")
 
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         n, k = x.shape
@@ -205,8 +242,60 @@ class CudaKernels:
         self._attention_dispatch(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale, window)
 
     def _attention_dispatch(self, q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, window) -> None:
-        self.paged_attention_generic(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+        if q.dtype == torch.bfloat16 and hd in (64, 128):
+            self.paged_attention_mma(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                                      scale=scale, window=window)
+        else:
+            self.paged_attention_generic(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                                         scale=scale, window=window)
+
+    TARGET_CTAS = 148 * 3          # SMs x resident CTAs of the decode configuration
+    MAX_SPLITS = 32
+    _scratch = {}
+
+    def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
+        """How many parts the keys of a decode step are cut into, so that few long sequences still fill
+        the GPU."""
+        tiles = max(1, (max_ctx + 63) // 64)
+        want = -(-self.TARGET_CTAS // max(1, num_seqs * num_kv_heads))
+        return max(1, min(want, tiles, self.MAX_SPLITS))
+
+    def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
+        t = self._scratch.get(device)
+        if t is None or t.numel() < n_floats:
+            t = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+            self._scratch[device] = t
+        return t
+
+    def paged_attention_mma(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
+                            n_split: Optional[int] = None, small_tiles: Optional[bool] = None) -> None:
+        n = q.shape[0]
+        if k_cache.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            raise KernelError("paged_attention_mma: bfloat16 only")
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or q.numel() != n * num_heads * head_dim:
+            raise KernelError("paged_attention_mma: cache / q shapes do not match the head counts")
+        decode = meta.max_q_len * (num_heads // num_kv_heads) <= 16
+        if small_tiles is None:
+            small_tiles = decode
+        if n_split is None:
+            n_split = getattr(meta, "n_split", None) or (self.attention_splits(meta.num_seqs, num_kv_heads, meta.max_ctx) if decode else 1)
+        part_o = part_lse = 0
+        if n_split > 1:
+            rows = n * num_heads
+            scratch = self.attention_scratch(q.device, rows * n_split * (head_dim + 1))
+            part_o = scratch.data_ptr()
+            part_lse = part_o + rows * n_split * head_dim * 4
+        bt = meta.block_table
+        fn = _fn("attention_mma", "iian_attention_mma",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
+                  part_o, part_lse, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
+                  num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split,
+                  1 if small_tiles else 0, _stream()), "attention_mma")
+        if n_split > 1:
+            LAUNCHES[0] += 1
 
     def paged_attention_generic(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale,
                                 window) -> None:

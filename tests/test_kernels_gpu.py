@@ -289,3 +289,70 @@ def test_sample_matches_the_plain_walk(V, params):
         target = u[r].item() * total
         slack = 1e-5 * total
         assert lo - slack <= target <= hi + slack, f"row {r}: u*total={target} not in [{lo}, {hi}]"
+
+
+@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,M,K_", [(1, 70, 64), (3, 16, 32), (8, 257, 96), (9, 100, 160), (17, 48, 4096), (33, 130, 320),
+                                    (64, 1000, 1024), (2, 4096, 12288)])
+def test_gemm_skinny(od, B, M, K_):
+    x = rnd(B, K_, dtype=torch.bfloat16, seed=20)
+    w = rnd(M, K_, dtype=torch.bfloat16, seed=21)
+    out = torch.full((B, M), float("nan"), dtype=od).cuda()
+    K().gemm_skinny(x, w, out)
+    want = x.double().cpu() @ w.double().cpu().T
+    assert (out.double().cpu() - want).abs().max() < tol(od if od == torch.bfloat16 else torch.float32, want.abs().max().item()) * \
+        (1 if od == torch.bfloat16 else 10)
+
+
+def test_gemm_skinny_rows_do_not_depend_on_the_batch():
+    x = rnd(40, 512, dtype=torch.bfloat16, seed=22)
+    w = rnd(90, 512, dtype=torch.bfloat16, seed=23)
+    full = torch.empty(40, 90, dtype=torch.float32).cuda()
+    K().gemm_skinny(x, w, full)
+    one = torch.empty(1, 90, dtype=torch.float32).cuda()
+    for r in (0, 17, 39):
+        K().gemm_skinny(x[r:r + 1].contiguous(), w, one)
+        assert torch.equal(one[0], full[r])
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    from iian_b200.ops.cuda_backend import KernelError
+    x = rnd(2, 40, dtype=torch.bfloat16)
+    w = rnd(8, 40, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):
+        K().gemm_skinny(x, w, torch.empty(2, 8, dtype=torch.bfloat16).cuda())      # K not a multiple of 32
+    x = rnd(65, 64, dtype=torch.bfloat16)
+    w = rnd(8, 64, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):
+        K().gemm_skinny(x, w, torch.empty(65, 8, dtype=torch.bfloat16).cuda())     # more than 64 rows
+
+
+MMA_CASES = [
+    # nh, nkv, hd, page, ctx_lens, q_lens, window
+    (8, 2, 128, 16, [300, 257, 31], [1, 1, 1], None),
+    (8, 2, 64, 16, [200, 77], [64, 77], None),
+    (32, 8, 128, 16, [1152], [1], None),
+    (6, 3, 64, 8, [37, 5, 64, 1], [37, 1, 20, 1], None),
+    (4, 4, 128, 12, [130, 90], [130, 13], 33),
+    (12, 2, 128, 16, [700, 65, 64, 63], [300, 65, 1, 63], None),
+    (6, 1, 64, 16, [500], [1], 100),
+    (16, 2, 128, 32, [2100], [2048], None),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+@pytest.mark.parametrize("standout", [False, True])
+@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles"])
+def test_paged_attention_mma(case, standout, mode):
+    nh, nkv, hd, ps, ctx_lens, q_lens, window = case
+    dtype = torch.bfloat16
+    q, kc, vc, m, want, scale = attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=5, standout=standout)
+    out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=dtype).cuda()
+    kw = {}
+    if mode == "split5":
+        kw = dict(n_split=5, small_tiles=True)
+    elif mode == "big_tiles":
+        kw = dict(n_split=1, small_tiles=False)
+    K().paged_attention_mma(q, kc, vc, out, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale, window=window, **kw)
+    err = (out.double().cpu() - want).abs().max().item()
+    assert err < tol(dtype, max(1.0, want.abs().max().item())), err
