@@ -368,3 +368,61 @@ IIAN_API int iian_attention_mma(
     else attention_combine_kernel<64><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(part_o, part_lse, (__nv_bfloat16 *) out, rows, n_split);
     return iian_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Split-KV attention for callers that must not allocate.  Declared in attention_mma.h.
+//
+// The split path above needs scratch memory for the partial results, and the regular entry point
+// expects the caller to bring it.  Some callers cannot: a program that has already handed the whole
+// device to a memory pool of its own (a cudaMalloc would fail, or take memory the pool believes it
+// owns), or a latency-critical loop that cannot afford cudaMalloc's device-wide synchronisation.  For
+// them the scratch lives in a fixed array inside this library.
+//
+//  * The array has kNoAllocScratchFloats floats (8 MiB).  Every GPU on which this library is loaded
+//    holds that much until the process exits.
+//  * A call needs N * nh * n_split * (hd + 1) floats; a larger request is refused with
+//    IIAN_ERR_LIMIT and nothing is launched.  iian_attention_mma_noalloc_capacity() returns the limit.
+//  * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
+//    device current) and remembers it per device.  Make that first call before any stream capture.
+//  * No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
+//  * All calls share the one array, and it keeps what the last call left in it.  Nothing in it has to
+//    start at zero: each (row, split) cell is fully written by the CTA that owns it before the merge
+//    kernel of the same call reads it.  Two calls whose kernels overlap on the GPU (different streams
+//    without an ordering between them) race on the array; order them.
+// ---------------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchFloats = (size_t) 2 * 1024 * 1024;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float * g_noalloc_ptr[kMaxDevices] = {};     // device address of the array, per device; host code must not
+                                             // pass g_noalloc_scratch itself to a kernel
+}
+
+IIAN_API long long iian_attention_mma_noalloc_capacity() { return (long long) kNoAllocScratchFloats; }
+
+IIAN_API int iian_attention_mma_noalloc(
+    const void * q, const void * k_cache, const void * v_cache, void * out,
+    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int n_split, int small_tiles, cudaStream_t stream) {
+    if (N <= 0 || S <= 0) return IIAN_OK;
+    if (n_split < 1 || nh <= 0 || hd <= 0) return IIAN_ERR_SHAPE;
+    const unsigned long long need = (unsigned long long) N * nh * n_split * (unsigned long long) (hd + 1);
+    if (n_split > 1 && need > kNoAllocScratchFloats) return IIAN_ERR_LIMIT;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return 1000 + (int) e;
+    if (dev < 0 || dev >= kMaxDevices) return IIAN_ERR_LIMIT;
+    if (g_noalloc_ptr[dev] == nullptr) {          // set-up, once per device, with that device current
+        float * ptr = nullptr;
+        e = cudaGetSymbolAddress((void **) &ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) return 1000 + (int) e;
+        g_noalloc_ptr[dev] = ptr;
+    }
+    float * part_o = g_noalloc_ptr[dev];
+    float * part_lse = part_o + (size_t) N * nh * n_split * hd;
+    return iian_attention_mma(q, k_cache, v_cache, out, part_o, part_lse, cu_q, ctx_len, block_table, max_blocks,
+                              N, S, max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, n_split, small_tiles,
+                              stream);
+}
