@@ -292,6 +292,248 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
     }
 }
 
+// Decode form: few rows (the G heads of one token, up to 16 rows per CTA), many keys.  The four warps
+// of a CTA share the rows and split the KEYS of every 64-key tile (16 each); each warp keeps a running
+// (max, sum, output) of its own, and the four are merged through shared memory at the end.  Three
+// cp.async stages keep two tiles in flight while one is consumed.  Every thread fetches one half row of
+// K and of V per tile, so a tile costs it one block-table lookup.
+template <int HD>
+__global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams p) {
+    constexpr int NW = 4, BM = 16, STAGES = 3;
+    constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
+    constexpr int TILE_BYTES = BN * HD * 2;
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char * sQ = smem;                               // [16][HD]
+    unsigned char * sK = sQ + BM * HD * 2;                   // [STAGES][BN][HD]
+    unsigned char * sV = sK + STAGES * TILE_BYTES;           // [STAGES][BN][HD]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g_ = lane >> 2, t_ = lane & 3;
+    const int kvh = blockIdx.y;
+    const int s = blockIdx.z / p.n_split, split = blockIdx.z % p.n_split;
+    const int G = p.nh / p.nkv;
+    const int q0 = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - q0;
+    const int ctx = p.ctx_len[s];
+    const int pos0 = ctx - q_len;
+    const int rows_total = q_len * G;
+    const int row0 = blockIdx.x * BM;
+    if (row0 >= rows_total) return;
+
+    const int tok_min = row0 / G;
+    const int tok_max = min(rows_total - 1, row0 + BM - 1) / G;
+    const int k_hi = pos0 + tok_max;
+    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : 0;
+    const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
+    const int n_tiles = tile_hi - tile_lo + 1;
+    const int per = (n_tiles + p.n_split - 1) / p.n_split;
+    const int tile_begin = tile_lo + split * per;
+    const int tile_end = min(tile_hi + 1, tile_begin + per);
+    const int n_my = max(0, tile_end - tile_begin);
+    const int * bt = p.block_table + (size_t) s * p.max_blocks;
+
+    auto load_kv = [&](int tile, int stage) {
+        const int r = tid >> 1, c0 = (tid & 1) * (CH / 2);       // one half row per thread
+        const int j = tile * BN + r;
+        bool valid = j <= k_hi;
+        size_t cell = 0;
+        if (valid) {
+            const int page = bt[j / p.page_size];
+            if (page < 0 || page >= p.num_pages) valid = false;
+            else cell = (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+        }
+        unsigned char * dK = sK + stage * TILE_BYTES;
+        unsigned char * dV = sV + stage * TILE_BYTES;
+#pragma unroll
+        for (int c = 0; c < CH / 2; c++) {
+            cp_async16(smem_u32(dK + swz<HD>(r, c0 + c)), p.k_cache + cell + (c0 + c) * 8, valid);
+            cp_async16(smem_u32(dV + swz<HD>(r, c0 + c)), p.v_cache + cell + (c0 + c) * 8, valid);
+        }
+    };
+
+    float o[DT][4];
+#pragma unroll
+    for (int i = 0; i < DT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    int row_tok[2], row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int R = row0 + g_ + 8 * h;
+        row_ok[h] = R < rows_total;
+        row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);
+    }
+
+    if (n_my > 0) {
+        for (int c = tid; c < BM * CH; c += NW * 32) {          // Q rows
+            const int r = c / CH, ch = c % CH;
+            const int R = row0 + r;
+            const bool valid = R < rows_total;
+            const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
+            cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
+        }
+        load_kv(tile_begin, 0);
+        cp_async_commit();
+        if (n_my > 1) load_kv(tile_begin + 1, 1);
+        cp_async_commit();
+
+        unsigned qf[KS][4];
+        for (int i = 0; i < n_my; i++) {
+            if (i + 2 < n_my) load_kv(tile_begin + i + 2, (i + 2) % STAGES);
+            cp_async_commit();
+            cp_async_wait<2>();
+            __syncthreads();
+            if (i == 0) {
+#pragma unroll
+                for (int ks = 0; ks < KS; ks++)
+                    ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                                smem_u32(sQ + swz<HD>(lane & 15, ks * 2 + (lane >> 4))));
+            }
+            const unsigned char * tK = sK + (i % STAGES) * TILE_BYTES;
+            const unsigned char * tV = sV + (i % STAGES) * TILE_BYTES;
+            float sc[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                unsigned b0, b1, b2, b3;
+                const int r = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+                ldmatrix_x4(b0, b1, b2, b3, smem_u32(tK + swz<HD>(r, ks * 2 + ((lane >> 3) & 1))));
+                mma16816(sc[0], qf[ks], b0, b1);
+                mma16816(sc[1], qf[ks], b2, b3);
+            }
+            const int key0 = (tile_begin + i) * BN + warp * 16;
+            float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int h = e >> 1;
+                    const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
+                    const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
+                    const float v = vis ? sc[nt][e] * p.scale_log2 : -INFINITY;
+                    sc[nt][e] = v;
+                    m_new[h] = fmaxf(m_new[h], v);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+            }
+            float corr[2], sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int h = 0; h < 2; h++) corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f(m_run[h] - m_new[h]);
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int h = e >> 1;
+                    const float pv = (m_new[h] == -INFINITY) ? 0.0f : exp2f(sc[nt][e] - m_new[h]);
+                    sc[nt][e] = pv;
+                    sum[h] += pv;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                l_run[h] = l_run[h] * corr[h] + sum[h];
+                m_run[h] = m_new[h];
+            }
+            if (corr[0] != 1.0f || corr[1] != 1.0f) {
+#pragma unroll
+                for (int dt = 0; dt < DT; dt++) {
+                    o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+                    o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+                }
+            }
+            unsigned a[4];
+            a[0] = pack_bf16(sc[0][0], sc[0][1]);
+            a[1] = pack_bf16(sc[0][2], sc[0][3]);
+            a[2] = pack_bf16(sc[1][0], sc[1][1]);
+            a[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+            for (int dp = 0; dp < DT / 2; dp++) {
+                unsigned b0, b1, b2, b3;
+                const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(tV + swz<HD>(r, dp * 2 + (lane >> 4))));
+                mma16816(o[2 * dp], a, b0, b1);
+                mma16816(o[2 * dp + 1], a, b2, b3);
+            }
+            __syncthreads();
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- merge the four warps ------------------------------------------------------------------
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float * mo = reinterpret_cast<float *>(sK);              // [NW][16][HD]   (stage memory is free now)
+    float * ml = mo + NW * BM * HD;                          // [NW][16][2]
+    __syncthreads();
+#pragma unroll
+    for (int dt = 0; dt < DT; dt++) {
+        const int d = dt * 8 + 2 * t_;
+        *reinterpret_cast<float2 *>(mo + ((size_t) warp * BM + g_) * HD + d) = make_float2(o[dt][0], o[dt][1]);
+        *reinterpret_cast<float2 *>(mo + ((size_t) warp * BM + g_ + 8) * HD + d) = make_float2(o[dt][2], o[dt][3]);
+    }
+    if (t_ == 0) {
+        ml[(warp * BM + g_) * 2] = m_run[0];         ml[(warp * BM + g_) * 2 + 1] = l_run[0];
+        ml[(warp * BM + g_ + 8) * 2] = m_run[1];     ml[(warp * BM + g_ + 8) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    {
+        const int r = tid >> 3, part = tid & 7;              // 8 threads per row, HD / 8 columns each
+        const int R = row0 + r;
+        if (R < rows_total) {
+            float mw[NW], m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NW; w++) { mw[w] = ml[(w * BM + r) * 2]; m = fmaxf(m, mw[w]); }
+            float sw[NW], l = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NW; w++) {
+                sw[w] = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - m);
+                l += sw[w] * ml[(w * BM + r) * 2 + 1];
+            }
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const int tok = R / G, head = kvh * G + R % G;
+            const size_t row_idx = (size_t) (q0 + tok) * p.nh + head;
+#pragma unroll
+            for (int c = 0; c < HD / 8; c += 2) {
+                const int d = part * (HD / 8) + c;
+                float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+                for (int w = 0; w < NW; w++) {
+                    const float2 x = *reinterpret_cast<const float2 *>(mo + ((size_t) w * BM + r) * HD + d);
+                    v0 += sw[w] * x.x;
+                    v1 += sw[w] * x.y;
+                }
+                if (p.n_split == 1)
+                    *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
+                else
+                    *reinterpret_cast<float2 *>(p.part_o + (row_idx * p.n_split + split) * HD + d) = make_float2(v0 * inv, v1 * inv);
+            }
+            if (p.n_split > 1 && part == 0)
+                p.part_lse[row_idx * p.n_split + split] = l > 0.0f ? m + log2f(l) : -INFINITY;
+        }
+    }
+}
+
+template <int HD>
+static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
+    const size_t smem = (size_t) 16 * HD * 2 + 2 * 3 * BN * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        if (e != cudaSuccess) return 1000 + (int) e;
+        configured = true;
+    }
+    dim3 grid((max_rows + 15) / 16, p.nkv, S * p.n_split);
+    attention_decode_kernel<HD><<<grid, 128, smem, stream>>>(p);
+    return iian_launch_status();
+}
+
 // merge the n_split partial results of every (token, head): one warp per row
 template <int HD>
 __global__ void attention_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_lse,
@@ -359,8 +601,8 @@ IIAN_API int iian_attention_mma(
     p.scale_log2 = scale * 1.4426950408889634f;
     const int max_rows = max_q_len * (nh / nkv);
     int rc;
-    if (hd == 128) rc = small_tiles ? launch_attention<128, 1>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
-    else rc = small_tiles ? launch_attention<64, 1>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
+    if (hd == 128) rc = small_tiles ? launch_decode<128>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
+    else rc = small_tiles ? launch_decode<64>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
     if (rc != IIAN_OK || n_split == 1) return rc;
     const int rows = N * nh;
     const int warps = 4;

@@ -27,6 +27,7 @@ __global__ void embedding_kernel(const W * __restrict__ table, const int * __res
 }
 
 // residual (f32, in place) += delta (A, optional); out (A) = rmsnorm(residual) * weight (f32)
+// General form: two passes over the row, any H.
 template <typename A>
 __global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta,
                                     const float * __restrict__ weight, A * __restrict__ out,
@@ -52,6 +53,65 @@ __global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __r
     const float inv = rsqrtf(ss / (float) H + eps);
     A * o = out + base;
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<A>(r[i] * inv * weight[i]);
+}
+
+template <typename A> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float * p) { return *reinterpret_cast<const float4 *>(p); }
+    static __device__ __forceinline__ void store(float * p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16 * p) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 * p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned *>(&a);
+        raw.y = *reinterpret_cast<unsigned *>(&b);
+        *reinterpret_cast<uint2 *>(p) = raw;
+    }
+};
+
+// Fast form for H % 4 == 0 and H <= 4 * VPT * blockDim: the row stays in registers, one pass over
+// memory, 16-byte accesses.  Thread t owns the float4 groups t, t + blockDim, ... (fixed by H alone).
+template <typename A, int VPT>
+__global__ void add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ delta,
+                                        const float * __restrict__ weight, A * __restrict__ out,
+                                        int H, float eps) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    const int groups = H >> 2;
+    float4 v[VPT];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int gi = threadIdx.x + k * blockDim.x;
+        if (gi < groups) {
+            float4 x = Vec4<float>::load(residual + base + 4 * gi);
+            if (delta != nullptr) {
+                const float4 d = Vec4<A>::load(delta + base + 4 * gi);
+                x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+                Vec4<float>::store(residual + base + 4 * gi, x);
+            }
+            v[k] = x;
+            ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float) H + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int gi = threadIdx.x + k * blockDim.x;
+        if (gi < groups) {
+            const float4 w = Vec4<float>::load(weight + 4 * gi);
+            Vec4<A>::store(out + base + 4 * gi, make_float4(v[k].x * inv * w.x, v[k].y * inv * w.y,
+                                                             v[k].z * inv * w.z, v[k].w * inv * w.w));
+        }
+    }
 }
 
 // x (A, read only) -> out (A) = rmsnorm(x) * weight; no residual
@@ -81,6 +141,29 @@ __global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ o
     const float u = to_f32(gate_up[row * 2 * F + F + col]);
     const float s = g / (1.0f + expf(-g));
     out[idx] = from_f32<A>(s * u);
+}
+
+// 8 elements per thread with 16-byte (bf16) or 2 x 16-byte (f32) accesses; needs F % 8 == 0
+template <typename A>
+__global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t groups) {
+    const size_t gidx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (gidx >= groups) return;
+    const int per_row = F >> 3;
+    const size_t row = gidx / per_row;
+    const int col = (int) (gidx - row * per_row) << 3;
+    const A * g = gate_up + row * 2 * F + col;
+    const A * u = g + F;
+    A * o = out + row * F + col;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float4 gv = Vec4<A>::load(g + 4 * h), uv = Vec4<A>::load(u + 4 * h);
+        float4 r;
+        r.x = gv.x / (1.0f + expf(-gv.x)) * uv.x;
+        r.y = gv.y / (1.0f + expf(-gv.y)) * uv.y;
+        r.z = gv.z / (1.0f + expf(-gv.z)) * uv.z;
+        r.w = gv.w / (1.0f + expf(-gv.w)) * uv.w;
+        Vec4<A>::store(o + 4 * h, r);
+    }
 }
 
 template <typename T>
@@ -120,10 +203,23 @@ IIAN_API int iian_embedding(const void * table, int table_dtype, const int * tok
 IIAN_API int iian_add_rms_norm(float * residual, const void * delta, const float * weight, void * out,
                                int act_dtype, int N, int H, float eps, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
-    const int threads = 256;   // fixed: the reduction order must not depend on the batch
+    if (act_dtype != IIAN_F32 && act_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
+    // the launch shape is a function of H alone, so the order of every sum does not depend on the batch
+    const bool aligned = H % 4 == 0 && ((uintptr_t) residual & 15) == 0 && ((uintptr_t) weight & 15) == 0 &&
+                         ((uintptr_t) out & 7) == 0 && ((uintptr_t) delta & 7) == 0;
+    if (aligned && H <= 4 * 4 * 1024) {
+        const int groups = H / 4;
+        int threads = 128;
+        while (threads < 1024 && threads * 2 <= groups) threads *= 2;      // >= 2 groups per thread up to 1024 threads
+        while (threads * 4 < groups) threads *= 2;
+        if (threads > 1024) threads = 1024;
+        if (act_dtype == IIAN_F32) add_rms_norm_vec_kernel<float, 4><<<N, threads, 0, stream>>>(residual, (const float *) delta, weight, (float *) out, H, eps);
+        else add_rms_norm_vec_kernel<__nv_bfloat16, 4><<<N, threads, 0, stream>>>(residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
+        return iian_launch_status();
+    }
+    const int threads = 256;
     if (act_dtype == IIAN_F32) add_rms_norm_kernel<float><<<N, threads, 0, stream>>>(residual, (const float *) delta, weight, (float *) out, H, eps);
-    else if (act_dtype == IIAN_BF16) add_rms_norm_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>(residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
-    else return IIAN_ERR_DTYPE;
+    else add_rms_norm_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>(residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
     return iian_launch_status();
 }
 
@@ -141,6 +237,13 @@ IIAN_API int iian_swiglu(const void * gate_up, void * out, int act_dtype, int N,
     const size_t total = (size_t) N * F;
     if (total == 0) return IIAN_OK;
     const int threads = 256;
+    if (F % 8 == 0 && ((uintptr_t) gate_up & 15) == 0 && ((uintptr_t) out & 15) == 0 && (act_dtype == IIAN_F32 || act_dtype == IIAN_BF16)) {
+        const size_t groups = total / 8;
+        const unsigned vblocks = (unsigned) ((groups + threads - 1) / threads);
+        if (act_dtype == IIAN_F32) swiglu_vec_kernel<float><<<vblocks, threads, 0, stream>>>((const float *) gate_up, (float *) out, F, groups);
+        else swiglu_vec_kernel<__nv_bfloat16><<<vblocks, threads, 0, stream>>>((const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, groups);
+        return iian_launch_status();
+    }
     const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
     if (act_dtype == IIAN_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float *) gate_up, (float *) out, F, total);
     else if (act_dtype == IIAN_BF16) swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, total);

@@ -16,9 +16,6 @@
 
 namespace iian {
 
-constexpr int kSkinnyWarps = 8;
-constexpr int kUnroll = 4;
-
 __device__ __forceinline__ uint4 ld_stream(const uint4 * p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -33,89 +30,150 @@ __device__ __forceinline__ void mma_bf16_16816(float * c, unsigned a0, unsigned 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, typename OutT>
-__global__ void __launch_bounds__(kSkinnyWarps * 32) gemm_skinny_kernel(
+// NT: 8-column tiles of the batch; MT: 16-row tiles of weights per block (they share the activation
+// fragments); WARPS: how many warps split K; UNROLL: 32-wide k chunks whose weight loads are issued
+// before the first of them is used.
+template <int NT, int MT, int WARPS, int UNROLL, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     const __nv_bfloat16 * __restrict__ x, const __nv_bfloat16 * __restrict__ w, OutT * __restrict__ out,
     int B, int M, int K) {
-    __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
+    extern __shared__ float red_raw[];
+    float (*red)[MT * 16][NT * 8 + 1] = reinterpret_cast<float (*)[MT * 16][NT * 8 + 1]>(red_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int m0 = blockIdx.x * 16;
-    const int r0 = min(m0 + g, M - 1), r1 = min(m0 + g + 8, M - 1);
-    const uint4 * w0 = reinterpret_cast<const uint4 *>(w + (size_t) r0 * K) + t;
-    const uint4 * w1 = reinterpret_cast<const uint4 *>(w + (size_t) r1 * K) + t;
+    const int m0 = blockIdx.x * (16 * MT);
+    const uint4 * w0[MT];
+    const uint4 * w1[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        const int r0 = min(m0 + mt * 16 + g, M - 1), r1 = min(m0 + mt * 16 + g + 8, M - 1);
+        w0[mt] = reinterpret_cast<const uint4 *>(w + (size_t) r0 * K) + t;
+        w1[mt] = reinterpret_cast<const uint4 *>(w + (size_t) r1 * K) + t;
+    }
     const uint4 * xr[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const int n = min(nt * 8 + g, B - 1);
         xr[nt] = reinterpret_cast<const uint4 *>(x + (size_t) n * K) + t;
     }
-    float acc[NT][4];
+    float acc[MT][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[mt][nt][i] = 0.0f;
 
     const int nchunks = K / 32;                      // a chunk = 32 k = 4 x 16 bytes per row
     int c = warp;
-    for (; c + (kUnroll - 1) * kSkinnyWarps < nchunks; c += kUnroll * kSkinnyWarps) {
-        uint4 a0[kUnroll], a1[kUnroll];
+    for (; c + (UNROLL - 1) * WARPS < nchunks; c += UNROLL * WARPS) {
+        uint4 a0[UNROLL][MT], a1[UNROLL][MT];
 #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-            a0[u] = ld_stream(w0 + (size_t) (c + u * kSkinnyWarps) * 4);
-            a1[u] = ld_stream(w1 + (size_t) (c + u * kSkinnyWarps) * 4);
-        }
+        for (int u = 0; u < UNROLL; u++)
 #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
+            for (int mt = 0; mt < MT; mt++) {
+                a0[u][mt] = ld_stream(w0[mt] + (size_t) (c + u * WARPS) * 4);
+                a1[u][mt] = ld_stream(w1[mt] + (size_t) (c + u * WARPS) * 4);
+            }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint4 b = __ldg(xr[nt] + (size_t) (c + u * kSkinnyWarps) * 4);
-                mma_bf16_16816(acc[nt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b.x, b.y);
-                mma_bf16_16816(acc[nt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b.z, b.w);
+                const uint4 b = __ldg(xr[nt] + (size_t) (c + u * WARPS) * 4);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    mma_bf16_16816(acc[mt][nt], a0[u][mt].x, a1[u][mt].x, a0[u][mt].y, a1[u][mt].y, b.x, b.y);
+                    mma_bf16_16816(acc[mt][nt], a0[u][mt].z, a1[u][mt].z, a0[u][mt].w, a1[u][mt].w, b.z, b.w);
+                }
             }
         }
     }
-    for (; c < nchunks; c += kSkinnyWarps) {
-        const uint4 a0 = ld_stream(w0 + (size_t) c * 4);
-        const uint4 a1 = ld_stream(w1 + (size_t) c * 4);
+    for (; c < nchunks; c += WARPS) {
+        uint4 a0[MT], a1[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            a0[mt] = ld_stream(w0[mt] + (size_t) c * 4);
+            a1[mt] = ld_stream(w1[mt] + (size_t) c * 4);
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             const uint4 b = __ldg(xr[nt] + (size_t) c * 4);
-            mma_bf16_16816(acc[nt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
-            mma_bf16_16816(acc[nt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                mma_bf16_16816(acc[mt][nt], a0[mt].x, a1[mt].x, a0[mt].y, a1[mt].y, b.x, b.y);
+                mma_bf16_16816(acc[mt][nt], a0[mt].z, a1[mt].z, a0[mt].w, a1[mt].w, b.z, b.w);
+            }
         }
     }
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
-        red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
-        red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
-        red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
-    }
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            red[warp][mt * 16 + g][nt * 8 + 2 * t] = acc[mt][nt][0];
+            red[warp][mt * 16 + g][nt * 8 + 2 * t + 1] = acc[mt][nt][1];
+            red[warp][mt * 16 + g + 8][nt * 8 + 2 * t] = acc[mt][nt][2];
+            red[warp][mt * 16 + g + 8][nt * 8 + 2 * t + 1] = acc[mt][nt][3];
+        }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += blockDim.x) {
-        const int n = idx / 16, r = idx % 16;
+    constexpr int ROWS = MT * 16;
+    for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += blockDim.x) {
+        const int n = idx / ROWS, r = idx % ROWS;
         const int m = m0 + r;
         if (n >= B || m >= M) continue;
         float s = 0.0f;
 #pragma unroll
-        for (int wv = 0; wv < kSkinnyWarps; wv++) s += red[wv][r][n];
+        for (int wv = 0; wv < WARPS; wv++) s += red[wv][r][n];      // fixed order: independent of the batch
         out[(size_t) n * M + m] = from_f32<OutT>(s);
     }
 }
 
-template <typename OutT>
-static int launch_skinny(const void * x, const void * w, void * out, int B, int M, int K, cudaStream_t stream) {
-    const unsigned blocks = (unsigned) ((M + 15) / 16);
-    const int threads = kSkinnyWarps * 32;
-    const __nv_bfloat16 * xp = (const __nv_bfloat16 *) x;
-    const __nv_bfloat16 * wp = (const __nv_bfloat16 *) w;
-    OutT * op = (OutT *) out;
-    if (B <= 8) gemm_skinny_kernel<1, OutT><<<blocks, threads, 0, stream>>>(xp, wp, op, B, M, K);
-    else if (B <= 16) gemm_skinny_kernel<2, OutT><<<blocks, threads, 0, stream>>>(xp, wp, op, B, M, K);
-    else if (B <= 32) gemm_skinny_kernel<4, OutT><<<blocks, threads, 0, stream>>>(xp, wp, op, B, M, K);
-    else gemm_skinny_kernel<8, OutT><<<blocks, threads, 0, stream>>>(xp, wp, op, B, M, K);
+template <int NT, int MT, int WARPS, int UNROLL, typename OutT>
+static int launch_cfg(const void * x, const void * w, void * out, int B, int M, int K, cudaStream_t stream) {
+    const unsigned blocks = (unsigned) ((M + 16 * MT - 1) / (16 * MT));
+    constexpr size_t smem = sizeof(float) * WARPS * MT * 16 * (NT * 8 + 1);
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+            if (e != cudaSuccess) return 1000 + (int) e;
+            configured = true;
+        }
+    }
+    gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT><<<blocks, WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K);
     return iian_launch_status();
+}
+
+// cfg = MT * 100 + WARPS * 10 + UNROLL; 0 = the default for this (B, M)
+template <int NT, typename OutT>
+static int launch_nt(const void * x, const void * w, void * out, int B, int M, int K, int cfg, cudaStream_t stream) {
+    if (cfg == 0) {
+        if (NT == 1) cfg = M >= 16384 ? 184 : 144;
+        else if (NT == 2) cfg = 284;
+        else cfg = 282;
+    }
+    switch (cfg) {
+        case 184: return launch_cfg<NT, 1, 8, 4, OutT>(x, w, out, B, M, K, stream);
+        case 182: return launch_cfg<NT, 1, 8, 2, OutT>(x, w, out, B, M, K, stream);
+        case 144: return launch_cfg<NT, 1, 4, 4, OutT>(x, w, out, B, M, K, stream);
+        case 148: return launch_cfg<NT, 1, 4, 8, OutT>(x, w, out, B, M, K, stream);
+        case 284: return launch_cfg<NT, 2, 8, 4, OutT>(x, w, out, B, M, K, stream);
+        case 282: return launch_cfg<NT, 2, 8, 2, OutT>(x, w, out, B, M, K, stream);
+        case 244: return launch_cfg<NT, 2, 4, 4, OutT>(x, w, out, B, M, K, stream);
+        case 242: return launch_cfg<NT, 2, 4, 2, OutT>(x, w, out, B, M, K, stream);
+        case 442: if (NT <= 4) return launch_cfg<(NT <= 4 ? NT : 4), 4, 4, 2, OutT>(x, w, out, B, M, K, stream); break;
+        case 482: if (NT <= 4) return launch_cfg<(NT <= 4 ? NT : 4), 4, 8, 2, OutT>(x, w, out, B, M, K, stream); break;
+    }
+    return IIAN_ERR_SHAPE;
+}
+
+template <typename OutT>
+static int launch_skinny(const void * x, const void * w, void * out, int B, int M, int K, int cfg, cudaStream_t stream) {
+    if (B <= 8) return launch_nt<1, OutT>(x, w, out, B, M, K, cfg, stream);
+    if (B <= 16) return launch_nt<2, OutT>(x, w, out, B, M, K, cfg, stream);
+    if (B <= 32) return launch_nt<4, OutT>(x, w, out, B, M, K, cfg, stream);
+    return launch_nt<8, OutT>(x, w, out, B, M, K, cfg, stream);
 }
 
 }  // namespace iian
@@ -123,14 +181,20 @@ static int launch_skinny(const void * x, const void * w, void * out, int B, int 
 using namespace iian;
 
 // x: [B, K] bf16, w: [M, K] bf16, out: [B, M] bf16 or f32.  Needs 1 <= B <= 64, K a multiple of 32
-// and 16-byte aligned x and w (rows are then aligned too).
-IIAN_API int iian_gemm_skinny(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
-                              cudaStream_t stream) {
+// and 16-byte aligned x and w (rows are then aligned too).  cfg selects a tile configuration
+// (MT * 100 + WARPS * 10 + UNROLL); 0 takes the default.
+IIAN_API int iian_gemm_skinny_cfg(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
+                                  int cfg, cudaStream_t stream) {
     if (B <= 0 || M <= 0) return IIAN_OK;
     if (B > 64) return IIAN_ERR_LIMIT;
     if (K <= 0 || K % 32 != 0) return IIAN_ERR_SHAPE;
     if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
-    if (out_dtype == IIAN_BF16) return launch_skinny<__nv_bfloat16>(x, w, out, B, M, K, stream);
-    if (out_dtype == IIAN_F32) return launch_skinny<float>(x, w, out, B, M, K, stream);
+    if (out_dtype == IIAN_BF16) return launch_skinny<__nv_bfloat16>(x, w, out, B, M, K, cfg, stream);
+    if (out_dtype == IIAN_F32) return launch_skinny<float>(x, w, out, B, M, K, cfg, stream);
     return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_gemm_skinny(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
+                              cudaStream_t stream) {
+    return iian_gemm_skinny_cfg(x, w, out, out_dtype, B, M, K, 0, stream);
 }

@@ -18,6 +18,7 @@ namespace iian {
 constexpr int kMaxHeadDim = 512;
 constexpr int kWarpsPerBlock = 4;
 
+
 template <typename A>
 __global__ void qk_norm_rope_store_kernel(
     const A * __restrict__ qkv, const float * __restrict__ bias,
@@ -27,7 +28,6 @@ __global__ void qk_norm_rope_store_kernel(
     const int * __restrict__ slots,
     int N, int nh, int nkv, int hd, int rot_dim, int rope_style, float eps,
     int page_size, int num_pages, int write_kv) {
-    __shared__ float stage[kWarpsPerBlock][kMaxHeadDim];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nh + 2 * nkv;
     const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;
@@ -39,23 +39,8 @@ __global__ void qk_norm_rope_store_kernel(
     const int slot = slots != nullptr ? slots[t] : -1;
     if (!is_q && (slot < 0 || slot >= num_pages * page_size)) return;   // padding token: nothing to store
 
-    const size_t in_off = (size_t) t * heads_total * hd + (size_t) h * hd;
-    float * s = stage[warp];
-    float ss = 0.0f;
-    for (int i = lane; i < hd; i += 32) {
-        float v = to_f32(qkv[in_off + i]);
-        if (bias != nullptr) v += bias[(size_t) h * hd + i];
-        s[i] = v;
-        ss += v * v;
-    }
-    const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
-    if (w != nullptr) {
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float) hd + eps);
-        for (int i = lane; i < hd; i += 32) s[i] = s[i] * inv * w[i];
-    }
-    __syncwarp();
-
+    const A * src = qkv + (size_t) t * heads_total * hd + (size_t) h * hd;
+    const float * b = bias != nullptr ? bias + (size_t) h * hd : nullptr;
     A * dst;
     if (is_q) {
         dst = q_out + ((size_t) t * nh + h) * hd;
@@ -65,31 +50,72 @@ __global__ void qk_norm_rope_store_kernel(
         A * base = is_k ? k_cache : v_cache;
         dst = base + (((size_t) page * nkv + kvh) * page_size + off) * hd;
     }
+    const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
     const bool rotate = (is_q || is_k) && inv_freq != nullptr && rot_dim > 0;
-    const float pos = rotate ? (float) positions[t] : 0.0f;
-    const int half = rot_dim / 2;
-    for (int i = lane; i < hd; i += 32) {
-        float o;
-        if (rotate && i < rot_dim) {
-            int j, i0, i1;
-            bool first;
-            if (rope_style == 0) {          // NEOX: (j, j + half)
-                first = i < half;
-                j = first ? i : i - half;
-                i0 = j; i1 = j + half;
-            } else {                         // interleaved: (2j, 2j + 1)
-                j = i >> 1;
-                first = (i & 1) == 0;
-                i0 = 2 * j; i1 = 2 * j + 1;
-            }
-            float sn, cs;
-            sincosf(pos * inv_freq[j], &sn, &cs);
-            const float x0 = s[i0], x1 = s[i1];
-            o = first ? x0 * cs - x1 * sn : x0 * sn + x1 * cs;
-        } else {
-            o = s[i];
+
+    if (w == nullptr && !rotate) {          // V (or an unnormalised, unrotated head): a copy
+        for (int i = lane; i < hd; i += 32) {
+            float v = to_f32(src[i]);
+            if (b != nullptr) v += b[i];
+            dst[i] = from_f32<A>(v);
         }
-        dst[i] = from_f32<A>(o);
+        return;
+    }
+    // A lane owns rotation pairs p = lane, lane + 32, ...: elements (i0, i1) = (p, p + half) in NEOX
+    // style, (2p, 2p + 1) interleaved; beyond the rotated part it owns single elements.  Both members
+    // of a pair sit in the same lane, so the rotation needs no exchange.
+    constexpr int kMaxPairs = kMaxHeadDim / 64;      // per lane
+    const int half = rotate ? rot_dim / 2 : 0;
+    float x0[kMaxPairs], x1[kMaxPairs], tail[kMaxPairs * 2];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kMaxPairs; k++) {
+        const int p = lane + 32 * k;
+        if (p < half) {
+            const int i0 = rope_style == 0 ? p : 2 * p, i1 = rope_style == 0 ? p + half : 2 * p + 1;
+            float a0 = to_f32(src[i0]), a1 = to_f32(src[i1]);
+            if (b != nullptr) { a0 += b[i0]; a1 += b[i1]; }
+            x0[k] = a0; x1[k] = a1;
+            ss += a0 * a0 + a1 * a1;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxPairs * 2; k++) {
+        const int i = 2 * half + lane + 32 * k;
+        if (i < hd) {
+            float a = to_f32(src[i]);
+            if (b != nullptr) a += b[i];
+            tail[k] = a;
+            ss += a * a;
+        }
+    }
+    float inv = 1.0f;
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float) hd + eps);
+    }
+    const float pos = rotate ? (float) positions[t] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < kMaxPairs; k++) {
+        const int p = lane + 32 * k;
+        if (p < half) {
+            const int i0 = rope_style == 0 ? p : 2 * p, i1 = rope_style == 0 ? p + half : 2 * p + 1;
+            float a0 = x0[k], a1 = x1[k];
+            if (w != nullptr) { a0 = a0 * inv * w[i0]; a1 = a1 * inv * w[i1]; }
+            float sn, cs;
+            sincosf(pos * inv_freq[p], &sn, &cs);
+            dst[i0] = from_f32<A>(a0 * cs - a1 * sn);
+            dst[i1] = from_f32<A>(a0 * sn + a1 * cs);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxPairs * 2; k++) {
+        const int i = 2 * half + lane + 32 * k;
+        if (i < hd) {
+            float a = tail[k];
+            if (w != nullptr) a = a * inv * w[i];
+            dst[i] = from_f32<A>(a);
+        }
     }
 }
 

@@ -79,6 +79,64 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float * __
     if (threadIdx.x == 0) out[blockIdx.x] = bi;
 }
 
+// Two-stage argmax for wide rows: `parts` blocks per row each reduce a contiguous slice to (value, id),
+// a second launch reduces the parts.  Ties still go to the lowest id.
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float * __restrict__ logits, int V, size_t stride,
+                                                             int parts, float * __restrict__ part_val,
+                                                             int * __restrict__ part_idx) {
+    __shared__ float fs[32];
+    __shared__ int is[32];
+    const int row = blockIdx.y, part = blockIdx.x;
+    const int per = (V + parts - 1) / parts;
+    const int begin = min(V, part * per), end = min(V, begin + per);
+    const float * r = logits + (size_t) row * stride;
+    float b = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = r[i];
+        if (v > b || (v == b && i < bi)) { b = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, b, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > b || (ob == b && oi < bi)) { b = ob; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { fs[warp] = b; is[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        b = lane < (blockDim.x >> 5) ? fs[lane] : -INFINITY;
+        bi = lane < (blockDim.x >> 5) ? is[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, b, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > b || (ob == b && oi < bi)) { b = ob; bi = oi; }
+        }
+        if (lane == 0) { part_val[(size_t) row * parts + part] = b; part_idx[(size_t) row * parts + part] = bi; }
+    }
+}
+
+__global__ void argmax_final_kernel(const float * __restrict__ part_val, const int * __restrict__ part_idx, int parts,
+                                    int * __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;       // one warp per row
+    float b = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lane; i < parts; i += 32) {
+        const float v = part_val[(size_t) row * parts + i];
+        const int idx = part_idx[(size_t) row * parts + i];
+        if (v > b || (v == b && idx < bi)) { b = v; bi = idx; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, b, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > b || (ob == b && oi < bi)) { b = ob; bi = oi; }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float * __restrict__ logits, int V, size_t stride,
     const float * __restrict__ temperature, const int * __restrict__ top_k, const float * __restrict__ top_p,
@@ -279,6 +337,21 @@ IIAN_API int iian_argmax(const float * logits, int R, int V, long long stride, i
     if (R <= 0) return IIAN_OK;
     if (V <= 0) return IIAN_ERR_SHAPE;
     argmax_kernel<<<R, kSampleThreads, 0, stream>>>(logits, V, (size_t) stride, out);
+    return iian_launch_status();
+}
+
+// Wide rows: scratch must hold R * parts floats followed by R * parts ints (parts = iian_argmax_parts(V)).
+IIAN_API int iian_argmax_parts(int V) { return V >= 16384 ? 64 : 0; }
+
+IIAN_API int iian_argmax_wide(const float * logits, int R, int V, long long stride, void * scratch, int * out,
+                              cudaStream_t stream) {
+    if (R <= 0) return IIAN_OK;
+    const int parts = iian_argmax_parts(V);
+    if (V <= 0 || parts == 0 || scratch == nullptr || R > 65535) return IIAN_ERR_SHAPE;
+    float * pv = (float *) scratch;
+    int * pi = (int *) (pv + (size_t) R * parts);
+    argmax_partial_kernel<<<dim3(parts, R), 256, 0, stream>>>(logits, V, (size_t) stride, parts, pv, pi);
+    argmax_final_kernel<<<R, 32, 0, stream>>>(pv, pi, parts, out);
     return iian_launch_status();
 }
 

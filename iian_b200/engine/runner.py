@@ -92,8 +92,10 @@ class StepContext:
         self.h_ctx_len: List[int] = []
         self.h_state_slots: List[int] = []
         self.decode_only = False
+        self.rows_identity = False     # the wanted rows are all rows in order: no gather is needed
         self.max_q_len = 0
         self.max_ctx = 0
+        self.upload_bytes = 0
 
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
@@ -261,6 +263,7 @@ class ModelRunner:
         if slot is not None:
             ctx.max_q_len, ctx.max_ctx = 1, slot.ctx_bucket
         ctx.decode_only = ctx.max_q_len == 1
+        ctx.rows_identity = slot is not None or rows == list(range(N))
         ctx.upload_bytes = total * 4
         for g in range(n_groups):
             ctx.metas.append(AttentionMeta(

@@ -183,14 +183,16 @@ class CudaKernels:
                 type(self)._library_f32_out = False
         return False
 
-    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0) -> None:
+        """``cfg`` picks a tile configuration (rows-per-block tiles * 100 + warps * 10 + unroll); 0: default."""
         n, k = x.shape
         m = w.shape[0]
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: x and w must be bfloat16")
-        fn = _fn("gemm_skinny", "iian_gemm_skinny", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        fn = _fn("gemm_skinny", "iian_gemm_skinny_cfg",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
         _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
-                  n, m, k, _stream()), "gemm_skinny")
+                  n, m, k, cfg, _stream()), "gemm_skinny")
 
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         n, k = x.shape
@@ -249,22 +251,28 @@ class CudaKernels:
             self.paged_attention_generic(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                                          scale=scale, window=window)
 
-    TARGET_CTAS = 148 * 3          # SMs x resident CTAs of the decode configuration
+    DECODE_SLOTS = 148 * 2         # SMs x resident CTAs of the decode kernel
     MAX_SPLITS = 32
     _scratch = {}
+    _scratch_keep = []
 
     def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
         """How many parts the keys of a decode step are cut into, so that few long sequences still fill
         the GPU."""
         tiles = max(1, (max_ctx + 63) // 64)
-        want = -(-self.TARGET_CTAS // max(1, num_seqs * num_kv_heads))
-        return max(1, min(want, tiles, self.MAX_SPLITS))
+        base = max(1, num_seqs * num_kv_heads)
+        want = -(-2 * self.DECODE_SLOTS // base)                 # about two waves of CTAs
+        n = min(want, max(1, tiles // 2), self.MAX_SPLITS)       # at least two key tiles per CTA ...
+        if base * n < self.DECODE_SLOTS // 2:
+            n = min(want, tiles, self.MAX_SPLITS)                # ... unless the GPU would stay mostly empty
+        return max(1, n)
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
         t = self._scratch.get(device)
         if t is None or t.numel() < n_floats:
             t = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
             self._scratch[device] = t
+            self._scratch_keep.append(t)        # a captured graph may still point at an older, smaller buffer
         return t
 
     def paged_attention_mma(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
@@ -322,6 +330,13 @@ class CudaKernels:
             raise KernelError("argmax: logits rows must be contiguous")
         if not logits.is_cuda or logits.dtype != torch.float32:
             raise KernelError("argmax: logits must be float32 on CUDA")
+        if v >= 16384 and r <= 65535:      # wide rows: many blocks per row, then a merge
+            scratch = self.attention_scratch(logits.device, r * 64 * 2)
+            fn = _fn("sampling", "iian_argmax_wide", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p])
+            _check(fn(logits.data_ptr(), r, v, logits.stride(0), scratch.data_ptr(), _cuda(out, "argmax out", torch.int32),
+                      _stream()), "argmax")
+            LAUNCHES[0] += 1
+            return
         fn = _fn("sampling", "iian_argmax", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p])
         _check(fn(logits.data_ptr(), r, v, logits.stride(0), _cuda(out, "argmax out", torch.int32), _stream()), "argmax")
 

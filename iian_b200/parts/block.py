@@ -39,7 +39,7 @@ class PreNormResidualBlock:
                 select_rows: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
         h = self.mixer_norm.forward(residual, delta, ctx)
         y = self.mixer.forward(h, ctx, cache, writes_cache)
-        if select_rows is not None:
+        if select_rows is not None and not getattr(ctx, "rows_identity", False):
             k = ops.kernels()
             r = select_rows.shape[0]
             res_sel = ctx.buf("residual_rows", (r, residual.shape[1]), residual.dtype)
