@@ -28,6 +28,7 @@ struct AttnParams {
     __nv_bfloat16 * out;            // [N, nh * HD]
     float * part_o;                 // [N * nh, n_split, HD]   (n_split > 1)
     float * part_lse;               // [N * nh, n_split]
+    int * counters;                 // [S * nkv * row tiles], zero between launches (decode form, n_split > 1)
     const int * cu_q;               // [S + 1]
     const int * ctx_len;            // [S]
     const int * block_table;        // [S, max_blocks]
@@ -118,18 +119,22 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
     auto load_kv = [&](int tile, int stage) {
         unsigned char * dK = sK + stage * BN * HD * 2;
         unsigned char * dV = sV + stage * BN * HD * 2;
-        for (int c = tid; c < BN * CH; c += NW * 32) {
-            const int r = c / CH, ch = c % CH;
-            const int j = tile * BN + r;
-            bool valid = j <= k_hi && j >= 0;
-            size_t cell = 0;
-            if (valid) {
-                const int page = bt[j / p.page_size];
-                if (page < 0 || page >= p.num_pages) valid = false;
-                else cell = (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD + ch * 8;
-            }
-            cp_async16(smem_u32(dK + swz<HD>(r, ch)), p.k_cache + cell, valid);
-            cp_async16(smem_u32(dV + swz<HD>(r, ch)), p.v_cache + cell, valid);
+        // NW * 32 threads share BN rows: each thread takes a fixed slice of one row -> one page lookup
+        constexpr int TPR = NW * 32 / BN;                  // threads per row
+        constexpr int CPT = CH / TPR;                      // chunks per thread
+        const int r = tid / TPR, c0 = (tid % TPR) * CPT;
+        const int j = tile * BN + r;
+        bool valid = j <= k_hi;
+        size_t cell = 0;
+        if (valid) {
+            const int page = bt[j / p.page_size];
+            if (page < 0 || page >= p.num_pages) valid = false;
+            else cell = (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+        }
+#pragma unroll
+        for (int c = 0; c < CPT; c++) {
+            cp_async16(smem_u32(dK + swz<HD>(r, c0 + c)), p.k_cache + cell + (c0 + c) * 8, valid);
+            cp_async16(smem_u32(dV + swz<HD>(r, c0 + c)), p.v_cache + cell + (c0 + c) * 8, valid);
         }
     };
 
@@ -146,6 +151,10 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
         row_ok[h] = R < rows_total;
         row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);       // position of the row's token
     }
+    // bounds over the 16 rows of this warp: tiles wholly below every row's diagonal need no mask
+    const int wr0 = row0 + warp * 16, wr1 = min(rows_total - 1, wr0 + 15);
+    const bool warp_rows_ok = wr0 + 15 < rows_total;
+    const int warp_pos_min = pos0 + min(wr0, rows_total - 1) / G, warp_pos_max = pos0 + max(wr1, 0) / G;
 
     if (tile_begin < tile_end) {
         load_q();
@@ -193,36 +202,45 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
                     mma16816(sc[2 * np + 1], qf[ks], b2, b3);
                 }
             }
-            // ---- mask, online softmax ---------------------------------------------------------
+            // ---- mask (only on tiles that touch a row's causal or window edge), online softmax ----
             const int key0 = tile * BN;
-            float m_new[2] = {m_run[0], m_run[1]};
+            const bool need_mask = key0 + BN - 1 > warp_pos_min || !warp_rows_ok ||
+                                   (p.window > 0 && warp_pos_max - key0 >= p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int nt = 0; nt < BN / 8; nt++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int h = e >> 1;
+                        const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
+                        if (!vis) sc[nt][e] = -INFINITY;
+                    }
+                }
+            }
+            float m_new[2] = {m_run[0], m_run[1]};          // maxima of the raw scores (the scale is positive)
 #pragma unroll
             for (int nt = 0; nt < BN / 8; nt++) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int h = e >> 1;
-                    const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                    const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
-                    const float v = vis ? sc[nt][e] * p.scale_log2 : -INFINITY;
-                    sc[nt][e] = v;
-                    m_new[h] = fmaxf(m_new[h], v);
-                }
+                m_new[0] = fmaxf(m_new[0], fmaxf(sc[nt][0], sc[nt][1]));
+                m_new[1] = fmaxf(m_new[1], fmaxf(sc[nt][2], sc[nt][3]));
             }
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
                 m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
             }
-            float corr[2], sum[2] = {0.0f, 0.0f};
+            float corr[2], neg[2], sum[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int h = 0; h < 2; h++)
-                corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f(m_run[h] - m_new[h]);   // m_run = -inf gives 0
+            for (int h = 0; h < 2; h++) {
+                corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f((m_run[h] - m_new[h]) * p.scale_log2);   // m_run = -inf gives 0
+                neg[h] = (m_new[h] == -INFINITY) ? 0.0f : m_new[h] * p.scale_log2;
+            }
 #pragma unroll
             for (int nt = 0; nt < BN / 8; nt++) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int h = e >> 1;
-                    const float pv = (m_new[h] == -INFINITY) ? 0.0f : exp2f(sc[nt][e] - m_new[h]);
+                    const float pv = exp2f(fmaf(sc[nt][e], p.scale_log2, -neg[h]));       // exp2(-inf) = 0 for masked keys
                     sc[nt][e] = pv;
                     sum[h] += pv;
                 }
@@ -287,7 +305,7 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
                 *reinterpret_cast<float2 *>(dst + d) = make_float2(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
             }
             if (t_ == 0)    // log-sum-exp in base 2; -inf marks a part that saw no key
-                p.part_lse[row_idx * p.n_split + split] = l_run[h] > 0.0f ? m_run[h] + log2f(l_run[h]) : -INFINITY;
+                p.part_lse[row_idx * p.n_split + split] = l_run[h] > 0.0f ? m_run[h] * p.scale_log2 + log2f(l_run[h]) : -INFINITY;
         }
     }
 }
@@ -296,7 +314,10 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
 // of a CTA share the rows and split the KEYS of every 64-key tile (16 each); each warp keeps a running
 // (max, sum, output) of its own, and the four are merged through shared memory at the end.  Three
 // cp.async stages keep two tiles in flight while one is consumed.  Every thread fetches one half row of
-// K and of V per tile, so a tile costs it one block-table lookup.
+// K and of V per tile, so a tile costs it one block-table lookup, and that lookup is issued a tile ahead
+// of its use.  With n_split > 1 the CTA that finishes last for its rows (a counter per row tile, bumped
+// after the partial results are fenced out) merges the parts and writes the output, so there is no
+// second launch; it leaves the counter at zero for the next launch.
 template <int HD>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams p) {
     constexpr int NW = 4, BM = 16, STAGES = 3;
@@ -306,6 +327,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     unsigned char * sQ = smem;                               // [16][HD]
     unsigned char * sK = sQ + BM * HD * 2;                   // [STAGES][BN][HD]
     unsigned char * sV = sK + STAGES * TILE_BYTES;           // [STAGES][BN][HD]
+    __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g_ = lane >> 2, t_ = lane & 3;
@@ -332,22 +354,23 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     const int n_my = max(0, tile_end - tile_begin);
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
 
-    auto load_kv = [&](int tile, int stage) {
-        const int r = tid >> 1, c0 = (tid & 1) * (CH / 2);       // one half row per thread
-        const int j = tile * BN + r;
-        bool valid = j <= k_hi;
-        size_t cell = 0;
-        if (valid) {
-            const int page = bt[j / p.page_size];
-            if (page < 0 || page >= p.num_pages) valid = false;
-            else cell = (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
-        }
+    const int ld_r = tid >> 1, ld_c0 = (tid & 1) * (CH / 2);     // this thread's half row of every tile
+    auto lookup = [&](int tile) -> int {                         // page of this thread's row, -1: nothing to load
+        const int j = tile * BN + ld_r;
+        if (tile >= tile_end || j > k_hi) return -1;
+        const int page = bt[j / p.page_size];
+        return (page < 0 || page >= p.num_pages) ? -1 : page;
+    };
+    auto load_kv = [&](int tile, int stage, int page) {
+        const int j = tile * BN + ld_r;
+        const bool valid = page >= 0;
+        const size_t cell = valid ? (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD : 0;
         unsigned char * dK = sK + stage * TILE_BYTES;
         unsigned char * dV = sV + stage * TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < CH / 2; c++) {
-            cp_async16(smem_u32(dK + swz<HD>(r, c0 + c)), p.k_cache + cell + (c0 + c) * 8, valid);
-            cp_async16(smem_u32(dV + swz<HD>(r, c0 + c)), p.v_cache + cell + (c0 + c) * 8, valid);
+            cp_async16(smem_u32(dK + swz<HD>(ld_r, ld_c0 + c)), p.k_cache + cell + (ld_c0 + c) * 8, valid);
+            cp_async16(smem_u32(dV + swz<HD>(ld_r, ld_c0 + c)), p.v_cache + cell + (ld_c0 + c) * 8, valid);
         }
     };
 
@@ -362,8 +385,12 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
         row_ok[h] = R < rows_total;
         row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);
     }
+    const int pos_min = pos0 + tok_min, pos_max = pos0 + tok_max;
+    const bool rows_full = row0 + BM <= rows_total;
 
     if (n_my > 0) {
+        const int pg0 = lookup(tile_begin), pg1 = lookup(tile_begin + 1);
+        int pg_next = lookup(tile_begin + 2);
         for (int c = tid; c < BM * CH; c += NW * 32) {          // Q rows
             const int r = c / CH, ch = c % CH;
             const int R = row0 + r;
@@ -371,15 +398,16 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
             const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
             cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
         }
-        load_kv(tile_begin, 0);
+        load_kv(tile_begin, 0, pg0);
         cp_async_commit();
-        if (n_my > 1) load_kv(tile_begin + 1, 1);
+        if (n_my > 1) load_kv(tile_begin + 1, 1, pg1);
         cp_async_commit();
 
         unsigned qf[KS][4];
         for (int i = 0; i < n_my; i++) {
-            if (i + 2 < n_my) load_kv(tile_begin + i + 2, (i + 2) % STAGES);
+            if (i + 2 < n_my) load_kv(tile_begin + i + 2, (i + 2) % STAGES, pg_next);
             cp_async_commit();
+            pg_next = lookup(tile_begin + i + 3);                // used one iteration from now
             cp_async_wait<2>();
             __syncthreads();
             if (i == 0) {
@@ -402,33 +430,39 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
                 mma16816(sc[1], qf[ks], b2, b3);
             }
             const int key0 = (tile_begin + i) * BN + warp * 16;
-            float m_new[2] = {m_run[0], m_run[1]};
+            const bool need_mask = key0 + 15 > pos_min || !rows_full || (p.window > 0 && pos_max - key0 >= p.window);
+            if (need_mask) {
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
+                for (int nt = 0; nt < 2; nt++) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int h = e >> 1;
-                    const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                    const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
-                    const float v = vis ? sc[nt][e] * p.scale_log2 : -INFINITY;
-                    sc[nt][e] = v;
-                    m_new[h] = fmaxf(m_new[h], v);
+                    for (int e = 0; e < 4; e++) {
+                        const int h = e >> 1;
+                        const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
+                        if (!vis) sc[nt][e] = -INFINITY;
+                    }
                 }
             }
+            float m_new[2];
+            m_new[0] = fmaxf(m_run[0], fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])));
+            m_new[1] = fmaxf(m_run[1], fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])));
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
                 m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
             }
-            float corr[2], sum[2] = {0.0f, 0.0f};
+            float corr[2], neg[2], sum[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int h = 0; h < 2; h++) corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f(m_run[h] - m_new[h]);
+            for (int h = 0; h < 2; h++) {
+                corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f((m_run[h] - m_new[h]) * p.scale_log2);
+                neg[h] = (m_new[h] == -INFINITY) ? 0.0f : m_new[h] * p.scale_log2;
+            }
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int h = e >> 1;
-                    const float pv = (m_new[h] == -INFINITY) ? 0.0f : exp2f(sc[nt][e] - m_new[h]);
+                    const float pv = exp2f(fmaf(sc[nt][e], p.scale_log2, -neg[h]));
                     sc[nt][e] = pv;
                     sum[h] += pv;
                 }
@@ -483,41 +517,77 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
         ml[(warp * BM + g_ + 8) * 2] = m_run[1];     ml[(warp * BM + g_ + 8) * 2 + 1] = l_run[1];
     }
     __syncthreads();
-    {
-        const int r = tid >> 3, part = tid & 7;              // 8 threads per row, HD / 8 columns each
-        const int R = row0 + r;
-        if (R < rows_total) {
-            float mw[NW], m = -INFINITY;
+    const int mr = tid >> 3, mpart = tid & 7;                // 8 threads per row, HD / 8 columns each
+    const int mR = row0 + mr;
+    const bool m_ok = mR < rows_total;
+    const size_t row_idx = m_ok ? (size_t) (q0 + mR / G) * p.nh + kvh * G + mR % G : 0;
+    if (m_ok) {
+        float mw[NW], m = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < NW; w++) { mw[w] = ml[(w * BM + r) * 2]; m = fmaxf(m, mw[w]); }
-            float sw[NW], l = 0.0f;
+        for (int w = 0; w < NW; w++) { mw[w] = ml[(w * BM + mr) * 2]; m = fmaxf(m, mw[w]); }
+        float sw[NW], l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) {
+            sw[w] = (mw[w] == -INFINITY) ? 0.0f : exp2f((mw[w] - m) * p.scale_log2);
+            l += sw[w] * ml[(w * BM + mr) * 2 + 1];
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+        for (int c = 0; c < HD / 8; c += 2) {
+            const int d = mpart * (HD / 8) + c;
+            float v0 = 0.0f, v1 = 0.0f;
 #pragma unroll
             for (int w = 0; w < NW; w++) {
-                sw[w] = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - m);
-                l += sw[w] * ml[(w * BM + r) * 2 + 1];
+                const float2 x = *reinterpret_cast<const float2 *>(mo + ((size_t) w * BM + mr) * HD + d);
+                v0 += sw[w] * x.x;
+                v1 += sw[w] * x.y;
             }
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const int tok = R / G, head = kvh * G + R % G;
-            const size_t row_idx = (size_t) (q0 + tok) * p.nh + head;
-#pragma unroll
-            for (int c = 0; c < HD / 8; c += 2) {
-                const int d = part * (HD / 8) + c;
-                float v0 = 0.0f, v1 = 0.0f;
-#pragma unroll
-                for (int w = 0; w < NW; w++) {
-                    const float2 x = *reinterpret_cast<const float2 *>(mo + ((size_t) w * BM + r) * HD + d);
-                    v0 += sw[w] * x.x;
-                    v1 += sw[w] * x.y;
-                }
-                if (p.n_split == 1)
-                    *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
-                else
-                    *reinterpret_cast<float2 *>(p.part_o + (row_idx * p.n_split + split) * HD + d) = make_float2(v0 * inv, v1 * inv);
-            }
-            if (p.n_split > 1 && part == 0)
-                p.part_lse[row_idx * p.n_split + split] = l > 0.0f ? m + log2f(l) : -INFINITY;
+            if (p.n_split == 1)
+                *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
+            else
+                *reinterpret_cast<float2 *>(p.part_o + (row_idx * p.n_split + split) * HD + d) = make_float2(v0 * inv, v1 * inv);
         }
+        if (p.n_split > 1 && mpart == 0)        // log-sum-exp in base 2; -inf marks a part that saw no key
+            p.part_lse[row_idx * p.n_split + split] = l > 0.0f ? m * p.scale_log2 + log2f(l) : -INFINITY;
     }
+    if (p.n_split == 1) return;
+
+    // ---- the last CTA of these rows merges the parts -------------------------------------------
+    __threadfence();
+    __syncthreads();
+    int * counter = p.counters + ((size_t) s * p.nkv + kvh) * gridDim.x + blockIdx.x;
+    if (tid == 0) s_last = (atomicAdd(counter, 1) == p.n_split - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (m_ok) {
+        const float * lse = p.part_lse + row_idx * p.n_split;
+        float mx = -INFINITY;
+        for (int i = 0; i < p.n_split; i++) mx = fmaxf(mx, __ldcg(lse + i));
+        float acc[HD / 8];
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) acc[c] = 0.0f;
+        float wsum = 0.0f;
+        if (mx != -INFINITY) {
+            for (int i = 0; i < p.n_split; i++) {
+                const float w = exp2f(__ldcg(lse + i) - mx);
+                if (w == 0.0f) continue;
+                wsum += w;
+                const float * po = p.part_o + (row_idx * p.n_split + i) * HD + mpart * (HD / 8);
+#pragma unroll
+                for (int c = 0; c < HD / 8; c += 4) {
+                    const float4 x = __ldcg(reinterpret_cast<const float4 *>(po + c));
+                    acc[c] += w * x.x; acc[c + 1] += w * x.y; acc[c + 2] += w * x.z; acc[c + 3] += w * x.w;
+                }
+            }
+        }
+        const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+        __nv_bfloat16 * dst = p.out + row_idx * HD + mpart * (HD / 8);
+#pragma unroll
+        for (int c = 0; c < HD / 8; c += 2)
+            *reinterpret_cast<__nv_bfloat162 *>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+    }
+    if (tid == 0) *counter = 0;
 }
 
 template <int HD>
@@ -582,20 +652,23 @@ static int launch_attention(const AttnParams & p, int S, int max_rows, cudaStrea
 
 using namespace iian;
 
-// Scratch needed for n_split > 1: part_o = N * nh * n_split * hd floats, part_lse = N * nh * n_split floats.
+// Scratch needed for n_split > 1: part_o = N * nh * n_split * hd floats, part_lse = N * nh * n_split floats,
+// and for the decode form (small_tiles) counters = S * nkv * ceil(max_q_len * nh / nkv / 16) ints that are
+// zero before the first launch (the kernel leaves them zero).
 IIAN_API int iian_attention_mma(
     const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
-    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
     float scale, int window, int n_split, int small_tiles, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
     if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
     if (n_split > 1 && (part_o == nullptr || part_lse == nullptr)) return IIAN_ERR_SHAPE;
+    if (n_split > 1 && small_tiles && counters == nullptr) return IIAN_ERR_SHAPE;
     if ((long long) S * n_split > 65535 || nkv > 65535) return IIAN_ERR_LIMIT;
     AttnParams p;
     p.q = (const __nv_bfloat16 *) q; p.k_cache = (const __nv_bfloat16 *) k_cache; p.v_cache = (const __nv_bfloat16 *) v_cache;
-    p.out = (__nv_bfloat16 *) out; p.part_o = part_o; p.part_lse = part_lse;
+    p.out = (__nv_bfloat16 *) out; p.part_o = part_o; p.part_lse = part_lse; p.counters = counters;
     p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_blocks = max_blocks;
     p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.n_split = n_split;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -603,7 +676,7 @@ IIAN_API int iian_attention_mma(
     int rc;
     if (hd == 128) rc = small_tiles ? launch_decode<128>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
     else rc = small_tiles ? launch_decode<64>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
-    if (rc != IIAN_OK || n_split == 1) return rc;
+    if (rc != IIAN_OK || n_split == 1 || small_tiles) return rc;      // the decode form merges its parts itself
     const int rows = N * nh;
     const int warps = 4;
     if (hd == 128) attention_combine_kernel<128><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(part_o, part_lse, (__nv_bfloat16 *) out, rows, n_split);
@@ -620,20 +693,25 @@ IIAN_API int iian_attention_mma(
 // owns), or a latency-critical loop that cannot afford cudaMalloc's device-wide synchronisation.  For
 // them the scratch lives in a fixed array inside this library.
 //
-//  * The array has kNoAllocScratchFloats floats (8 MiB).  Every GPU on which this library is loaded
-//    holds that much until the process exits.
-//  * A call needs N * nh * n_split * (hd + 1) floats; a larger request is refused with
-//    IIAN_ERR_LIMIT and nothing is launched.  iian_attention_mma_noalloc_capacity() returns the limit.
+//  * The array has kNoAllocScratchFloats floats (8 MiB) for partial results, after a fixed region of
+//    kNoAllocCounters ints for the per-row-tile arrival counters.  Every GPU on which this library is
+//    loaded holds both until the process exits.
+//  * A call needs N * nh * n_split * (hd + 1) floats and S * nkv * ceil(max_q_len * nh / nkv / 16)
+//    counters; a larger request is refused with IIAN_ERR_LIMIT and nothing is launched.
+//    iian_attention_mma_noalloc_capacity() returns the limit in floats.
 //  * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
 //    device current) and remembers it per device.  Make that first call before any stream capture.
 //  * No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
-//  * All calls share the one array, and it keeps what the last call left in it.  Nothing in it has to
-//    start at zero: each (row, split) cell is fully written by the CTA that owns it before the merge
-//    kernel of the same call reads it.  Two calls whose kernels overlap on the GPU (different streams
-//    without an ordering between them) race on the array; order them.
+//  * All calls share the one array, and it keeps what the last call left in it.  The partial results
+//    need no clearing: each (row, split) cell is fully written by the CTA that owns it before the merging
+//    CTA of the same call reads it.  The counters must be zero when a launch starts; they live in a
+//    region of their own that nothing else is ever written to, start at zero (static storage) and are
+//    put back to zero by the kernel itself.  Two calls whose kernels overlap on the GPU (different
+//    streams without an ordering between them) race on the array; order them.
 // ---------------------------------------------------------------------------------------------------
 constexpr size_t kNoAllocScratchFloats = (size_t) 2 * 1024 * 1024;
-static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+constexpr size_t kNoAllocCounters = (size_t) 64 * 1024;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocCounters + kNoAllocScratchFloats];
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -652,6 +730,9 @@ IIAN_API int iian_attention_mma_noalloc(
     if (n_split < 1 || nh <= 0 || hd <= 0) return IIAN_ERR_SHAPE;
     const unsigned long long need = (unsigned long long) N * nh * n_split * (unsigned long long) (hd + 1);
     if (n_split > 1 && need > kNoAllocScratchFloats) return IIAN_ERR_LIMIT;
+    if (nkv <= 0 || nh % nkv != 0) return IIAN_ERR_SHAPE;
+    const unsigned long long n_counters = (unsigned long long) S * nkv * (((unsigned long long) max_q_len * (nh / nkv) + 15) / 16);
+    if (n_split > 1 && n_counters > kNoAllocCounters) return IIAN_ERR_LIMIT;
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return 1000 + (int) e;
@@ -662,9 +743,10 @@ IIAN_API int iian_attention_mma_noalloc(
         if (e != cudaSuccess || ptr == nullptr) return 1000 + (int) e;
         g_noalloc_ptr[dev] = ptr;
     }
-    float * part_o = g_noalloc_ptr[dev];
+    int * counters = reinterpret_cast<int *>(g_noalloc_ptr[dev]);       // an int region of its own, zero at rest
+    float * part_o = g_noalloc_ptr[dev] + kNoAllocCounters;
     float * part_lse = part_o + (size_t) N * nh * n_split * hd;
-    return iian_attention_mma(q, k_cache, v_cache, out, part_o, part_lse, cu_q, ctx_len, block_table, max_blocks,
+    return iian_attention_mma(q, k_cache, v_cache, out, part_o, part_lse, counters, cu_q, ctx_len, block_table, max_blocks,
                               N, S, max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, n_split, small_tiles,
                               stream);
 }

@@ -149,7 +149,7 @@ static int launch_cfg(const void * x, const void * w, void * out, int B, int M, 
 template <int NT, typename OutT>
 static int launch_nt(const void * x, const void * w, void * out, int B, int M, int K, int cfg, cudaStream_t stream) {
     if (cfg == 0) {
-        if (NT == 1) cfg = M >= 16384 ? 184 : 144;
+        if (NT == 1) cfg = M >= 65536 ? 144 : 184;
         else if (NT == 2) cfg = 284;
         else cfg = 282;
     }

@@ -157,14 +157,15 @@ class CudaKernels:
         self._linear_dispatch(x, w, out, n, m, k)
 
     # rows up to which the weight-streaming kernel is used; above it the library GEMM takes over
-    SKINNY_MAX_ROWS = 64
+    # (measured on B200 at the Qwen3-8B sizes: the streaming kernel wins up to 8 rows, cuBLAS from 16)
+    SKINNY_MAX_ROWS = 8
 
     def _linear_dispatch(self, x, w, out, n, m, k) -> None:
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
             if n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
                 self.gemm_skinny(x, w, out)
                 return
-            if n > 16 and self._library_gemm(x, w, out):
+            if n > self.SKINNY_MAX_ROWS and self._library_gemm(x, w, out):
                 return
         self.gemm_simt(x, w, out)
 
@@ -275,6 +276,17 @@ class CudaKernels:
             self._scratch_keep.append(t)        # a captured graph may still point at an older, smaller buffer
         return t
 
+    _counters = {}
+
+    def attention_counters(self, device, n: int) -> torch.Tensor:
+        """Zeroed int32 counters for the decode kernel's in-kernel merge (it puts them back to zero)."""
+        t = self._counters.get(device)
+        if t is None or t.numel() < n:
+            t = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+            self._counters[device] = t
+            self._scratch_keep.append(t)
+        return t
+
     def paged_attention_mma(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
                             n_split: Optional[int] = None, small_tiles: Optional[bool] = None) -> None:
         n = q.shape[0]
@@ -287,22 +299,25 @@ class CudaKernels:
             small_tiles = decode
         if n_split is None:
             n_split = getattr(meta, "n_split", None) or (self.attention_splits(meta.num_seqs, num_kv_heads, meta.max_ctx) if decode else 1)
-        part_o = part_lse = 0
+        part_o = part_lse = counters = 0
         if n_split > 1:
             rows = n * num_heads
             scratch = self.attention_scratch(q.device, rows * n_split * (head_dim + 1))
             part_o = scratch.data_ptr()
             part_lse = part_o + rows * n_split * head_dim * 4
+            if small_tiles:
+                row_tiles = -(-meta.max_q_len * (num_heads // num_kv_heads) // 16)
+                counters = self.attention_counters(q.device, meta.num_seqs * num_kv_heads * row_tiles).data_ptr()
         bt = meta.block_table
         fn = _fn("attention_mma", "iian_attention_mma",
-                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
         _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
-                  part_o, part_lse, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
                   num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split,
                   1 if small_tiles else 0, _stream()), "attention_mma")
-        if n_split > 1:
+        if n_split > 1 and not small_tiles:
             LAUNCHES[0] += 1
 
     def paged_attention_generic(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale,

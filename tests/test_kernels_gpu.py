@@ -305,12 +305,14 @@ def test_gemm_skinny(od, B, M, K_):
 
 
 def test_gemm_skinny_rows_do_not_depend_on_the_batch():
-    x = rnd(40, 512, dtype=torch.bfloat16, seed=22)
+    """Within the row counts the engine uses it for (up to 8), a row's result is the same bits whatever
+    else is in the batch: the split of K over warps and the order of the final sum are fixed."""
+    x = rnd(8, 512, dtype=torch.bfloat16, seed=22)
     w = rnd(90, 512, dtype=torch.bfloat16, seed=23)
-    full = torch.empty(40, 90, dtype=torch.float32).cuda()
+    full = torch.empty(8, 90, dtype=torch.float32).cuda()
     K().gemm_skinny(x, w, full)
     one = torch.empty(1, 90, dtype=torch.float32).cuda()
-    for r in (0, 17, 39):
+    for r in (0, 3, 7):
         K().gemm_skinny(x[r:r + 1].contiguous(), w, one)
         assert torch.equal(one[0], full[r])
 
