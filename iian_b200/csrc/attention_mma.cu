@@ -58,6 +58,12 @@ __device__ __forceinline__ void mma16816(float * c, const unsigned * a, unsigned
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x in one MUFU instruction (about 2 ulp; -inf gives 0).  The probabilities are rounded to bfloat16 next.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned *>(&v);
@@ -79,6 +85,7 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
     unsigned char * sQ = smem;
     unsigned char * sK = sQ + BM * HD * 2;                 // [2][BN][HD]
     unsigned char * sV = sK + 2 * BN * HD * 2;             // [2][BN][HD]
+    __shared__ long long s_cell[2][BN];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g_ = lane >> 2, t_ = lane & 3;
@@ -116,25 +123,32 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
             cp_async16(smem_u32(sQ + swz<HD>(r, ch)), src, valid);
         }
     };
-    auto load_kv = [&](int tile, int stage) {
+    // Row bases (element offset of a key's row in the cache, -1: nothing to load) are looked up once per
+    // row into shared memory; the copies then run over consecutive 16-byte chunks, so that a warp's
+    // request covers whole contiguous rows.
+    auto lookup_rows = [&](int tile, int slot) {
+        if (tid < BN) {
+            const int j = tile * BN + tid;
+            long long cell = -1;
+            if (tile < tile_end && j <= k_hi) {
+                const int page = bt[j / p.page_size];
+                if (page >= 0 && page < p.num_pages)
+                    cell = (((long long) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+            }
+            s_cell[slot][tid] = cell;
+        }
+    };
+    auto load_kv = [&](int stage, int slot) {
         unsigned char * dK = sK + stage * BN * HD * 2;
         unsigned char * dV = sV + stage * BN * HD * 2;
-        // NW * 32 threads share BN rows: each thread takes a fixed slice of one row -> one page lookup
-        constexpr int TPR = NW * 32 / BN;                  // threads per row
-        constexpr int CPT = CH / TPR;                      // chunks per thread
-        const int r = tid / TPR, c0 = (tid % TPR) * CPT;
-        const int j = tile * BN + r;
-        bool valid = j <= k_hi;
-        size_t cell = 0;
-        if (valid) {
-            const int page = bt[j / p.page_size];
-            if (page < 0 || page >= p.num_pages) valid = false;
-            else cell = (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
-        }
 #pragma unroll
-        for (int c = 0; c < CPT; c++) {
-            cp_async16(smem_u32(dK + swz<HD>(r, c0 + c)), p.k_cache + cell + (c0 + c) * 8, valid);
-            cp_async16(smem_u32(dV + swz<HD>(r, c0 + c)), p.v_cache + cell + (c0 + c) * 8, valid);
+        for (int c = tid; c < BN * CH; c += NW * 32) {
+            const int r = c / CH, ch = c % CH;
+            const long long cell = s_cell[slot][r];
+            const bool valid = cell >= 0;
+            const size_t off = valid ? (size_t) cell + ch * 8 : 0;
+            cp_async16(smem_u32(dK + swz<HD>(r, ch)), p.k_cache + off, valid);
+            cp_async16(smem_u32(dV + swz<HD>(r, ch)), p.v_cache + off, valid);
         }
     };
 
@@ -157,8 +171,11 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
     const int warp_pos_min = pos0 + min(wr0, rows_total - 1) / G, warp_pos_max = pos0 + max(wr1, 0) / G;
 
     if (tile_begin < tile_end) {
+        lookup_rows(tile_begin, 0);
+        lookup_rows(tile_begin + 1, 1);
+        __syncthreads();
         load_q();
-        load_kv(tile_begin, 0);
+        load_kv(0, 0);
         cp_async_commit();
 
         unsigned qf[KS][4];
@@ -167,13 +184,14 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
         for (int tile = tile_begin; tile < tile_end; tile++) {
             const int stage = (tile - tile_begin) & 1;
             if (tile + 1 < tile_end) {
-                load_kv(tile + 1, stage ^ 1);
+                load_kv(stage ^ 1, stage ^ 1);      // rows of tile + 1 were looked up an iteration ago
                 cp_async_commit();
                 cp_async_wait<1>();
             } else {
                 cp_async_wait<0>();
             }
             __syncthreads();
+            lookup_rows(tile + 2, stage);           // slot `stage` held this tile's rows; its copies are issued
             if (!q_loaded) {
 #pragma unroll
                 for (int ks = 0; ks < KS; ks++) {
@@ -240,7 +258,7 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int h = e >> 1;
-                    const float pv = exp2f(fmaf(sc[nt][e], p.scale_log2, -neg[h]));       // exp2(-inf) = 0 for masked keys
+                    const float pv = fast_exp2(fmaf(sc[nt][e], p.scale_log2, -neg[h]));   // 2^-inf = 0 for masked keys
                     sc[nt][e] = pv;
                     sum[h] += pv;
                 }
@@ -328,6 +346,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     unsigned char * sK = sQ + BM * HD * 2;                   // [STAGES][BN][HD]
     unsigned char * sV = sK + STAGES * TILE_BYTES;           // [STAGES][BN][HD]
     __shared__ int s_last;
+    __shared__ long long s_cell[STAGES][BN];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g_ = lane >> 2, t_ = lane & 3;
@@ -354,23 +373,32 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     const int n_my = max(0, tile_end - tile_begin);
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
 
-    const int ld_r = tid >> 1, ld_c0 = (tid & 1) * (CH / 2);     // this thread's half row of every tile
-    auto lookup = [&](int tile) -> int {                         // page of this thread's row, -1: nothing to load
-        const int j = tile * BN + ld_r;
-        if (tile >= tile_end || j > k_hi) return -1;
-        const int page = bt[j / p.page_size];
-        return (page < 0 || page >= p.num_pages) ? -1 : page;
+    // Row bases (element offset of a key's row in the cache, -1: nothing to load) are looked up once per
+    // row into a ring of shared-memory slots, a tile ahead of the copies that use them; the copies run
+    // over consecutive 16-byte chunks, so that a warp's request covers whole contiguous rows.
+    auto lookup_rows = [&](int tile, int slot) {
+        if (tid < BN) {
+            const int j = tile * BN + tid;
+            long long cell = -1;
+            if (tile < tile_end && j <= k_hi) {
+                const int page = bt[j / p.page_size];
+                if (page >= 0 && page < p.num_pages)
+                    cell = (((long long) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+            }
+            s_cell[slot][tid] = cell;
+        }
     };
-    auto load_kv = [&](int tile, int stage, int page) {
-        const int j = tile * BN + ld_r;
-        const bool valid = page >= 0;
-        const size_t cell = valid ? (((size_t) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD : 0;
+    auto load_kv = [&](int stage) {                          // the slot of a tile is its stage
         unsigned char * dK = sK + stage * TILE_BYTES;
         unsigned char * dV = sV + stage * TILE_BYTES;
 #pragma unroll
-        for (int c = 0; c < CH / 2; c++) {
-            cp_async16(smem_u32(dK + swz<HD>(ld_r, ld_c0 + c)), p.k_cache + cell + (ld_c0 + c) * 8, valid);
-            cp_async16(smem_u32(dV + swz<HD>(ld_r, ld_c0 + c)), p.v_cache + cell + (ld_c0 + c) * 8, valid);
+        for (int c = tid; c < BN * CH; c += NW * 32) {
+            const int r = c / CH, ch = c % CH;
+            const long long cell = s_cell[stage][r];
+            const bool valid = cell >= 0;
+            const size_t off = valid ? (size_t) cell + ch * 8 : 0;
+            cp_async16(smem_u32(dK + swz<HD>(r, ch)), p.k_cache + off, valid);
+            cp_async16(smem_u32(dV + swz<HD>(r, ch)), p.v_cache + off, valid);
         }
     };
 
@@ -389,8 +417,10 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     const bool rows_full = row0 + BM <= rows_total;
 
     if (n_my > 0) {
-        const int pg0 = lookup(tile_begin), pg1 = lookup(tile_begin + 1);
-        int pg_next = lookup(tile_begin + 2);
+        lookup_rows(tile_begin, 0);
+        lookup_rows(tile_begin + 1, 1);
+        lookup_rows(tile_begin + 2, 2);
+        __syncthreads();
         for (int c = tid; c < BM * CH; c += NW * 32) {          // Q rows
             const int r = c / CH, ch = c % CH;
             const int R = row0 + r;
@@ -398,18 +428,18 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
             const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
             cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
         }
-        load_kv(tile_begin, 0, pg0);
+        load_kv(0);
         cp_async_commit();
-        if (n_my > 1) load_kv(tile_begin + 1, 1, pg1);
+        if (n_my > 1) load_kv(1);
         cp_async_commit();
 
         unsigned qf[KS][4];
         for (int i = 0; i < n_my; i++) {
-            if (i + 2 < n_my) load_kv(tile_begin + i + 2, (i + 2) % STAGES, pg_next);
+            if (i + 2 < n_my) load_kv((i + 2) % STAGES);
             cp_async_commit();
-            pg_next = lookup(tile_begin + i + 3);                // used one iteration from now
             cp_async_wait<2>();
             __syncthreads();
+            lookup_rows(tile_begin + i + 3, i % STAGES);         // this tile's copies were issued two iterations ago
             if (i == 0) {
 #pragma unroll
                 for (int ks = 0; ks < KS; ks++)
@@ -462,7 +492,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int h = e >> 1;
-                    const float pv = exp2f(fmaf(sc[nt][e], p.scale_log2, -neg[h]));
+                    const float pv = fast_exp2(fmaf(sc[nt][e], p.scale_log2, -neg[h]));
                     sc[nt][e] = pv;
                     sum[h] += pv;
                 }
