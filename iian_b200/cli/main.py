@@ -182,7 +182,7 @@ def cmd_bench(argv: List[str]) -> int:
 def cmd_random_weights(argv: List[str]) -> int:
     o = Options("iian random-weights", "Write a model folder (config.json, model.safetensors) with random weights "
                                        "from a configuration and a seed.")
-    o.positional("config", "a config.json (or a folder holding one) that gives the architecture and every size")
+    o.positional("model_config", "a config.json (or a folder holding one) that gives the architecture and every size")
     o.positional("out", "folder to write")
     o.add("--seed", "Seed of the weights", "N", 0, int)
     o.add("--std", "Standard deviation of the matrices", "X", 0.02, float)
@@ -193,7 +193,7 @@ def cmd_random_weights(argv: List[str]) -> int:
     import torch
     from ..config.registry import architecture_of
     from ..weights.random_init import write_model_folder
-    path = os.path.join(ns.config, "config.json") if os.path.isdir(ns.config) else ns.config
+    path = os.path.join(ns.model_config, "config.json") if os.path.isdir(ns.model_config) else ns.model_config
     try:
         with open(path, "r", encoding="utf-8") as f:
             raw = json.load(f)
