@@ -416,10 +416,16 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     const int pos_min = pos0 + tok_min, pos_max = pos0 + tok_max;
     const bool rows_full = row0 + BM <= rows_total;
 
+    // Everything up to here reads only the step's integer buffers, which were uploaded before the first
+    // kernel of the step; Q and the newest K/V rows come from the kernel before this one.
+    pdl_launch_dependents();
     if (n_my > 0) {
         lookup_rows(tile_begin, 0);
         lookup_rows(tile_begin + 1, 1);
         lookup_rows(tile_begin + 2, 2);
+    }
+    pdl_wait();
+    if (n_my > 0) {
         __syncthreads();
         for (int c = tid; c < BM * CH; c += NW * 32) {          // Q rows
             const int r = c / CH, ch = c % CH;
@@ -630,8 +636,7 @@ static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t
         configured = true;
     }
     dim3 grid((max_rows + 15) / 16, p.nkv, S * p.n_split);
-    attention_decode_kernel<HD><<<grid, 128, smem, stream>>>(p);
-    return iian_launch_status();
+    return iian_launch(attention_decode_kernel<HD>, grid, dim3(128), smem, stream, p);
 }
 
 // merge the n_split partial results of every (token, head): one warp per row

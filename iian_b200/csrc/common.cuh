@@ -25,6 +25,41 @@ static inline int iian_launch_status() {
 
 namespace iian {
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// A decode step is a chain of short kernels; with the usual stream order each one starts only after the
+// one before it has drained.  Launched with the programmatic-serialization attribute, a kernel may begin
+// while its predecessor is still running: it announces that its own successor may be launched
+// (pdl_launch_dependents), does what does not depend on the predecessor (index arithmetic, fetching
+// weights), and calls pdl_wait() before it first reads what the predecessor wrote or writes anything
+// itself.  pdl_wait() returns once the predecessor grid has completed and its writes are visible; without
+// the launch attribute both calls do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+}  // namespace iian
+
+// Host side: set by iian_set_pdl (every library has its own copy; the Python layer sets them all).
+static int g_iian_pdl = 0;
+IIAN_API void iian_set_pdl(int on) { g_iian_pdl = on ? 1 : 0; }
+
+template <typename... KArgs, typename... Args>
+static inline int iian_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_iian_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    return e == cudaSuccess ? IIAN_OK : 1000 + (int) e;
+}
+
+namespace iian {
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -15,6 +15,8 @@ namespace iian {
 template <typename W>
 __global__ void embedding_kernel(const W * __restrict__ table, const int * __restrict__ tokens,
                                  float * __restrict__ out, int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t];
     float * o = out + (size_t) t * H;
@@ -32,6 +34,8 @@ template <typename A>
 __global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta,
                                     const float * __restrict__ weight, A * __restrict__ out,
                                     int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     const size_t base = (size_t) blockIdx.x * H;
     float * r = residual + base;
@@ -82,6 +86,8 @@ template <typename A, int VPT>
 __global__ void add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ delta,
                                         const float * __restrict__ weight, A * __restrict__ out,
                                         int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     const size_t base = (size_t) blockIdx.x * H;
     const int groups = H >> 2;
@@ -133,6 +139,8 @@ __global__ void rms_norm_kernel(const A * __restrict__ x, const float * __restri
 
 template <typename A>
 __global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t row = idx / F;
@@ -146,6 +154,8 @@ __global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ o
 // 8 elements per thread with 16-byte (bf16) or 2 x 16-byte (f32) accesses; needs F % 8 == 0
 template <typename A>
 __global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t groups) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t gidx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (gidx >= groups) return;
     const int per_row = F >> 3;
@@ -169,6 +179,8 @@ __global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict
 template <typename T>
 __global__ void gather_rows_kernel(const T * __restrict__ src, const int * __restrict__ rows,
                                    T * __restrict__ out, int H, int n_src) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = rows[blockIdx.x];
     T * o = out + (size_t) blockIdx.x * H;
     if (r < 0 || r >= n_src) {
@@ -194,10 +206,9 @@ IIAN_API int iian_embedding(const void * table, int table_dtype, const int * tok
                             int N, int H, int V, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     const int threads = H >= 1024 ? 256 : 128;
-    if (table_dtype == IIAN_F32) embedding_kernel<float><<<N, threads, 0, stream>>>((const float *) table, tokens, out, H, V);
-    else if (table_dtype == IIAN_BF16) embedding_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>((const __nv_bfloat16 *) table, tokens, out, H, V);
-    else return IIAN_ERR_DTYPE;
-    return iian_launch_status();
+    if (table_dtype == IIAN_F32) return iian_launch(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) table, tokens, out, H, V);
+    if (table_dtype == IIAN_BF16) return iian_launch(embedding_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) table, tokens, out, H, V);
+    return IIAN_ERR_DTYPE;
 }
 
 IIAN_API int iian_add_rms_norm(float * residual, const void * delta, const float * weight, void * out,
@@ -213,14 +224,12 @@ IIAN_API int iian_add_rms_norm(float * residual, const void * delta, const float
         while (threads < 1024 && threads * 2 <= groups) threads *= 2;      // >= 2 groups per thread up to 1024 threads
         while (threads * 4 < groups) threads *= 2;
         if (threads > 1024) threads = 1024;
-        if (act_dtype == IIAN_F32) add_rms_norm_vec_kernel<float, 4><<<N, threads, 0, stream>>>(residual, (const float *) delta, weight, (float *) out, H, eps);
-        else add_rms_norm_vec_kernel<__nv_bfloat16, 4><<<N, threads, 0, stream>>>(residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
-        return iian_launch_status();
+        if (act_dtype == IIAN_F32) return iian_launch(add_rms_norm_vec_kernel<float, 4>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta, weight, (float *) out, H, eps);
+        return iian_launch(add_rms_norm_vec_kernel<__nv_bfloat16, 4>, dim3(N), dim3(threads), 0, stream, residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
     }
     const int threads = 256;
-    if (act_dtype == IIAN_F32) add_rms_norm_kernel<float><<<N, threads, 0, stream>>>(residual, (const float *) delta, weight, (float *) out, H, eps);
-    else add_rms_norm_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>(residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
-    return iian_launch_status();
+    if (act_dtype == IIAN_F32) return iian_launch(add_rms_norm_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta, weight, (float *) out, H, eps);
+    return iian_launch(add_rms_norm_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
 }
 
 IIAN_API int iian_rms_norm(const void * x, const float * weight, void * out, int act_dtype, int N, int H,
@@ -240,25 +249,22 @@ IIAN_API int iian_swiglu(const void * gate_up, void * out, int act_dtype, int N,
     if (F % 8 == 0 && ((uintptr_t) gate_up & 15) == 0 && ((uintptr_t) out & 15) == 0 && (act_dtype == IIAN_F32 || act_dtype == IIAN_BF16)) {
         const size_t groups = total / 8;
         const unsigned vblocks = (unsigned) ((groups + threads - 1) / threads);
-        if (act_dtype == IIAN_F32) swiglu_vec_kernel<float><<<vblocks, threads, 0, stream>>>((const float *) gate_up, (float *) out, F, groups);
-        else swiglu_vec_kernel<__nv_bfloat16><<<vblocks, threads, 0, stream>>>((const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, groups);
-        return iian_launch_status();
+        if (act_dtype == IIAN_F32) return iian_launch(swiglu_vec_kernel<float>, dim3(vblocks), dim3(threads), 0, stream, (const float *) gate_up, (float *) out, F, groups);
+        return iian_launch(swiglu_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, groups);
     }
     const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
-    if (act_dtype == IIAN_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float *) gate_up, (float *) out, F, total);
-    else if (act_dtype == IIAN_BF16) swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, total);
-    else return IIAN_ERR_DTYPE;
-    return iian_launch_status();
+    if (act_dtype == IIAN_F32) return iian_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) gate_up, (float *) out, F, total);
+    if (act_dtype == IIAN_BF16) return iian_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, total);
+    return IIAN_ERR_DTYPE;
 }
 
 IIAN_API int iian_gather_rows(const void * src, const int * rows, void * out, int dtype, int R, int H,
                               int n_src, cudaStream_t stream) {
     if (R <= 0) return IIAN_OK;
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == IIAN_F32) gather_rows_kernel<float><<<R, threads, 0, stream>>>((const float *) src, rows, (float *) out, H, n_src);
-    else if (dtype == IIAN_BF16) gather_rows_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>((const __nv_bfloat16 *) src, rows, (__nv_bfloat16 *) out, H, n_src);
-    else return IIAN_ERR_DTYPE;
-    return iian_launch_status();
+    if (dtype == IIAN_F32) return iian_launch(gather_rows_kernel<float>, dim3(R), dim3(threads), 0, stream, (const float *) src, rows, (float *) out, H, n_src);
+    if (dtype == IIAN_BF16) return iian_launch(gather_rows_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, (const __nv_bfloat16 *) src, rows, (__nv_bfloat16 *) out, H, n_src);
+    return IIAN_ERR_DTYPE;
 }
 
 IIAN_API int iian_add_bias(void * x, const float * bias, int act_dtype, int N, int M, cudaStream_t stream) {

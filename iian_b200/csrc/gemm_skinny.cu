@@ -39,6 +39,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     int B, int M, int K) {
     extern __shared__ float red_raw[];
     float (*red)[MT * 16][NT * 8 + 1] = reinterpret_cast<float (*)[MT * 16][NT * 8 + 1]>(red_raw);
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.x * (16 * MT);
@@ -65,9 +66,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
             for (int i = 0; i < 4; i++) acc[mt][nt][i] = 0.0f;
 
     const int nchunks = K / 32;                      // a chunk = 32 k = 4 x 16 bytes per row
-    int c = warp;
-    for (; c + (UNROLL - 1) * WARPS < nchunks; c += UNROLL * WARPS) {
-        uint4 a0[UNROLL][MT], a1[UNROLL][MT];
+    uint4 a0[UNROLL][MT], a1[UNROLL][MT];
+    auto load_round = [&](int c) {
 #pragma unroll
         for (int u = 0; u < UNROLL; u++)
 #pragma unroll
@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
                 a0[u][mt] = ld_stream(w0[mt] + (size_t) (c + u * WARPS) * 4);
                 a1[u][mt] = ld_stream(w1[mt] + (size_t) (c + u * WARPS) * 4);
             }
+    };
+    auto compute_round = [&](int c) {
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
 #pragma unroll
@@ -87,21 +89,35 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
                 }
             }
         }
+    };
+    // The weights do not depend on the kernel before this one: the first round of loads is in flight
+    // before this kernel waits for its activations.
+    int c = warp;
+    const bool first_round = c + (UNROLL - 1) * WARPS < nchunks;
+    if (first_round) load_round(c);
+    pdl_wait();
+    if (first_round) {
+        compute_round(c);
+        c += UNROLL * WARPS;
+    }
+    for (; c + (UNROLL - 1) * WARPS < nchunks; c += UNROLL * WARPS) {
+        load_round(c);
+        compute_round(c);
     }
     for (; c < nchunks; c += WARPS) {
-        uint4 a0[MT], a1[MT];
+        uint4 t0[MT], t1[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
-            a0[mt] = ld_stream(w0[mt] + (size_t) c * 4);
-            a1[mt] = ld_stream(w1[mt] + (size_t) c * 4);
+            t0[mt] = ld_stream(w0[mt] + (size_t) c * 4);
+            t1[mt] = ld_stream(w1[mt] + (size_t) c * 4);
         }
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             const uint4 b = __ldg(xr[nt] + (size_t) c * 4);
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
-                mma_bf16_16816(acc[mt][nt], a0[mt].x, a1[mt].x, a0[mt].y, a1[mt].y, b.x, b.y);
-                mma_bf16_16816(acc[mt][nt], a0[mt].z, a1[mt].z, a0[mt].w, a1[mt].w, b.z, b.w);
+                mma_bf16_16816(acc[mt][nt], t0[mt].x, t1[mt].x, t0[mt].y, t1[mt].y, b.x, b.y);
+                mma_bf16_16816(acc[mt][nt], t0[mt].z, t1[mt].z, t0[mt].w, t1[mt].w, b.z, b.w);
             }
         }
     }
@@ -140,9 +156,8 @@ static int launch_cfg(const void * x, const void * w, void * out, int B, int M, 
             configured = true;
         }
     }
-    gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT><<<blocks, WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K);
-    return iian_launch_status();
+    return iian_launch(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT>, dim3(blocks), dim3(WARPS * 32), smem, stream,
+                       (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K);
 }
 
 // cfg = MT * 100 + WARPS * 10 + UNROLL; 0 = the default for this (B, M)
@@ -153,17 +168,18 @@ static int launch_nt(const void * x, const void * w, void * out, int B, int M, i
         else if (NT == 2) cfg = 284;
         else cfg = 282;
     }
+    if (NT == 1) {
+        switch (cfg) {
+            case 184: return launch_cfg<1, 1, 8, 4, OutT>(x, w, out, B, M, K, stream);
+            case 188: return launch_cfg<1, 1, 8, 8, OutT>(x, w, out, B, M, K, stream);
+            case 144: return launch_cfg<1, 1, 4, 4, OutT>(x, w, out, B, M, K, stream);
+            case 148: return launch_cfg<1, 1, 4, 8, OutT>(x, w, out, B, M, K, stream);
+        }
+        return IIAN_ERR_SHAPE;
+    }
     switch (cfg) {
-        case 184: return launch_cfg<NT, 1, 8, 4, OutT>(x, w, out, B, M, K, stream);
-        case 182: return launch_cfg<NT, 1, 8, 2, OutT>(x, w, out, B, M, K, stream);
-        case 144: return launch_cfg<NT, 1, 4, 4, OutT>(x, w, out, B, M, K, stream);
-        case 148: return launch_cfg<NT, 1, 4, 8, OutT>(x, w, out, B, M, K, stream);
         case 284: return launch_cfg<NT, 2, 8, 4, OutT>(x, w, out, B, M, K, stream);
         case 282: return launch_cfg<NT, 2, 8, 2, OutT>(x, w, out, B, M, K, stream);
-        case 244: return launch_cfg<NT, 2, 4, 4, OutT>(x, w, out, B, M, K, stream);
-        case 242: return launch_cfg<NT, 2, 4, 2, OutT>(x, w, out, B, M, K, stream);
-        case 442: if (NT <= 4) return launch_cfg<(NT <= 4 ? NT : 4), 4, 4, 2, OutT>(x, w, out, B, M, K, stream); break;
-        case 482: if (NT <= 4) return launch_cfg<(NT <= 4 ? NT : 4), 4, 8, 2, OutT>(x, w, out, B, M, K, stream); break;
     }
     return IIAN_ERR_SHAPE;
 }

@@ -28,6 +28,8 @@ __global__ void qk_norm_rope_store_kernel(
     const int * __restrict__ slots,
     int N, int nh, int nkv, int hd, int rot_dim, int rope_style, float eps,
     int page_size, int num_pages, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nh + 2 * nkv;
     const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;
@@ -138,14 +140,13 @@ IIAN_API int iian_qk_norm_rope_store(
     const unsigned blocks = (unsigned) ((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const int threads = kWarpsPerBlock * 32;
     if (act_dtype == IIAN_F32)
-        qk_norm_rope_store_kernel<float><<<blocks, threads, 0, stream>>>(
+        return iian_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(threads), 0, stream,
             (const float *) qkv, bias, (float *) q_out, (float *) k_cache, (float *) v_cache, q_weight, k_weight,
             inv_freq, positions, slots, N, nh, nkv, hd, rot_dim, rope_style, eps, page_size, num_pages, write_kv);
-    else if (act_dtype == IIAN_BF16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+    if (act_dtype == IIAN_BF16)
+        return iian_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
             (const __nv_bfloat16 *) qkv, bias, (__nv_bfloat16 *) q_out, (__nv_bfloat16 *) k_cache,
             (__nv_bfloat16 *) v_cache, q_weight, k_weight, inv_freq, positions, slots, N, nh, nkv, hd, rot_dim,
             rope_style, eps, page_size, num_pages, write_kv);
-    else return IIAN_ERR_DTYPE;
-    return iian_launch_status();
+    return IIAN_ERR_DTYPE;
 }

@@ -86,6 +86,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float * __res
                                                              int * __restrict__ part_idx) {
     __shared__ float fs[32];
     __shared__ int is[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.y, part = blockIdx.x;
     const int per = (V + parts - 1) / parts;
     const int begin = min(V, part * per), end = min(V, begin + per);
@@ -120,6 +122,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float * __res
 
 __global__ void argmax_final_kernel(const float * __restrict__ part_val, const int * __restrict__ part_idx, int parts,
                                     int * __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, lane = threadIdx.x;       // one warp per row
     float b = -INFINITY;
     int bi = 0x7fffffff;
@@ -350,9 +354,9 @@ IIAN_API int iian_argmax_wide(const float * logits, int R, int V, long long stri
     if (V <= 0 || parts == 0 || scratch == nullptr || R > 65535) return IIAN_ERR_SHAPE;
     float * pv = (float *) scratch;
     int * pi = (int *) (pv + (size_t) R * parts);
-    argmax_partial_kernel<<<dim3(parts, R), 256, 0, stream>>>(logits, V, (size_t) stride, parts, pv, pi);
-    argmax_final_kernel<<<R, 32, 0, stream>>>(pv, pi, parts, out);
-    return iian_launch_status();
+    const int rc = iian_launch(argmax_partial_kernel, dim3(parts, R), dim3(256), 0, stream, logits, V, (size_t) stride, parts, pv, pi);
+    if (rc != IIAN_OK) return rc;
+    return iian_launch(argmax_final_kernel, dim3(R), dim3(32), 0, stream, (const float *) pv, (const int *) pi, parts, out);
 }
 
 IIAN_API int iian_sample(const float * logits, int R, int V, long long stride, const float * temperature,

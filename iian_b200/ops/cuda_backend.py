@@ -10,6 +10,7 @@ mat-vec kernels do not cover).
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -68,8 +69,19 @@ def _stream() -> int:
 _sigs_done = set()
 
 
+# Programmatic dependent launch for the decode-path kernels (see csrc/common.cuh); IIAN_PDL=0 turns it off.
+PDL = os.environ.get("IIAN_PDL", "1") not in ("0", "false", "off")
+_pdl_set = set()
+
+
 def _fn(lib_name: str, fn_name: str, argtypes):
     lib = _build.load(lib_name)
+    if lib_name not in _pdl_set:
+        _pdl_set.add(lib_name)
+        if hasattr(lib, "iian_set_pdl"):
+            lib.iian_set_pdl.argtypes = [c_int]
+            lib.iian_set_pdl.restype = None
+            lib.iian_set_pdl(1 if PDL else 0)
     fn = getattr(lib, fn_name)
     key = (lib_name, fn_name)
     if key not in _sigs_done:
