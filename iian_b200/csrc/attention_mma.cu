@@ -418,7 +418,6 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 
     // Everything up to here reads only the step's integer buffers, which were uploaded before the first
     // kernel of the step; Q and the newest K/V rows come from the kernel before this one.
-    pdl_launch_dependents();
     if (n_my > 0) {
         lookup_rows(tile_begin, 0);
         lookup_rows(tile_begin + 1, 1);
@@ -532,6 +531,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
         }
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();        // the keys are read: the next kernel may start fetching its weights
 
     // ---- merge the four warps ------------------------------------------------------------------
 #pragma unroll

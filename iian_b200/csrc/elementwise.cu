@@ -15,8 +15,8 @@ namespace iian {
 template <typename W>
 __global__ void embedding_kernel(const W * __restrict__ table, const int * __restrict__ tokens,
                                  float * __restrict__ out, int H, int V) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = tokens[t];
     float * o = out + (size_t) t * H;
@@ -34,8 +34,8 @@ template <typename A>
 __global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta,
                                     const float * __restrict__ weight, A * __restrict__ out,
                                     int H, float eps) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[32];
     const size_t base = (size_t) blockIdx.x * H;
     float * r = residual + base;
@@ -86,8 +86,8 @@ template <typename A, int VPT>
 __global__ void add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ delta,
                                         const float * __restrict__ weight, A * __restrict__ out,
                                         int H, float eps) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[32];
     const size_t base = (size_t) blockIdx.x * H;
     const int groups = H >> 2;
@@ -139,8 +139,8 @@ __global__ void rms_norm_kernel(const A * __restrict__ x, const float * __restri
 
 template <typename A>
 __global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t total) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t row = idx / F;
@@ -154,8 +154,8 @@ __global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ o
 // 8 elements per thread with 16-byte (bf16) or 2 x 16-byte (f32) accesses; needs F % 8 == 0
 template <typename A>
 __global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t groups) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const size_t gidx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (gidx >= groups) return;
     const int per_row = F >> 3;
@@ -179,8 +179,8 @@ __global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict
 template <typename T>
 __global__ void gather_rows_kernel(const T * __restrict__ src, const int * __restrict__ rows,
                                    T * __restrict__ out, int H, int n_src) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int r = rows[blockIdx.x];
     T * o = out + (size_t) blockIdx.x * H;
     if (r < 0 || r >= n_src) {

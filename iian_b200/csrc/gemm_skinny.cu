@@ -36,10 +36,10 @@ __device__ __forceinline__ void mma_bf16_16816(float * c, unsigned a0, unsigned 
 template <int NT, int MT, int WARPS, int UNROLL, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     const __nv_bfloat16 * __restrict__ x, const __nv_bfloat16 * __restrict__ w, OutT * __restrict__ out,
-    int B, int M, int K) {
+    int B, int M, int K, float * __restrict__ part, int * __restrict__ counters) {
     extern __shared__ float red_raw[];
+    __shared__ int s_last;
     float (*red)[MT * 16][NT * 8 + 1] = reinterpret_cast<float (*)[MT * 16][NT * 8 + 1]>(red_raw);
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.x * (16 * MT);
@@ -92,19 +92,22 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     };
     // The weights do not depend on the kernel before this one: the first round of loads is in flight
     // before this kernel waits for its activations.
-    int c = warp;
-    const bool first_round = c + (UNROLL - 1) * WARPS < nchunks;
+    // gridDim.y CTAs split K between them (contiguous ranges of chunks); inside a CTA the warps interleave
+    const int ksplit = gridDim.y, ks = blockIdx.y;
+    const int c_begin = (int) ((long long) nchunks * ks / ksplit), c_end = (int) ((long long) nchunks * (ks + 1) / ksplit);
+    int c = c_begin + warp;
+    const bool first_round = c + (UNROLL - 1) * WARPS < c_end;
     if (first_round) load_round(c);
     pdl_wait();
     if (first_round) {
         compute_round(c);
         c += UNROLL * WARPS;
     }
-    for (; c + (UNROLL - 1) * WARPS < nchunks; c += UNROLL * WARPS) {
+    for (; c + (UNROLL - 1) * WARPS < c_end; c += UNROLL * WARPS) {
         load_round(c);
         compute_round(c);
     }
-    for (; c < nchunks; c += WARPS) {
+    for (; c < c_end; c += WARPS) {
         uint4 t0[MT], t1[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
@@ -121,6 +124,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
             }
         }
     }
+    // The weights are read: let the next kernel of the chain start (it waits for this grid's results
+    // before it touches them).  Triggering earlier would let a whole cascade of future kernels become
+    // resident and spin, taking registers and shared memory from the kernel that is actually running.
+    pdl_launch_dependents();
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
@@ -132,19 +139,50 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
         }
     __syncthreads();
     constexpr int ROWS = MT * 16;
-    for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += blockDim.x) {
+    constexpr int CELLS = ROWS * NT * 8;
+    if (ksplit == 1) {
+        for (int idx = threadIdx.x; idx < CELLS; idx += blockDim.x) {
+            const int n = idx / ROWS, r = idx % ROWS;
+            const int m = m0 + r;
+            if (n >= B || m >= M) continue;
+            float s = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < WARPS; wv++) s += red[wv][r][n];      // fixed order: independent of the batch
+            out[(size_t) n * M + m] = from_f32<OutT>(s);
+        }
+        return;
+    }
+    // split K: every CTA leaves its partial sums in scratch; the CTA that arrives last for this row block
+    // adds the parts in the order of their index (not of their arrival) and writes the result
+    float * mine = part + ((size_t) blockIdx.x * ksplit + ks) * CELLS;
+    for (int idx = threadIdx.x; idx < CELLS; idx += blockDim.x) {
+        const int n = idx / ROWS, r = idx % ROWS;
+        float s = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < WARPS; wv++) s += red[wv][r][n];
+        mine[idx] = s;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(counters + blockIdx.x, 1) == ksplit - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float * all = part + (size_t) blockIdx.x * ksplit * CELLS;
+    for (int idx = threadIdx.x; idx < CELLS; idx += blockDim.x) {
         const int n = idx / ROWS, r = idx % ROWS;
         const int m = m0 + r;
         if (n >= B || m >= M) continue;
         float s = 0.0f;
-#pragma unroll
-        for (int wv = 0; wv < WARPS; wv++) s += red[wv][r][n];      // fixed order: independent of the batch
+        for (int i = 0; i < ksplit; i++) s += __ldcg(all + (size_t) i * CELLS + idx);
         out[(size_t) n * M + m] = from_f32<OutT>(s);
     }
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 
 template <int NT, int MT, int WARPS, int UNROLL, typename OutT>
-static int launch_cfg(const void * x, const void * w, void * out, int B, int M, int K, cudaStream_t stream) {
+static int launch_cfg(const void * x, const void * w, void * out, int B, int M, int K, int ksplit, float * part,
+                      int * counters, cudaStream_t stream) {
     const unsigned blocks = (unsigned) ((M + 16 * MT - 1) / (16 * MT));
     constexpr size_t smem = sizeof(float) * WARPS * MT * 16 * (NT * 8 + 1);
     if (smem > 48 * 1024) {
@@ -156,13 +194,14 @@ static int launch_cfg(const void * x, const void * w, void * out, int B, int M, 
             configured = true;
         }
     }
-    return iian_launch(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT>, dim3(blocks), dim3(WARPS * 32), smem, stream,
-                       (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K);
+    return iian_launch(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT>, dim3(blocks, ksplit), dim3(WARPS * 32), smem, stream,
+                       (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K, part, counters);
 }
 
 // cfg = MT * 100 + WARPS * 10 + UNROLL; 0 = the default for this (B, M)
 template <int NT, typename OutT>
-static int launch_nt(const void * x, const void * w, void * out, int B, int M, int K, int cfg, cudaStream_t stream) {
+static int launch_nt(const void * x, const void * w, void * out, int B, int M, int K, int cfg, int ksplit, float * part,
+                     int * counters, cudaStream_t stream) {
     if (cfg == 0) {
         if (NT == 1) cfg = M >= 65536 ? 144 : 184;
         else if (NT == 2) cfg = 284;
@@ -170,26 +209,27 @@ static int launch_nt(const void * x, const void * w, void * out, int B, int M, i
     }
     if (NT == 1) {
         switch (cfg) {
-            case 184: return launch_cfg<1, 1, 8, 4, OutT>(x, w, out, B, M, K, stream);
-            case 188: return launch_cfg<1, 1, 8, 8, OutT>(x, w, out, B, M, K, stream);
-            case 144: return launch_cfg<1, 1, 4, 4, OutT>(x, w, out, B, M, K, stream);
-            case 148: return launch_cfg<1, 1, 4, 8, OutT>(x, w, out, B, M, K, stream);
+            case 184: return launch_cfg<1, 1, 8, 4, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 188: return launch_cfg<1, 1, 8, 8, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 144: return launch_cfg<1, 1, 4, 4, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 148: return launch_cfg<1, 1, 4, 8, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
         }
         return IIAN_ERR_SHAPE;
     }
     switch (cfg) {
-        case 284: return launch_cfg<NT, 2, 8, 4, OutT>(x, w, out, B, M, K, stream);
-        case 282: return launch_cfg<NT, 2, 8, 2, OutT>(x, w, out, B, M, K, stream);
+        case 284: return launch_cfg<NT, 2, 8, 4, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+        case 282: return launch_cfg<NT, 2, 8, 2, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
     }
     return IIAN_ERR_SHAPE;
 }
 
 template <typename OutT>
-static int launch_skinny(const void * x, const void * w, void * out, int B, int M, int K, int cfg, cudaStream_t stream) {
-    if (B <= 8) return launch_nt<1, OutT>(x, w, out, B, M, K, cfg, stream);
-    if (B <= 16) return launch_nt<2, OutT>(x, w, out, B, M, K, cfg, stream);
-    if (B <= 32) return launch_nt<4, OutT>(x, w, out, B, M, K, cfg, stream);
-    return launch_nt<8, OutT>(x, w, out, B, M, K, cfg, stream);
+static int launch_skinny(const void * x, const void * w, void * out, int B, int M, int K, int cfg, int ksplit, float * part,
+                         int * counters, cudaStream_t stream) {
+    if (B <= 8) return launch_nt<1, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (B <= 16) return launch_nt<2, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (B <= 32) return launch_nt<4, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    return launch_nt<8, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
 }
 
 }  // namespace iian
@@ -198,19 +238,24 @@ using namespace iian;
 
 // x: [B, K] bf16, w: [M, K] bf16, out: [B, M] bf16 or f32.  Needs 1 <= B <= 64, K a multiple of 32
 // and 16-byte aligned x and w (rows are then aligned too).  cfg selects a tile configuration
-// (MT * 100 + WARPS * 10 + UNROLL); 0 takes the default.
+// (MT * 100 + WARPS * 10 + UNROLL); 0 takes the default.  ksplit > 1 cuts K over that many CTAs per row
+// block and needs scratch: part = ceil(M / rows per block) * ksplit * (rows per block * 8 * ceil(B / 8))
+// floats and counters = ceil(M / rows per block) ints that are zero before the first launch (the kernel
+// leaves them zero).
 IIAN_API int iian_gemm_skinny_cfg(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
-                                  int cfg, cudaStream_t stream) {
+                                  int cfg, int ksplit, float * part, int * counters, cudaStream_t stream) {
     if (B <= 0 || M <= 0) return IIAN_OK;
     if (B > 64) return IIAN_ERR_LIMIT;
     if (K <= 0 || K % 32 != 0) return IIAN_ERR_SHAPE;
     if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
-    if (out_dtype == IIAN_BF16) return launch_skinny<__nv_bfloat16>(x, w, out, B, M, K, cfg, stream);
-    if (out_dtype == IIAN_F32) return launch_skinny<float>(x, w, out, B, M, K, cfg, stream);
+    if (ksplit < 1 || ksplit > 64 || ksplit > K / 32) return IIAN_ERR_SHAPE;
+    if (ksplit > 1 && (part == nullptr || counters == nullptr)) return IIAN_ERR_SHAPE;
+    if (out_dtype == IIAN_BF16) return launch_skinny<__nv_bfloat16>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (out_dtype == IIAN_F32) return launch_skinny<float>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
     return IIAN_ERR_DTYPE;
 }
 
 IIAN_API int iian_gemm_skinny(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
                               cudaStream_t stream) {
-    return iian_gemm_skinny_cfg(x, w, out, out_dtype, B, M, K, 0, stream);
+    return iian_gemm_skinny_cfg(x, w, out, out_dtype, B, M, K, 0, 1, nullptr, nullptr, stream);
 }

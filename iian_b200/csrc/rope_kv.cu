@@ -28,8 +28,8 @@ __global__ void qk_norm_rope_store_kernel(
     const int * __restrict__ slots,
     int N, int nh, int nkv, int hd, int rot_dim, int rope_style, float eps,
     int page_size, int num_pages, int write_kv) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nh + 2 * nkv;
     const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;

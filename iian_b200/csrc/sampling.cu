@@ -86,8 +86,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float * __res
                                                              int * __restrict__ part_idx) {
     __shared__ float fs[32];
     __shared__ int is[32];
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.y, part = blockIdx.x;
     const int per = (V + parts - 1) / parts;
     const int begin = min(V, part * per), end = min(V, begin + per);
@@ -122,8 +122,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float * __res
 
 __global__ void argmax_final_kernel(const float * __restrict__ part_val, const int * __restrict__ part_idx, int parts,
                                     int * __restrict__ out) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.x, lane = threadIdx.x;       // one warp per row
     float b = -INFINITY;
     int bi = 0x7fffffff;

@@ -69,8 +69,9 @@ def _stream() -> int:
 _sigs_done = set()
 
 
-# Programmatic dependent launch for the decode-path kernels (see csrc/common.cuh); IIAN_PDL=0 turns it off.
-PDL = os.environ.get("IIAN_PDL", "1") not in ("0", "false", "off")
+# Programmatic dependent launch for the decode-path kernels (see csrc/common.cuh).  Measured on the whole
+# decode step it does not pay (4.57 ms against 4.33 ms at batch 8), so it is off unless IIAN_PDL=1.
+PDL = os.environ.get("IIAN_PDL", "0") not in ("0", "false", "off")
 _pdl_set = set()
 
 
@@ -196,16 +197,56 @@ class CudaKernels:
                 type(self)._library_f32_out = False
         return False
 
-    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0) -> None:
-        """``cfg`` picks a tile configuration (rows-per-block tiles * 100 + warps * 10 + unroll); 0: default."""
+    def skinny_ksplit(self, n: int, m: int, k: int) -> int:
+        """Into how many CTAs K is cut: matrices with few rows would otherwise leave most of the GPU's
+        memory pipeline idle (a row block of 16 is one CTA)."""
+        if n > 8:
+            return 1
+        blocks = -(-m // 16)
+        want = -(-self.SKINNY_TARGET_CTAS // blocks)
+        return max(1, min(want, 8, k // 256))
+
+    SKINNY_TARGET_CTAS = 148 * 4
+
+    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0, ksplit: int = 0) -> None:
+        """``cfg`` picks a tile configuration (rows-per-block tiles * 100 + warps * 10 + unroll); ``ksplit``
+        the number of CTAs that share K for one row block; 0: defaults."""
         n, k = x.shape
         m = w.shape[0]
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: x and w must be bfloat16")
+        if ksplit <= 0:
+            ksplit = self.skinny_ksplit(n, m, k)
+        part = counters = 0
+        if ksplit > 1:
+            rows = 32 if n > 8 else 16
+            blocks = -(-m // rows)
+            nt = 1 if n <= 8 else 2 if n <= 16 else 4 if n <= 32 else 8
+            part = self.gemm_scratch(x.device, blocks * ksplit * rows * 8 * nt).data_ptr()
+            counters = self.gemm_counters(x.device, blocks).data_ptr()
         fn = _fn("gemm_skinny", "iian_gemm_skinny_cfg",
-                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
         _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
-                  n, m, k, cfg, _stream()), "gemm_skinny")
+                  n, m, k, cfg, ksplit, part, counters, _stream()), "gemm_skinny")
+
+    _gemm_scratch = {}
+    _gemm_counters = {}
+
+    def gemm_scratch(self, device, n_floats: int) -> torch.Tensor:
+        t = self._gemm_scratch.get(device)
+        if t is None or t.numel() < n_floats:
+            t = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+            self._gemm_scratch[device] = t
+            self._scratch_keep.append(t)
+        return t
+
+    def gemm_counters(self, device, n: int) -> torch.Tensor:
+        t = self._gemm_counters.get(device)
+        if t is None or t.numel() < n:
+            t = torch.zeros(max(n, 1 << 14), dtype=torch.int32, device=device)
+            self._gemm_counters[device] = t
+            self._scratch_keep.append(t)
+        return t
 
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         n, k = x.shape

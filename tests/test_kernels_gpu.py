@@ -304,6 +304,23 @@ def test_gemm_skinny(od, B, M, K_):
         (1 if od == torch.bfloat16 else 10)
 
 
+@pytest.mark.parametrize("ksplit", [2, 3, 8])
+@pytest.mark.parametrize("B,M,K_", [(1, 70, 512), (8, 257, 4096), (5, 4096, 1024), (33, 100, 2048)])
+def test_gemm_skinny_split_k(ksplit, B, M, K_):
+    """K cut over several CTAs: the last one to arrive adds the parts in index order, so two runs give the
+    same bits, and the counters are left at zero for the next launch."""
+    x = rnd(B, K_, dtype=torch.bfloat16, seed=30)
+    w = rnd(M, K_, dtype=torch.bfloat16, seed=31)
+    want = x.double().cpu() @ w.double().cpu().T
+    outs = []
+    for _ in range(3):
+        out = torch.full((B, M), float("nan"), dtype=torch.float32).cuda()
+        K().gemm_skinny(x, w, out, ksplit=ksplit)
+        outs.append(out.clone())
+    assert (outs[0].double().cpu() - want).abs().max() < 2e-4 * max(1.0, want.abs().max().item())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
 def test_gemm_skinny_rows_do_not_depend_on_the_batch():
     """Within the row counts the engine uses it for (up to 8), a row's result is the same bits whatever
     else is in the batch: the split of K over warps and the order of the final sum are fixed."""
