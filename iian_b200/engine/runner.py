@@ -16,6 +16,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
@@ -110,6 +112,7 @@ class ModelRunner:
                  cuda_graphs: bool = False, max_model_len: Optional[int] = None):
         self.model = model
         self.cuda_graphs = cuda_graphs and model.device.type == "cuda"
+        self.weight_prefetch = os.environ.get("IIAN_WEIGHT_PREFETCH", "1") not in ("0", "false", "off")
         self.max_model_len = max_model_len or capacity_tokens
         self._graphs: Dict[Tuple[int, int], "_GraphSlot"] = {}
         self.launches = 0                 # kernel launches issued through this runner (graph replays included)
@@ -331,15 +334,33 @@ class ModelRunner:
         kv_heads = [n.num_kv_heads for n in self.model.cache_needs().values() if isinstance(n, KVNeed)]
         k = ops.kernels()
         slot.n_split = k.attention_splits(num_seqs, min(kv_heads), ctx_bucket) if kv_heads and hasattr(k, "attention_splits") else 1
-        # run once eagerly (loads kernels, sizes every buffer), then capture the same launches
+        # run once eagerly (loads kernels, sizes every buffer, records the order in which weights are
+        # streamed), then capture the same launches -- with a side stream that prefetches the next weights
         ctx = self.build_context(entries, slot)
-        self.model.forward(ctx, self.storage)
+        prefetch = self.weight_prefetch and hasattr(k, "weight_log")
+        if prefetch:
+            k.weight_log = []
+        try:
+            self.model.forward(ctx, self.storage)
+        finally:
+            weights = k.weight_log if prefetch else None
+            if prefetch:
+                k.weight_log = None
         torch.cuda.synchronize(self.device)
         slot.workspace.frozen = True
         before = _launch_count()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            slot.logits = self.model.forward(ctx, self.storage)
+            if prefetch and weights:
+                from ..ops.cuda_backend import WeightPrefetcher
+                k.prefetcher = WeightPrefetcher(weights)
+            try:
+                slot.logits = self.model.forward(ctx, self.storage)
+                if k.prefetcher is not None:
+                    k.prefetcher.join()
+            finally:
+                if prefetch:
+                    k.prefetcher = None
         slot.launches = _launch_count() - before
         slot.graph = graph
         return slot

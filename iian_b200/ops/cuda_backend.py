@@ -173,10 +173,18 @@ class CudaKernels:
     # (measured on B200 at the Qwen3-8B sizes: the streaming kernel wins up to 8 rows, cuBLAS from 16)
     SKINNY_MAX_ROWS = 8
 
+    # Weight prefetch for captured decode graphs (see csrc/prefetch.cu and WeightPrefetcher below)
+    weight_log = None          # a list while the order of weight-streaming products is being recorded
+    prefetcher = None          # a WeightPrefetcher while a decode graph is being captured
+
     def _linear_dispatch(self, x, w, out, n, m, k) -> None:
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
             if n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
                 self.gemm_skinny(x, w, out)
+                if self.weight_log is not None:
+                    self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
+                if self.prefetcher is not None:
+                    self.prefetcher.after_product(self)
                 return
             if n > self.SKINNY_MAX_ROWS and self._library_gemm(x, w, out):
                 return
@@ -255,6 +263,10 @@ class CudaKernels:
                  [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
         _check(fn(_cuda(x, "linear x"), _code(x, "linear x"), _cuda(w, "linear w"), _code(w, "linear w"),
                   _cuda(out, "linear out"), _code(out, "linear out"), n, m, k, _stream()), "gemm_simt")
+
+    def prefetch_l2(self, ptr: int, nbytes: int) -> None:
+        fn = _fn("prefetch", "iian_prefetch_l2", [c_void_p, c_longlong, c_void_p])
+        _check(fn(ptr, nbytes, _stream()), "prefetch_l2")
 
     # ---- attention -----------------------------------------------------------------------
     def qk_norm_rope_store(self, qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
@@ -419,3 +431,58 @@ class CudaKernels:
                   _cuda(top_k, "top_k", torch.int32), _cuda(top_p, "top_p", torch.float32),
                   _cuda(min_p, "min_p", torch.float32), _cuda(uniform, "uniform", torch.float32),
                   _cuda(out, "sample out", torch.int32), _stream()), "sample")
+
+
+class WeightPrefetcher:
+    """Keeps HBM busy between the weight-streaming products of a captured decode step.
+
+    ``weights`` is the order in which the step's products read their weights (recorded on an eager
+    run).  After product ``i`` has been launched on the capturing stream, a side stream (forked with an
+    event, so it starts when product ``i`` completes) prefetches what comes next into L2: from the end of
+    what was prefetched so far up to ``window`` bytes beyond the start of product ``i + 1``'s weights.
+    The side stream is joined into the main stream before the capture ends.
+    """
+
+    def __init__(self, weights, window: int = 96 << 20):
+        self.weights = list(weights)
+        self.starts = []
+        pos = 0
+        for _, nbytes in self.weights:
+            self.starts.append(pos)
+            pos += nbytes
+        self.total = pos
+        self.window = window
+        self.side = torch.cuda.Stream()
+        self.index = 0             # products launched so far
+        self.cursor = 0            # bytes of the concatenated weight sequence already asked for
+        self.launches = 0
+
+    def after_product(self, kernels) -> None:
+        i = self.index
+        self.index += 1
+        if self.index >= len(self.weights):
+            return
+        begin = max(self.cursor, self.starts[self.index])
+        end = min(self.total, self.starts[self.index] + self.window)
+        if end <= begin:
+            return
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            j = self.index
+            while j < len(self.weights) and self.starts[j] < end:
+                ptr, nbytes = self.weights[j]
+                lo = max(begin, self.starts[j]) - self.starts[j]
+                hi = min(end, self.starts[j] + nbytes) - self.starts[j]
+                if hi > lo:
+                    kernels.prefetch_l2(ptr + lo, hi - lo)
+                    self.launches += 1
+                j += 1
+        self.cursor = end
+
+    def join(self) -> None:
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        torch.cuda.current_stream().wait_event(ev)
