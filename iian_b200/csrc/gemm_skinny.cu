@@ -203,7 +203,7 @@ template <int NT, typename OutT>
 static int launch_nt(const void * x, const void * w, void * out, int B, int M, int K, int cfg, int ksplit, float * part,
                      int * counters, cudaStream_t stream) {
     if (cfg == 0) {
-        if (NT == 1) cfg = M >= 65536 ? 144 : 184;
+        if (NT == 1) cfg = M >= 65536 ? 144 : (K >= 8192 ? 188 : 184);
         else if (NT == 2) cfg = 284;
         else cfg = 282;
     }
