@@ -1,0 +1,316 @@
+// out[t, n] = sum_k x[t, k] * w[n, k] for many rows t (prefill portions, large decode batches) on the
+// fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory, operands brought
+// into shared memory by TMA (cp.async.bulk.tensor, no multicast), an mbarrier pipeline between one
+// producer thread, one MMA-issuing thread and four epilogue warps.
+//
+// Both operands are K-major (activations [T, K] and weights [N, K], k contiguous), which is how the
+// weights are stored in the file and in the reference (ggml_mul_mat(W, x), src/iian/graph.cpp:121-160).
+// The reference hands products of this size to cuBLAS (third_party/ggml/src/ggml-cuda/ggml-cuda.cu:
+// 1548-1608); this kernel is the engine's own, so that what follows the product can ride in its
+// epilogue: a plain store, or SiLU(gate) * up for a gate|up matrix whose rows are interleaved in groups
+// of 8 (gate rows 16j..16j+7, up rows 16j+8..16j+15 hold the same 8 features).
+//
+// Tile: 128 rows x BN columns (BN = 128 or 256) per CTA, K in blocks of 64 (one 128-byte swizzle
+// atom), STAGES shared-memory stages.  Roles: warp 0 lane 0 issues TMA loads; warp 1 allocates tensor
+// memory and its lane 0 issues the MMAs (4 per K block, K = 16 each) and commits; warps 2..5 read the
+// accumulator (tcgen05.ld, 32 lanes each), convert and store.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter records where it gave up in
+// `status`, and every role falls through to the common exit, where tensor memory is freed.  A kernel
+// that gave up has written garbage; the host checks `status` after the stream has been synchronised.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace iian {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;                 // 64 bf16 = 128 bytes = one swizzle atom
+constexpr int TC_THREADS = 192;           // warp 0: TMA, warp 1: MMA + TMEM, warps 2..5: epilogue
+constexpr unsigned kSpinLimit = 2u * 1000u * 1000u;
+
+enum { EPI_STORE = 0, EPI_SWIGLU8 = 1 };
+
+struct TcStatus { int code; int where; };
+
+__device__ __forceinline__ unsigned smem_addr(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// bounded wait for the phase with this parity; false: gave up
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    for (unsigned spin = 0; spin < kSpinLimit; spin++) {
+        unsigned done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap * map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp gets lane i's 32 columns
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned * r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile with 128-byte rows, 128-byte swizzle, groups of 8 rows
+// 1024 bytes apart.  Start address and offsets are in units of 16 bytes.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long) ((addr & 0x3FFFF) >> 4);           // bits  0-13: start address
+    d |= (unsigned long long) 1 << 16;                            // bits 16-29: leading byte offset (unused with swizzle)
+    d |= (unsigned long long) (1024 >> 4) << 32;                  // bits 32-45: stride byte offset (8 rows)
+    d |= (unsigned long long) 1 << 46;                            // bits 46-47: descriptor version of this architecture
+    d |= (unsigned long long) 2 << 61;                            // bits 61-63: 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M x N tile.
+__host__ __device__ constexpr unsigned instr_desc_bf16(int m, int n) {
+    return (1u << 4)                      // accumulator format f32
+         | (1u << 7) | (1u << 10)         // A and B are bf16
+         | ((unsigned) (n >> 3) << 17)    // N / 8
+         | ((unsigned) (m >> 4) << 24);   // M / 16
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+    OutT * __restrict__ out, int T, int N, int K, int ldo, TcStatus * status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
+    unsigned char * smem = (unsigned char *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_addr(&full_bar[s]), 1); mbar_init(smem_addr(&empty_bar[s]), 1); }
+        mbar_init(smem_addr(&acc_bar), 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {          // tensor memory: BN columns of 128 lanes x 32 bits
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"((unsigned) BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer ---------------------------------------------------------------------------
+        for (int kb = 0; kb < num_kb; kb++) {
+            const int s = kb % STAGES;
+            const unsigned phase = (kb / STAGES) & 1;
+            if (!mbar_wait(smem_addr(&empty_bar[s]), phase ^ 1)) { status->code = 1; status->where = kb; failed = 1; break; }
+            const unsigned bar = smem_addr(&full_bar[s]);
+            mbar_expect_tx(bar, STAGE_BYTES);
+            tma_load_2d(smem_addr(smem + s * STAGE_BYTES), &map_a, kb * TC_BK, m0, bar);
+            tma_load_2d(smem_addr(smem + s * STAGE_BYTES + A_BYTES), &map_b, kb * TC_BK, n0, bar);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer -------------------------------------------------------------------------
+        constexpr unsigned idesc = instr_desc_bf16(TC_BM, BN);
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && ok; kb++) {
+            const int s = kb % STAGES;
+            const unsigned phase = (kb / STAGES) & 1;
+            if (!mbar_wait(smem_addr(&full_bar[s]), phase)) { status->code = 2; status->where = kb; failed = 1; ok = false; break; }
+            tc_fence_after();
+            const unsigned long long da = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES));
+            const unsigned long long db = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + A_BYTES));
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; k++)          // 32 bytes further along K per step, inside the swizzle atom
+                tc_mma(tmem_base, da + (unsigned long long) (k * 2), db + (unsigned long long) (k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_commit(smem_addr(&empty_bar[s]));          // the stage is free once these MMAs have read it
+        }
+        tc_commit(smem_addr(&acc_bar));                   // the accumulator is complete (or nothing was issued)
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 -------------------------
+        const int q = warp & 3;
+        const bool ok = mbar_wait(smem_addr(&acc_bar), 0);
+        if (!ok) { if (lane == 0) { status->code = 3; status->where = warp; } failed = 1; }
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                unsigned r[32];
+                tc_ld32(tmem_base + ((unsigned) (q * 32) << 16) + (unsigned) c0, r);
+                tc_wait_ld();
+                if (failed || row >= T) continue;
+                if (EPI == EPI_STORE) {
+                    const int col = n0 + c0;
+                    OutT * dst = out + (size_t) row * ldo + col;
+                    if (col + 32 <= N && (((uintptr_t) dst) & 15) == 0) {
+                        if (sizeof(OutT) == 2) {
+#pragma unroll
+                            for (int v = 0; v < 4; v++) {
+                                uint4 pk;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                                pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+                                pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+                                *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(dst) + 8 * v) = pk;
+                            }
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < 8; v++)
+                                *reinterpret_cast<uint4 *>(reinterpret_cast<float *>(dst) + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        }
+                    } else {
+                        for (int i = 0; i < 32; i++)
+                            if (col + i < N) dst[i] = from_f32<OutT>(__uint_as_float(r[i]));
+                    }
+                } else {
+                    // columns come in groups of 16: 8 gate values, then the 8 up values of the same features;
+                    // the output has N / 2 columns
+                    const int fcol = (n0 + c0) / 2;
+                    OutT * dst = out + (size_t) row * ldo + fcol;
+#pragma unroll
+                    for (int grp = 0; grp < 2; grp++) {
+                        float a[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const float g = __uint_as_float(r[16 * grp + i]), u = __uint_as_float(r[16 * grp + 8 + i]);
+                            a[i] = g / (1.0f + __expf(-g)) * u;
+                        }
+                        if (n0 + c0 + 16 * grp + 16 <= N) {
+                            if (sizeof(OutT) == 2 && (((uintptr_t) (dst + 8 * grp)) & 15) == 0) {
+                                uint4 pk;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
+                                pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+                                pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+                                *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(dst) + 8 * grp) = pk;
+                            } else {
+                                for (int i = 0; i < 8; i++) dst[8 * grp + i] = from_f32<OutT>(a[i]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---- common exit: everybody arrives here, also after a wait that gave up -------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned) BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void * p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn) p;
+    }
+    return fn;
+}
+
+// a [rows, K] bf16 row-major matrix, boxes of [box_rows, 64], 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap * map, const void * base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return IIAN_ERR_LIMIT;
+    cuuint64_t dims[2] = {(cuuint64_t) K, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) K * 2};
+    cuuint32_t box[2] = {(cuuint32_t) TC_BK, (cuuint32_t) box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? IIAN_OK : 2000 + (int) r;
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out, int T, int N, int K, int ldo, TcStatus * status,
+                     cudaStream_t stream) {
+    constexpr size_t smem = (size_t) STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, EPI, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        if (e != cudaSuccess) return 1000 + (int) e;
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (T + TC_BM - 1) / TC_BM);
+    gemm_tcgen05_kernel<BN, STAGES, EPI, OutT><<<grid, TC_THREADS, smem, stream>>>(ma, mb, (OutT *) out, T, N, K, ldo, status);
+    return iian_launch_status();
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+// x: [T, K] bf16, w: [N, K] bf16; out: [T, N] (epilogue 0) or [T, N / 2] (epilogue 1: SiLU(gate) * up over
+// rows interleaved in groups of 8), bf16 or f32.  K must be a multiple of 8 (16-byte rows for TMA), x and w
+// 16-byte aligned.  status: two ints on the device, zero before the launch; non-zero afterwards means a
+// wait gave up (code 1 producer, 2 MMA, 3 epilogue) and the output is not valid.
+IIAN_API int iian_gemm_tcgen05(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
+                               int bn, int * status, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return IIAN_OK;
+    if (K <= 0 || K % 8 != 0) return IIAN_ERR_SHAPE;
+    if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
+    if (epilogue == EPI_SWIGLU8 && N % 16 != 0) return IIAN_ERR_SHAPE;
+    if (status == nullptr) return IIAN_ERR_SHAPE;
+    if (bn != 128 && bn != 256) return IIAN_ERR_SHAPE;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, x, T, K, TC_BM);
+    if (rc != IIAN_OK) return rc;
+    rc = make_map(&mb, w, N, K, bn);
+    if (rc != IIAN_OK) return rc;
+    TcStatus * st = (TcStatus *) status;
+    const int ldo = epilogue == EPI_SWIGLU8 ? N / 2 : N;
+    if (out_dtype == IIAN_BF16) {
+        if (bn == 256) return epilogue == EPI_STORE ? launch_tc<256, 4, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream)
+                                                    : launch_tc<256, 4, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream);
+        return epilogue == EPI_STORE ? launch_tc<128, 6, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream)
+                                     : launch_tc<128, 6, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream);
+    }
+    if (out_dtype == IIAN_F32) {
+        if (epilogue != EPI_STORE) return IIAN_ERR_DTYPE;
+        if (bn == 256) return launch_tc<256, 4, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, stream);
+        return launch_tc<128, 6, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, stream);
+    }
+    return IIAN_ERR_DTYPE;
+}

@@ -258,6 +258,44 @@ class CudaKernels:
         _check(fn(_cuda(x, "linear x"), _code(x, "linear x"), _cuda(w, "linear w"), _code(w, "linear w"),
                   _cuda(out, "linear out"), _code(out, "linear out"), n, m, k, _stream()), "gemm_simt")
 
+    # ---- tcgen05 + TMA product for many rows ----------------------------------------------------
+    _tc_status = {}
+
+    def tcgen05_status_buffer(self, device) -> torch.Tensor:
+        t = self._tc_status.get(device)
+        if t is None:
+            t = torch.zeros(2, dtype=torch.int32, device=device)
+            self._tc_status[device] = t
+        return t
+
+    def tcgen05_check(self, device) -> None:
+        """Synchronise and raise if a tcgen05 kernel gave up waiting (its output would be garbage)."""
+        t = self._tc_status.get(device)
+        if t is None:
+            return
+        code, where = t.tolist()
+        if code != 0:
+            t.zero_()
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "an epilogue warp"}.get(code, f"role {code}")
+            raise KernelError(f"gemm_tcgen05: {role} gave up waiting on its barrier (at {where}); the result is not valid")
+
+    def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, bn: int = 0) -> None:
+        """``epilogue`` 0: out[t, n] = x . w; 1: w holds gate and up rows interleaved in groups of 8 and
+        out[t, f] = silu(gate_f) * up_f with half as many columns."""
+        t_rows, k = x.shape
+        n = w.shape[0]
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise KernelError("gemm_tcgen05: x and w must be bfloat16")
+        want_cols = n // 2 if epilogue == 1 else n
+        if w.shape[1] != k or out.shape != (t_rows, want_cols):
+            raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+        if bn == 0:
+            bn = 256 if n % 256 == 0 or n > 4096 else 128
+        fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
+                  t_rows, n, k, epilogue, bn, self.tcgen05_status_buffer(x.device).data_ptr(), _stream()), "gemm_tcgen05")
+
     def prefetch_l2(self, ptr: int, nbytes: int) -> None:
         fn = _fn("prefetch", "iian_prefetch_l2", [c_void_p, c_longlong, c_void_p])
         _check(fn(ptr, nbytes, _stream()), "prefetch_l2")
