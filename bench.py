@@ -251,6 +251,8 @@ def main() -> int:
         prefill = {"value": T / (p_ms * 1e-3), "tokens": T, "ms": p_ms,
                    "frac": flops / (p_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / (p_ms * 1e-3) / 1e12}
     sampler.stop()
+    if hasattr(kern, "tcgen05_check"):
+        kern.tcgen05_check(dev)          # a tcgen05 kernel that gave up on a barrier would have left garbage
 
     line = {
         "metric": "decode tokens/s (Qwen3-8B shape, batch 8)" if B == 8 else f"decode tokens/s (Qwen3-8B shape, batch {B})",

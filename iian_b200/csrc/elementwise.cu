@@ -137,23 +137,27 @@ __global__ void rms_norm_kernel(const A * __restrict__ x, const float * __restri
         out[base + i] = from_f32<A>(to_f32(x[base + i]) * inv * weight[i]);
 }
 
+// gate_up rows are [gate (F) | up (F)] (interleave 0) or groups of 16 columns holding 8 gate values and
+// then the 8 up values of the same features (interleave 8, the layout the fused product kernels want)
 template <typename A>
-__global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t total) {
+__global__ void swiglu_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t total, int interleave) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t row = idx / F;
     const int col = (int) (idx - row * F);
-    const float g = to_f32(gate_up[row * 2 * F + col]);
-    const float u = to_f32(gate_up[row * 2 * F + F + col]);
+    const size_t gi = interleave ? row * 2 * F + (size_t) (col / 8) * 16 + col % 8 : row * 2 * F + col;
+    const size_t ui = interleave ? gi + 8 : gi + F;
+    const float g = to_f32(gate_up[gi]);
+    const float u = to_f32(gate_up[ui]);
     const float s = g / (1.0f + expf(-g));
     out[idx] = from_f32<A>(s * u);
 }
 
 // 8 elements per thread with 16-byte (bf16) or 2 x 16-byte (f32) accesses; needs F % 8 == 0
 template <typename A>
-__global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t groups) {
+__global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict__ out, int F, size_t groups, int interleave) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t gidx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
@@ -161,8 +165,8 @@ __global__ void swiglu_vec_kernel(const A * __restrict__ gate_up, A * __restrict
     const int per_row = F >> 3;
     const size_t row = gidx / per_row;
     const int col = (int) (gidx - row * per_row) << 3;
-    const A * g = gate_up + row * 2 * F + col;
-    const A * u = g + F;
+    const A * g = gate_up + row * 2 * F + (interleave ? 2 * col : col);
+    const A * u = g + (interleave ? 8 : F);
     A * o = out + row * F + col;
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -242,19 +246,20 @@ IIAN_API int iian_rms_norm(const void * x, const float * weight, void * out, int
     return iian_launch_status();
 }
 
-IIAN_API int iian_swiglu(const void * gate_up, void * out, int act_dtype, int N, int F, cudaStream_t stream) {
+IIAN_API int iian_swiglu(const void * gate_up, void * out, int act_dtype, int N, int F, int interleave, cudaStream_t stream) {
+    if (interleave != 0 && (interleave != 8 || F % 8 != 0)) return IIAN_ERR_SHAPE;
     const size_t total = (size_t) N * F;
     if (total == 0) return IIAN_OK;
     const int threads = 256;
     if (F % 8 == 0 && ((uintptr_t) gate_up & 15) == 0 && ((uintptr_t) out & 15) == 0 && (act_dtype == IIAN_F32 || act_dtype == IIAN_BF16)) {
         const size_t groups = total / 8;
         const unsigned vblocks = (unsigned) ((groups + threads - 1) / threads);
-        if (act_dtype == IIAN_F32) return iian_launch(swiglu_vec_kernel<float>, dim3(vblocks), dim3(threads), 0, stream, (const float *) gate_up, (float *) out, F, groups);
-        return iian_launch(swiglu_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, groups);
+        if (act_dtype == IIAN_F32) return iian_launch(swiglu_vec_kernel<float>, dim3(vblocks), dim3(threads), 0, stream, (const float *) gate_up, (float *) out, F, groups, interleave);
+        return iian_launch(swiglu_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, groups, interleave);
     }
     const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
-    if (act_dtype == IIAN_F32) return iian_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) gate_up, (float *) out, F, total);
-    if (act_dtype == IIAN_BF16) return iian_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, total);
+    if (act_dtype == IIAN_F32) return iian_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) gate_up, (float *) out, F, total, interleave);
+    if (act_dtype == IIAN_BF16) return iian_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) gate_up, (__nv_bfloat16 *) out, F, total, interleave);
     return IIAN_ERR_DTYPE;
 }
 

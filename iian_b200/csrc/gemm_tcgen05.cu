@@ -10,10 +10,11 @@
 // epilogue: a plain store, or SiLU(gate) * up for a gate|up matrix whose rows are interleaved in groups
 // of 8 (gate rows 16j..16j+7, up rows 16j+8..16j+15 hold the same 8 features).
 //
-// Tile: 128 rows x BN columns (BN = 128 or 256) per CTA, K in blocks of 64 (one 128-byte swizzle
-// atom), STAGES shared-memory stages.  Roles: warp 0 lane 0 issues TMA loads; warp 1 allocates tensor
-// memory and its lane 0 issues the MMAs (4 per K block, K = 16 each) and commits; warps 2..5 read the
-// accumulator (tcgen05.ld, 32 lanes each), convert and store.
+// Tile: 128 rows x BN columns (BN = 128 or 256), K in blocks of 64 (one 128-byte swizzle atom), STAGES
+// shared-memory stages; one persistent CTA per SM walks the tiles.  Roles: warp 0 lane 0 issues TMA
+// loads; warp 1 allocates tensor memory (two accumulators) and its lane 0 issues the MMAs (4 per K
+// block, K = 16 each) and commits; warps 2..5 read an accumulator (tcgen05.ld, 32 lanes each), convert
+// and store while the next tile is already being multiplied into the other accumulator.
 //
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter records where it gave up in
 // `status`, and every role falls through to the common exit, where tensor memory is freed.  A kernel
@@ -97,6 +98,70 @@ __host__ __device__ constexpr unsigned instr_desc_bf16(int m, int n) {
          | ((unsigned) (m >> 4) << 24);   // M / 16
 }
 
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// One accumulator tile (128 x BN, float32, in tensor memory) -> global memory.  `r` holds 32 consecutive
+// columns of this thread's row.
+template <int EPI, typename OutT>
+__device__ __forceinline__ void epilogue_store32(const unsigned * r, OutT * __restrict__ out, int row, int col0, int N, int ldo) {
+    if (EPI == EPI_STORE) {
+        OutT * dst = out + (size_t) row * ldo + col0;
+        if (col0 + 32 <= N && (((uintptr_t) dst) & 15) == 0) {
+            if (sizeof(OutT) == 2) {
+#pragma unroll
+                for (int v = 0; v < 4; v++) {
+                    uint4 pk;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                    pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+                    pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+                    *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(dst) + 8 * v) = pk;
+                }
+            } else {
+#pragma unroll
+                for (int v = 0; v < 8; v++)
+                    *reinterpret_cast<uint4 *>(reinterpret_cast<float *>(dst) + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            }
+        } else {
+            for (int i = 0; i < 32; i++)
+                if (col0 + i < N) dst[i] = from_f32<OutT>(__uint_as_float(r[i]));
+        }
+    } else {
+        // columns come in groups of 16: 8 gate values, then the 8 up values of the same features; the
+        // output has N / 2 columns
+        OutT * dst = out + (size_t) row * ldo + col0 / 2;
+#pragma unroll
+        for (int grp = 0; grp < 2; grp++) {
+            float a[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float g = __uint_as_float(r[16 * grp + i]), u = __uint_as_float(r[16 * grp + 8 + i]);
+                a[i] = g / (1.0f + __expf(-g)) * u;
+            }
+            if (col0 + 16 * grp + 16 <= N) {
+                if (sizeof(OutT) == 2 && (((uintptr_t) (dst + 8 * grp)) & 15) == 0) {
+                    uint4 pk;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
+                    pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+                    pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+                    *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(dst) + 8 * grp) = pk;
+                } else {
+                    for (int i = 0; i < 8; i++) dst[8 * grp + i] = from_f32<OutT>(a[i]);
+                }
+            }
+        }
+    }
+}
+
+// Persistent: gridDim.x CTAs (one per SM) walk the output tiles round-robin, row tiles fastest, so the
+// CTAs that run together share a few weight tiles (read from HBM once, then from L2) and sweep the
+// activations, which stay in L2 as a whole.  Tensor memory holds two accumulators: while the epilogue
+// warps drain one, the MMA thread already fills the other with the next tile.
 template <int BN, int STAGES, int EPI, typename OutT>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -105,22 +170,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
     // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
     unsigned char * smem = (unsigned char *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    constexpr unsigned TMEM_COLS = 2 * BN;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_base_s;
     __shared__ int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (T + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const int num_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(smem_addr(&full_bar[s]), 1); mbar_init(smem_addr(&empty_bar[s]), 1); }
-        mbar_init(smem_addr(&acc_bar), 1);
+        for (int b = 0; b < 2; b++) { mbar_init(smem_addr(&acc_full[b]), 1); mbar_init(smem_addr(&acc_empty[b]), 4); }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {          // tensor memory: BN columns of 128 lanes x 32 bits
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"((unsigned) BN) : "memory");
+    if (warp == 1) {          // tensor memory: two accumulators of BN columns (128 lanes x 32 bits each)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -129,108 +196,78 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
     const unsigned tmem_base = tmem_base_s;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer ---------------------------------------------------------------------------
-        for (int kb = 0; kb < num_kb; kb++) {
-            const int s = kb % STAGES;
-            const unsigned phase = (kb / STAGES) & 1;
-            if (!mbar_wait(smem_addr(&empty_bar[s]), phase ^ 1)) { status->code = 1; status->where = kb; failed = 1; break; }
-            const unsigned bar = smem_addr(&full_bar[s]);
-            mbar_expect_tx(bar, STAGE_BYTES);
-            tma_load_2d(smem_addr(smem + s * STAGE_BYTES), &map_a, kb * TC_BK, m0, bar);
-            tma_load_2d(smem_addr(smem + s * STAGE_BYTES + A_BYTES), &map_b, kb * TC_BK, n0, bar);
+        // ---- producer: the stage ring runs on across tiles -------------------------------------------
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            for (int kb = 0; kb < num_kb; kb++, it++) {
+                const int s = it % STAGES;
+                const unsigned phase = (it / STAGES) & 1;
+                if (!mbar_wait(smem_addr(&empty_bar[s]), phase ^ 1)) { status->code = 1; status->where = it; failed = 1; goto done; }
+                const unsigned bar = smem_addr(&full_bar[s]);
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(smem_addr(smem + s * STAGE_BYTES), &map_a, kb * TC_BK, m0, bar);
+                tma_load_2d(smem_addr(smem + s * STAGE_BYTES + A_BYTES), &map_b, kb * TC_BK, n0, bar);
+            }
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer -------------------------------------------------------------------------
+        // ---- MMA issuer -----------------------------------------------------------------------------
         constexpr unsigned idesc = instr_desc_bf16(TC_BM, BN);
-        bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; kb++) {
-            const int s = kb % STAGES;
-            const unsigned phase = (kb / STAGES) & 1;
-            if (!mbar_wait(smem_addr(&full_bar[s]), phase)) { status->code = 2; status->where = kb; failed = 1; ok = false; break; }
+        int it = 0, use = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, use++) {
+            const int buf = use & 1;
+            const unsigned acc_phase = (use >> 1) & 1;
+            if (!mbar_wait(smem_addr(&acc_empty[buf]), acc_phase ^ 1)) { status->code = 4; status->where = use; failed = 1; goto done; }
             tc_fence_after();
-            const unsigned long long da = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES));
-            const unsigned long long db = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + A_BYTES));
+            const unsigned d_tmem = tmem_base + (unsigned) (buf * BN);
+            for (int kb = 0; kb < num_kb; kb++, it++) {
+                const int s = it % STAGES;
+                const unsigned phase = (it / STAGES) & 1;
+                if (!mbar_wait(smem_addr(&full_bar[s]), phase)) { status->code = 2; status->where = it; failed = 1; goto done; }
+                tc_fence_after();
+                const unsigned long long da = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES));
+                const unsigned long long db = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + A_BYTES));
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; k++)          // 32 bytes further along K per step, inside the swizzle atom
-                tc_mma(tmem_base, da + (unsigned long long) (k * 2), db + (unsigned long long) (k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            tc_commit(smem_addr(&empty_bar[s]));          // the stage is free once these MMAs have read it
+                for (int k = 0; k < TC_BK / 16; k++)      // 32 bytes further along K per step, inside the swizzle atom
+                    tc_mma(d_tmem, da + (unsigned long long) (k * 2), db + (unsigned long long) (k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tc_commit(smem_addr(&empty_bar[s]));      // the stage is free once these MMAs have read it
+            }
+            tc_commit(smem_addr(&acc_full[buf]));         // this accumulator is complete
         }
-        tc_commit(smem_addr(&acc_bar));                   // the accumulator is complete (or nothing was issued)
     } else if (warp >= 2) {
-        // ---- epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 -------------------------
+        // ---- epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 ----------------------------
         const int q = warp & 3;
-        const bool ok = mbar_wait(smem_addr(&acc_bar), 0);
-        if (!ok) { if (lane == 0) { status->code = 3; status->where = warp; } failed = 1; }
-        tc_fence_after();
-        const int row = m0 + q * 32 + lane;
-        if (ok) {
+        int use = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, use++) {
+            const int buf = use & 1;
+            const unsigned acc_phase = (use >> 1) & 1;
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            if (!mbar_wait(smem_addr(&acc_full[buf]), acc_phase)) {
+                if (lane == 0) { status->code = 3; status->where = use; }
+                failed = 1;
+                break;
+            }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned r[32];
-                tc_ld32(tmem_base + ((unsigned) (q * 32) << 16) + (unsigned) c0, r);
+                tc_ld32(tmem_base + ((unsigned) (q * 32) << 16) + (unsigned) (buf * BN + c0), r);
                 tc_wait_ld();
-                if (failed || row >= T) continue;
-                if (EPI == EPI_STORE) {
-                    const int col = n0 + c0;
-                    OutT * dst = out + (size_t) row * ldo + col;
-                    if (col + 32 <= N && (((uintptr_t) dst) & 15) == 0) {
-                        if (sizeof(OutT) == 2) {
-#pragma unroll
-                            for (int v = 0; v < 4; v++) {
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                                pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
-                                pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
-                                *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(dst) + 8 * v) = pk;
-                            }
-                        } else {
-#pragma unroll
-                            for (int v = 0; v < 8; v++)
-                                *reinterpret_cast<uint4 *>(reinterpret_cast<float *>(dst) + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32; i++)
-                            if (col + i < N) dst[i] = from_f32<OutT>(__uint_as_float(r[i]));
-                    }
-                } else {
-                    // columns come in groups of 16: 8 gate values, then the 8 up values of the same features;
-                    // the output has N / 2 columns
-                    const int fcol = (n0 + c0) / 2;
-                    OutT * dst = out + (size_t) row * ldo + fcol;
-#pragma unroll
-                    for (int grp = 0; grp < 2; grp++) {
-                        float a[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const float g = __uint_as_float(r[16 * grp + i]), u = __uint_as_float(r[16 * grp + 8 + i]);
-                            a[i] = g / (1.0f + __expf(-g)) * u;
-                        }
-                        if (n0 + c0 + 16 * grp + 16 <= N) {
-                            if (sizeof(OutT) == 2 && (((uintptr_t) (dst + 8 * grp)) & 15) == 0) {
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
-                                pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
-                                pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
-                                *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(dst) + 8 * grp) = pk;
-                            } else {
-                                for (int i = 0; i < 8; i++) dst[8 * grp + i] = from_f32<OutT>(a[i]);
-                            }
-                        }
-                    }
-                }
+                if (row < T) epilogue_store32<EPI, OutT>(r, out, row, n0 + c0, N, ldo);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_addr(&acc_empty[buf]));     // four arrivals free the accumulator
         }
     }
+done:
     // ---- common exit: everybody arrives here, also after a wait that gave up -------------------------
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned) BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -273,7 +310,13 @@ static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out,
         if (e != cudaSuccess) return 1000 + (int) e;
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (T + TC_BM - 1) / TC_BM);
+    const int tiles = ((T + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    dim3 grid(tiles < sms ? tiles : sms);
     gemm_tcgen05_kernel<BN, STAGES, EPI, OutT><<<grid, TC_THREADS, smem, stream>>>(ma, mb, (OutT *) out, T, N, K, ldo, status);
     return iian_launch_status();
 }

@@ -134,13 +134,14 @@ class CudaKernels:
         _check(fn(_cuda(x, "rms_norm in"), _cuda(weight, "norm weight", torch.float32), _cuda(out, "rms_norm out"),
                   _code(x, "rms_norm in"), n, h, eps, _stream()), "rms_norm")
 
-    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
+        """``interleave`` 0: columns are [gate | up]; 8: groups of 16 columns, 8 gate then 8 up values."""
         n, f2 = gate_up.shape
         if out.shape != (n, f2 // 2) or f2 % 2 or out.dtype != gate_up.dtype:
             raise KernelError("swiglu: out must be [N, F] for gate_up [N, 2F] of the same dtype")
-        fn = _fn("elementwise", "iian_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-        _check(fn(_cuda(gate_up, "gate_up"), _cuda(out, "swiglu out"), _code(out, "swiglu out"), n, f2 // 2, _stream()),
-               "swiglu")
+        fn = _fn("elementwise", "iian_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(gate_up, "gate_up"), _cuda(out, "swiglu out"), _code(out, "swiglu out"), n, f2 // 2, interleave,
+                  _stream()), "swiglu")
 
     def gather_rows(self, src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         r, h = out.shape
@@ -177,8 +178,29 @@ class CudaKernels:
     weight_log = None          # a list while the order of weight-streaming products is being recorded
     prefetcher = None          # a WeightPrefetcher while a decode graph is being captured
 
+    # rows from which the tcgen05 kernel takes over (below it, and above the streaming kernel's range, the
+    # library GEMM is faster: one row tile of 128 leaves most SMs without work)
+    TCGEN05_MIN_ROWS = 128
+    LIBRARY_GEMM_ONLY = os.environ.get("IIAN_LIBRARY_GEMM", "0") not in ("0", "false", "off")
+
+    def _tcgen05_ok(self, x, w, n, k) -> bool:
+        return (not self.LIBRARY_GEMM_ONLY and n >= self.TCGEN05_MIN_ROWS and k % 8 == 0
+                and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def can_fuse_swiglu(self, x: torch.Tensor, w: torch.Tensor, interleave: int) -> bool:
+        """Whether ``linear_swiglu`` can run for these operands (else: linear, then swiglu)."""
+        return interleave == 8 and w.shape[0] % 16 == 0 and self._tcgen05_ok(x, w, x.shape[0], x.shape[1])
+
+    def linear_swiglu(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t, f] = silu(x . w_gate_f) * (x . w_up_f) for w with gate and up rows interleaved in groups of 8."""
+        self.gemm_tcgen05(x, w, out, epilogue=1)
+
     def _linear_dispatch(self, x, w, out, n, m, k) -> None:
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if self._tcgen05_ok(x, w, n, k):
+                self.gemm_tcgen05(x, w, out)
+                return
             if n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
                 self.gemm_skinny(x, w, out)
                 if self.weight_log is not None:

@@ -2,7 +2,10 @@
 (src/iian/graph.cpp:116-163 with ``FfnOp::SILU`` / ``FfnGate::PAR``, src/iian/arch/qwen3.cpp:97).
 ``silu(z) = z / (1 + exp(-z))`` (third_party/ggml/src/ggml-cpu/vec.h:1046-1048).
 
-Gate and up projections run as one matrix product over the rows ``Wgate | Wup`` stacked at load time.
+Gate and up projections run as one matrix product over the rows of both, stacked at load time in groups of
+8 (8 gate rows, then the 8 up rows of the same features, ...), so that a product kernel that owns 16
+consecutive rows holds both halves of 8 features and can apply SiLU(gate) * up in its epilogue.  If the
+intermediate size is no multiple of 8 the rows are stacked as ``Wgate | Wup``.
 """
 from __future__ import annotations
 
@@ -27,6 +30,7 @@ class GatedMLP(FeedForward):
         if act != "silu":
             raise ValueError(f"gated_mlp: activation '{act}' has no kernel (silu only)")
         self.w_gate_up = self.w_down = None
+        self.interleave = 0
 
     def tensors(self) -> Dict[str, TensorSpec]:
         return {
@@ -39,7 +43,14 @@ class GatedMLP(FeedForward):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        if self.inter % 8 == 0:
+            k = g.shape[1]
+            self.w_gate_up = torch.stack([g.view(self.inter // 8, 8, k), u.view(self.inter // 8, 8, k)], dim=1) \
+                .reshape(2 * self.inter, k).contiguous()
+            self.interleave = 8
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+            self.interleave = 0
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def kernel_libraries(self):
@@ -48,10 +59,13 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         k = ops.kernels()
         n = x.shape[0]
-        gate_up = ctx.buf("gate_up", (n, 2 * self.inter), self.dtype)
-        k.linear(x, self.w_gate_up, gate_up)
         act = ctx.buf("ffn_act", (n, self.inter), self.dtype)
-        k.swiglu(gate_up, act)
+        if hasattr(k, "can_fuse_swiglu") and k.can_fuse_swiglu(x, self.w_gate_up, self.interleave):
+            k.linear_swiglu(x, self.w_gate_up, act)            # the activation rides in the product's epilogue
+        else:
+            gate_up = ctx.buf("gate_up", (n, 2 * self.inter), self.dtype)
+            k.linear(x, self.w_gate_up, gate_up)
+            k.swiglu(gate_up, act, self.interleave)
         out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
         k.linear(act, self.w_down, out)
         return out

@@ -31,9 +31,13 @@ class FakeKernels:
         xf = x.float()
         out.copy_((xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
 
-    def swiglu(self, gate_up, out):
+    def swiglu(self, gate_up, out, interleave=0):
         f = out.shape[1]
-        g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
+        if interleave:
+            v = gate_up.float().view(gate_up.shape[0], f // 8, 2, 8)
+            g, u = v[:, :, 0].reshape(-1, f), v[:, :, 1].reshape(-1, f)
+        else:
+            g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
         out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
     def gather_rows(self, src, rows, out):

@@ -70,6 +70,13 @@ def test_rms_norm_and_swiglu_and_gather_and_bias(dtype):
     want = plain.silu(g) * u
     assert (act.double().cpu() - want).abs().max() < tol(dtype, want.abs().max().item())
 
+    gu8 = rnd(5, 2 * 80, dtype=dtype, seed=16, std=2.0)
+    act8 = torch.empty(5, 80, dtype=dtype).cuda()
+    K().swiglu(gu8, act8, interleave=8)
+    v = gu8.double().cpu().view(5, 10, 2, 8)
+    want = plain.silu(v[:, :, 0].reshape(5, 80)) * v[:, :, 1].reshape(5, 80)
+    assert (act8.double().cpu() - want).abs().max() < tol(dtype, want.abs().max().item())
+
     rows = torch.tensor([6, 0, 3], dtype=torch.int32).cuda()
     sel = torch.empty(3, 130, dtype=dtype).cuda()
     K().gather_rows(x, rows, sel)
