@@ -33,7 +33,10 @@ __device__ __forceinline__ void mma_bf16_16816(float * c, unsigned a0, unsigned 
 // NT: 8-column tiles of the batch; MT: 16-row tiles of weights per block (they share the activation
 // fragments); WARPS: how many warps split K; UNROLL: 32-wide k chunks whose weight loads are issued
 // before the first of them is used.
-template <int NT, int MT, int WARPS, int UNROLL, typename OutT>
+// EPI 0: store the products.  EPI 1: the weight rows hold gate and up projections interleaved in groups of
+// 8 (rows 16j..16j+7 gate, 16j+8..16j+15 up, same 8 features); the kernel stores silu(gate) * up, half as
+// many columns (src/iian/graph.cpp:135).
+template <int NT, int MT, int WARPS, int UNROLL, int EPI, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     const __nv_bfloat16 * __restrict__ x, const __nv_bfloat16 * __restrict__ w, OutT * __restrict__ out,
     int B, int M, int K, float * __restrict__ part, int * __restrict__ counters) {
@@ -140,6 +143,19 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     __syncthreads();
     constexpr int ROWS = MT * 16;
     constexpr int CELLS = ROWS * NT * 8;
+    if (EPI == 1) {                                  // (ksplit is 1 here)
+        for (int idx = threadIdx.x; idx < CELLS / 2; idx += blockDim.x) {
+            const int n = idx / (ROWS / 2), f = idx % (ROWS / 2);
+            const int r = (f / 8) * 16 + f % 8;      // gate row; its up row is 8 further
+            const int m = m0 + r;
+            if (n >= B || m + 8 >= M) continue;
+            float g = 0.0f, u = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < WARPS; wv++) { g += red[wv][r][n]; u += red[wv][r + 8][n]; }
+            out[(size_t) n * (M / 2) + (m0 / 2 + f)] = from_f32<OutT>(g / (1.0f + expf(-g)) * u);
+        }
+        return;
+    }
     if (ksplit == 1) {
         for (int idx = threadIdx.x; idx < CELLS; idx += blockDim.x) {
             const int n = idx / ROWS, r = idx % ROWS;
@@ -180,7 +196,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(
     if (threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 
-template <int NT, int MT, int WARPS, int UNROLL, typename OutT>
+template <int NT, int MT, int WARPS, int UNROLL, int EPI, typename OutT>
 static int launch_cfg(const void * x, const void * w, void * out, int B, int M, int K, int ksplit, float * part,
                       int * counters, cudaStream_t stream) {
     const unsigned blocks = (unsigned) ((M + 16 * MT - 1) / (16 * MT));
@@ -188,18 +204,18 @@ static int launch_cfg(const void * x, const void * w, void * out, int B, int M, 
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT>,
+            cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, EPI, OutT>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
             if (e != cudaSuccess) return 1000 + (int) e;
             configured = true;
         }
     }
-    return iian_launch(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, OutT>, dim3(blocks, ksplit), dim3(WARPS * 32), smem, stream,
+    return iian_launch(gemm_skinny_kernel<NT, MT, WARPS, UNROLL, EPI, OutT>, dim3(blocks, ksplit), dim3(WARPS * 32), smem, stream,
                        (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K, part, counters);
 }
 
 // cfg = MT * 100 + WARPS * 10 + UNROLL; 0 = the default for this (B, M)
-template <int NT, typename OutT>
+template <int NT, int EPI, typename OutT>
 static int launch_nt(const void * x, const void * w, void * out, int B, int M, int K, int cfg, int ksplit, float * part,
                      int * counters, cudaStream_t stream) {
     if (cfg == 0) {
@@ -209,27 +225,28 @@ static int launch_nt(const void * x, const void * w, void * out, int B, int M, i
     }
     if (NT == 1) {
         switch (cfg) {
-            case 184: return launch_cfg<1, 1, 8, 4, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
-            case 188: return launch_cfg<1, 1, 8, 8, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
-            case 144: return launch_cfg<1, 1, 4, 4, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
-            case 148: return launch_cfg<1, 1, 4, 8, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 184: return launch_cfg<1, 1, 8, 4, EPI, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 188: return launch_cfg<1, 1, 8, 8, EPI, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 144: return launch_cfg<1, 1, 4, 4, EPI, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+            case 148: return launch_cfg<1, 1, 4, 8, EPI, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
         }
         return IIAN_ERR_SHAPE;
     }
     switch (cfg) {
-        case 284: return launch_cfg<NT, 2, 8, 4, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
-        case 282: return launch_cfg<NT, 2, 8, 2, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+        case 284: return launch_cfg<NT, 2, 8, 4, EPI, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
+        case 282: return launch_cfg<NT, 2, 8, 2, EPI, OutT>(x, w, out, B, M, K, ksplit, part, counters, stream);
     }
     return IIAN_ERR_SHAPE;
 }
 
-template <typename OutT>
+template <int EPI, typename OutT>
 static int launch_skinny(const void * x, const void * w, void * out, int B, int M, int K, int cfg, int ksplit, float * part,
                          int * counters, cudaStream_t stream) {
-    if (B <= 8) return launch_nt<1, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
-    if (B <= 16) return launch_nt<2, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
-    if (B <= 32) return launch_nt<4, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
-    return launch_nt<8, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (B <= 8) return launch_nt<1, EPI, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (EPI != 0) return IIAN_ERR_LIMIT;          // the fused epilogue is built for up to 8 rows
+    if (B <= 16) return launch_nt<2, 0, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (B <= 32) return launch_nt<4, 0, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    return launch_nt<8, 0, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
 }
 
 }  // namespace iian
@@ -241,21 +258,27 @@ using namespace iian;
 // (MT * 100 + WARPS * 10 + UNROLL); 0 takes the default.  ksplit > 1 cuts K over that many CTAs per row
 // block and needs scratch: part = ceil(M / rows per block) * ksplit * (rows per block * 8 * ceil(B / 8))
 // floats and counters = ceil(M / rows per block) ints that are zero before the first launch (the kernel
-// leaves them zero).
+// leaves them zero).  epilogue 1 stores silu(gate) * up for gate/up rows interleaved in groups of 8 (out is
+// [B, M / 2] bf16; up to 8 rows, no split).
 IIAN_API int iian_gemm_skinny_cfg(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
-                                  int cfg, int ksplit, float * part, int * counters, cudaStream_t stream) {
+                                  int cfg, int ksplit, float * part, int * counters, int epilogue, cudaStream_t stream) {
     if (B <= 0 || M <= 0) return IIAN_OK;
     if (B > 64) return IIAN_ERR_LIMIT;
     if (K <= 0 || K % 32 != 0) return IIAN_ERR_SHAPE;
     if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
     if (ksplit < 1 || ksplit > 64 || ksplit > K / 32) return IIAN_ERR_SHAPE;
     if (ksplit > 1 && (part == nullptr || counters == nullptr)) return IIAN_ERR_SHAPE;
-    if (out_dtype == IIAN_BF16) return launch_skinny<__nv_bfloat16>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
-    if (out_dtype == IIAN_F32) return launch_skinny<float>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (epilogue == 1) {
+        if (M % 16 != 0 || ksplit != 1 || out_dtype != IIAN_BF16) return IIAN_ERR_SHAPE;
+        return launch_skinny<1, __nv_bfloat16>(x, w, out, B, M, K, cfg, 1, nullptr, nullptr, stream);
+    }
+    if (epilogue != 0) return IIAN_ERR_SHAPE;
+    if (out_dtype == IIAN_BF16) return launch_skinny<0, __nv_bfloat16>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
+    if (out_dtype == IIAN_F32) return launch_skinny<0, float>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
     return IIAN_ERR_DTYPE;
 }
 
 IIAN_API int iian_gemm_skinny(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
                               cudaStream_t stream) {
-    return iian_gemm_skinny_cfg(x, w, out, out_dtype, B, M, K, 0, 1, nullptr, nullptr, stream);
+    return iian_gemm_skinny_cfg(x, w, out, out_dtype, B, M, K, 0, 1, nullptr, nullptr, 0, stream);
 }

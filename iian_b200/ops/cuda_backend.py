@@ -188,13 +188,26 @@ class CudaKernels:
                 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
+    def _skinny_ok(self, x, w, n, k) -> bool:
+        return (n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
     def can_fuse_swiglu(self, x: torch.Tensor, w: torch.Tensor, interleave: int) -> bool:
         """Whether ``linear_swiglu`` can run for these operands (else: linear, then swiglu)."""
-        return interleave == 8 and w.shape[0] % 16 == 0 and self._tcgen05_ok(x, w, x.shape[0], x.shape[1])
+        n, k = x.shape
+        return interleave == 8 and w.shape[0] % 16 == 0 and (self._tcgen05_ok(x, w, n, k) or self._skinny_ok(x, w, n, k))
 
     def linear_swiglu(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         """out[t, f] = silu(x . w_gate_f) * (x . w_up_f) for w with gate and up rows interleaved in groups of 8."""
-        self.gemm_tcgen05(x, w, out, epilogue=1)
+        n, k = x.shape
+        if self._tcgen05_ok(x, w, n, k):
+            self.gemm_tcgen05(x, w, out, epilogue=1)
+            return
+        self.gemm_skinny(x, w, out, epilogue=1)
+        if self.weight_log is not None:
+            self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
+        if self.prefetcher is not None:
+            self.prefetcher.after_product(self)
 
     def _linear_dispatch(self, x, w, out, n, m, k) -> None:
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
@@ -232,7 +245,8 @@ class CudaKernels:
         memory pipeline idle (a row block of 16 is one CTA)."""
         return 1       # measured on B200 at the Qwen3-8B sizes: one CTA per row block is fastest for every shape
 
-    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0, ksplit: int = 0) -> None:
+    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0, ksplit: int = 0,
+                    epilogue: int = 0) -> None:
         """``cfg`` picks a tile configuration (rows-per-block tiles * 100 + warps * 10 + unroll); ``ksplit``
         the number of CTAs that share K for one row block; 0: defaults."""
         n, k = x.shape
@@ -240,7 +254,7 @@ class CudaKernels:
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: x and w must be bfloat16")
         if ksplit <= 0:
-            ksplit = self.skinny_ksplit(n, m, k)
+            ksplit = 1 if epilogue else self.skinny_ksplit(n, m, k)
         part = counters = 0
         if ksplit > 1:
             rows = 32 if n > 8 else 16
@@ -249,9 +263,9 @@ class CudaKernels:
             part = self.gemm_scratch(x.device, blocks * ksplit * rows * 8 * nt).data_ptr()
             counters = self.gemm_counters(x.device, blocks).data_ptr()
         fn = _fn("gemm_skinny", "iian_gemm_skinny_cfg",
-                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
         _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
-                  n, m, k, cfg, ksplit, part, counters, _stream()), "gemm_skinny")
+                  n, m, k, cfg, ksplit, part, counters, epilogue, _stream()), "gemm_skinny")
 
     _gemm_scratch = {}
     _gemm_counters = {}

@@ -328,6 +328,18 @@ def test_gemm_skinny_split_k(ksplit, B, M, K_):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
 
 
+@pytest.mark.parametrize("B,F,K_", [(1, 16, 64), (8, 160, 96), (5, 12288, 4096)])
+def test_gemm_skinny_swiglu_epilogue(B, F, K_):
+    x = rnd(B, K_, dtype=torch.bfloat16, seed=40)
+    wg, wu = rnd(F, K_, dtype=torch.bfloat16, seed=41, std=0.05), rnd(F, K_, dtype=torch.bfloat16, seed=42, std=0.05)
+    inter = torch.stack([wg.view(F // 8, 8, K_), wu.view(F // 8, 8, K_)], dim=1).reshape(2 * F, K_).contiguous()
+    out = torch.full((B, F), float("nan"), dtype=torch.bfloat16).cuda()
+    K().gemm_skinny(x, inter, out, epilogue=1)
+    xd = x.double().cpu()
+    want = plain.silu(xd @ wg.double().cpu().T) * (xd @ wu.double().cpu().T)
+    assert (out.double().cpu() - want).abs().max() < tol(torch.bfloat16, max(1.0, want.abs().max().item()))
+
+
 def test_gemm_skinny_rows_do_not_depend_on_the_batch():
     """Within the row counts the engine uses it for (up to 8), a row's result is the same bits whatever
     else is in the batch: the split of K over warps and the order of the final sum are fixed."""
