@@ -1,6 +1,5 @@
 // Fused per-head RMSNorm of Q and K, rotary position encoding, and the write of K and V into
-// the paged cache.  One block per token; its warps share the heads of the concatenated projection
-// output Q | K | V.
+// the paged cache.  One warp per (token, head) of the concatenated projection output Q | K | V.
 //
 // Reference order (src/iian/arch/qwen3.cpp:80-87): norm over the head axis with one weight
 // [head_dim] shared by all heads, then rotation; V is stored untouched.  Rotation, NEOX pairing
@@ -17,19 +16,119 @@
 namespace iian {
 
 constexpr int kMaxHeadDim = 512;
-constexpr int kWarpsPerBlock = 8;
+constexpr int kWarpsPerBlock = 4;
 
 
-// One block per token; its warps take the heads in turn.  A lane owns rotation pairs p = lane, lane + 32,
-// ...: elements (p, p + half) in NEOX style, (2p, 2p + 1) interleaved, and beyond the rotated part single
-// elements.  Both members of a pair sit in the same lane, so the rotation needs no exchange, and the
-// sines and cosines of a token are computed once per warp and reused for every head.
+// cos and sin of pos * inv_freq[p] for every token of the step and every rotation pair: computed once per
+// step and shared by all layers that rotate alike (the angles do not depend on the layer).
+__global__ void rotary_table_kernel(const float * __restrict__ inv_freq, const int * __restrict__ positions,
+                                    float2 * __restrict__ table, int half, long long total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long idx = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int t = (int) (idx / half), p = (int) (idx % half);
+    float sn, cs;
+    sincosf((float) positions[t] * inv_freq[p], &sn, &cs);
+    table[idx] = make_float2(cs, sn);
+}
+
+template <typename A> struct Pair;
+template <> struct Pair<float> {
+    static __device__ __forceinline__ float2 load(const float * p) { return *reinterpret_cast<const float2 *>(p); }
+    static __device__ __forceinline__ void store(float * p, float2 v) { *reinterpret_cast<float2 *>(p) = v; }
+};
+template <> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 load(const __nv_bfloat16 * p) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 * p, float2 v) {
+        *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(v.x, v.y);
+    }
+};
+
+// Fast form: one warp per (token, head); NEOX pairs over the whole head (or no rotation), head size a
+// multiple of 4, angles from the table.  A lane owns two adjacent pairs at a time, i.e. two adjacent
+// elements in each half of the head, so every access is a 2-element vector.
+template <typename A>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_fast_kernel(
+    const A * __restrict__ qkv, A * __restrict__ q_out, A * __restrict__ k_cache, A * __restrict__ v_cache,
+    const float * __restrict__ q_weight, const float * __restrict__ k_weight, const float2 * __restrict__ table,
+    const int * __restrict__ slots, int N, int nh, int nkv, int hd, float eps, int page_size, int num_pages, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nh + 2 * nkv;
+    const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= (long long) N * heads_total) return;
+    const int t = (int) (item / heads_total);
+    const int h = (int) (item % heads_total);
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    if (!is_q && !write_kv) return;
+    const int slot = slots != nullptr ? slots[t] : -1;
+    if (!is_q && (slot < 0 || slot >= num_pages * page_size)) return;   // padding token: nothing to store
+    const A * src = qkv + (size_t) t * heads_total * hd + (size_t) h * hd;
+    A * dst;
+    if (is_q) {
+        dst = q_out + ((size_t) t * nh + h) * hd;
+    } else {
+        const int kvh = is_k ? h - nh : h - nh - nkv;
+        const int page = slot / page_size, off = slot % page_size;
+        A * base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t) page * nkv + kvh) * page_size + off) * hd;
+    }
+    const int half = hd >> 1;
+    const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    const bool rotate = (is_q || is_k) && table != nullptr;
+    constexpr int kIter = kMaxHeadDim / 128;       // a pass covers 64 pairs
+    float2 lo[kIter], hi[kIter];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kIter; k++) {
+        const int p0 = 2 * lane + 64 * k;
+        if (p0 < half) {
+            lo[k] = Pair<A>::load(src + p0);
+            hi[k] = Pair<A>::load(src + half + p0);
+            ss += lo[k].x * lo[k].x + lo[k].y * lo[k].y + hi[k].x * hi[k].x + hi[k].y * hi[k].y;
+        }
+    }
+    float inv = 1.0f;
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float) hd + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < kIter; k++) {
+        const int p0 = 2 * lane + 64 * k;
+        if (p0 < half) {
+            float2 a = lo[k], c = hi[k];
+            if (w != nullptr) {
+                const float2 wl = *reinterpret_cast<const float2 *>(w + p0), wh = *reinterpret_cast<const float2 *>(w + half + p0);
+                a.x = a.x * inv * wl.x; a.y = a.y * inv * wl.y;
+                c.x = c.x * inv * wh.x; c.y = c.y * inv * wh.y;
+            }
+            if (rotate) {
+                const float4 cssn = *reinterpret_cast<const float4 *>(table + (size_t) t * half + p0);   // cos0 sin0 cos1 sin1
+                const float2 r0 = make_float2(a.x * cssn.x - c.x * cssn.y, a.y * cssn.z - c.y * cssn.w);
+                const float2 r1 = make_float2(a.x * cssn.y + c.x * cssn.x, a.y * cssn.w + c.y * cssn.z);
+                a = r0; c = r1;
+            }
+            Pair<A>::store(dst + p0, a);
+            Pair<A>::store(dst + half + p0, c);
+        }
+    }
+}
+
+// General form: one warp per (token, head); any head size, partial rotation, either pairing style, bias.
+// A lane owns rotation pairs p = lane, lane + 32, ...: elements (p, p + half) in NEOX style, (2p, 2p + 1)
+// interleaved; beyond the rotated part it owns single elements.  Both members of a pair sit in the same
+// lane, so the rotation needs no exchange.
 template <typename A>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_kernel(
     const A * __restrict__ qkv, const float * __restrict__ bias,
     A * __restrict__ q_out, A * __restrict__ k_cache, A * __restrict__ v_cache,
     const float * __restrict__ q_weight, const float * __restrict__ k_weight,
-    const float * __restrict__ inv_freq, const int * __restrict__ positions,
+    const float * __restrict__ inv_freq, const float2 * __restrict__ table, const int * __restrict__ positions,
     const int * __restrict__ slots,
     int N, int nh, int nkv, int hd, int rot_dim, int rope_style, float eps,
     int page_size, int num_pages, int write_kv) {
@@ -37,93 +136,89 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_kernel
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nh + 2 * nkv;
-    const int t = blockIdx.x;
+    const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= (long long) N * heads_total) return;
+    const int t = (int) (item / heads_total);
+    const int h = (int) (item % heads_total);
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    if (!is_q && !write_kv) return;
     const int slot = slots != nullptr ? slots[t] : -1;
-    const bool store_kv = write_kv && slot >= 0 && slot < num_pages * page_size;   // a padding token stores nothing
+    if (!is_q && (slot < 0 || slot >= num_pages * page_size)) return;   // padding token: nothing to store
+
+    const A * src = qkv + (size_t) t * heads_total * hd + (size_t) h * hd;
+    const float * b = bias != nullptr ? bias + (size_t) h * hd : nullptr;
+    A * dst;
+    if (is_q) {
+        dst = q_out + ((size_t) t * nh + h) * hd;
+    } else {
+        const int kvh = is_k ? h - nh : h - nh - nkv;
+        const int page = slot / page_size, off = slot % page_size;
+        A * base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t) page * nkv + kvh) * page_size + off) * hd;
+    }
+    const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    const bool rotate = (is_q || is_k) && inv_freq != nullptr && rot_dim > 0;
+
+    if (w == nullptr && !rotate) {          // V (or an unnormalised, unrotated head): a copy
+        for (int i = lane; i < hd; i += 32) {
+            float v = to_f32(src[i]);
+            if (b != nullptr) v += b[i];
+            dst[i] = from_f32<A>(v);
+        }
+        return;
+    }
     constexpr int kMaxPairs = kMaxHeadDim / 64;      // per lane
-    const bool has_rope = inv_freq != nullptr && rot_dim > 0;
-    const int half = has_rope ? rot_dim / 2 : 0;
-    float cs[kMaxPairs], sn[kMaxPairs];
-    if (has_rope) {
-        const float pos = (float) positions[t];
+    const int half = rotate ? rot_dim / 2 : 0;
+    float x0[kMaxPairs], x1[kMaxPairs], tail[kMaxPairs * 2];
+    float ss = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kMaxPairs; k++) {
-            const int p = lane + 32 * k;
-            if (p < half) sincosf(pos * inv_freq[p], &sn[k], &cs[k]);
+    for (int k = 0; k < kMaxPairs; k++) {
+        const int p = lane + 32 * k;
+        if (p < half) {
+            const int i0 = rope_style == 0 ? p : 2 * p, i1 = rope_style == 0 ? p + half : 2 * p + 1;
+            float a0 = to_f32(src[i0]), a1 = to_f32(src[i1]);
+            if (b != nullptr) { a0 += b[i0]; a1 += b[i1]; }
+            x0[k] = a0; x1[k] = a1;
+            ss += a0 * a0 + a1 * a1;
         }
     }
-    for (int h = warp; h < heads_total; h += kWarpsPerBlock) {
-        const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
-        if (!is_q && !store_kv) continue;
-        const A * src = qkv + (size_t) t * heads_total * hd + (size_t) h * hd;
-        const float * b = bias != nullptr ? bias + (size_t) h * hd : nullptr;
-        A * dst;
-        if (is_q) {
-            dst = q_out + ((size_t) t * nh + h) * hd;
-        } else {
-            const int kvh = is_k ? h - nh : h - nh - nkv;
-            const int page = slot / page_size, off = slot % page_size;
-            A * base = is_k ? k_cache : v_cache;
-            dst = base + (((size_t) page * nkv + kvh) * page_size + off) * hd;
-        }
-        const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
-        const bool rotate = (is_q || is_k) && has_rope;
-        if (w == nullptr && !rotate) {          // V (or an unnormalised, unrotated head): a copy
-            for (int i = lane; i < hd; i += 32) {
-                float v = to_f32(src[i]);
-                if (b != nullptr) v += b[i];
-                dst[i] = from_f32<A>(v);
-            }
-            continue;
-        }
-        const int hr = rotate ? half : 0;
-        float x0[kMaxPairs], x1[kMaxPairs], tail[kMaxPairs * 2];
-        float ss = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kMaxPairs; k++) {
-            const int p = lane + 32 * k;
-            if (p < hr) {
-                const int i0 = rope_style == 0 ? p : 2 * p, i1 = rope_style == 0 ? p + hr : 2 * p + 1;
-                float a0 = to_f32(src[i0]), a1 = to_f32(src[i1]);
-                if (b != nullptr) { a0 += b[i0]; a1 += b[i1]; }
-                x0[k] = a0; x1[k] = a1;
-                ss += a0 * a0 + a1 * a1;
-            }
+    for (int k = 0; k < kMaxPairs * 2; k++) {
+        const int i = 2 * half + lane + 32 * k;
+        if (i < hd) {
+            float a = to_f32(src[i]);
+            if (b != nullptr) a += b[i];
+            tail[k] = a;
+            ss += a * a;
         }
+    }
+    float inv = 1.0f;
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float) hd + eps);
+    }
+    const float pos = rotate ? (float) positions[t] : 0.0f;
 #pragma unroll
-        for (int k = 0; k < kMaxPairs * 2; k++) {
-            const int i = 2 * hr + lane + 32 * k;
-            if (i < hd) {
-                float a = to_f32(src[i]);
-                if (b != nullptr) a += b[i];
-                tail[k] = a;
-                ss += a * a;
-            }
+    for (int k = 0; k < kMaxPairs; k++) {
+        const int p = lane + 32 * k;
+        if (p < half) {
+            const int i0 = rope_style == 0 ? p : 2 * p, i1 = rope_style == 0 ? p + half : 2 * p + 1;
+            float a0 = x0[k], a1 = x1[k];
+            if (w != nullptr) { a0 = a0 * inv * w[i0]; a1 = a1 * inv * w[i1]; }
+            float sn, cs;
+            if (table != nullptr) { const float2 e = table[(size_t) t * half + p]; cs = e.x; sn = e.y; }
+            else sincosf(pos * inv_freq[p], &sn, &cs);
+            dst[i0] = from_f32<A>(a0 * cs - a1 * sn);
+            dst[i1] = from_f32<A>(a0 * sn + a1 * cs);
         }
-        float inv = 1.0f;
-        if (w != nullptr) {
-            ss = warp_sum(ss);
-            inv = rsqrtf(ss / (float) hd + eps);
-        }
+    }
 #pragma unroll
-        for (int k = 0; k < kMaxPairs; k++) {
-            const int p = lane + 32 * k;
-            if (p < hr) {
-                const int i0 = rope_style == 0 ? p : 2 * p, i1 = rope_style == 0 ? p + hr : 2 * p + 1;
-                float a0 = x0[k], a1 = x1[k];
-                if (w != nullptr) { a0 = a0 * inv * w[i0]; a1 = a1 * inv * w[i1]; }
-                dst[i0] = from_f32<A>(a0 * cs[k] - a1 * sn[k]);
-                dst[i1] = from_f32<A>(a0 * sn[k] + a1 * cs[k]);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < kMaxPairs * 2; k++) {
-            const int i = 2 * hr + lane + 32 * k;
-            if (i < hd) {
-                float a = tail[k];
-                if (w != nullptr) a = a * inv * w[i];
-                dst[i] = from_f32<A>(a);
-            }
+    for (int k = 0; k < kMaxPairs * 2; k++) {
+        const int i = 2 * half + lane + 32 * k;
+        if (i < hd) {
+            float a = tail[k];
+            if (w != nullptr) a = a * inv * w[i];
+            dst[i] = from_f32<A>(a);
         }
     }
 }
@@ -132,10 +227,22 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_kernel
 
 using namespace iian;
 
-// qkv: [N, (nh + 2 nkv) * hd].  q_weight / k_weight / inv_freq / bias / slots may be null.
+// table[t, p] = (cos, sin)(positions[t] * inv_freq[p]) for p < half; float2 per entry.
+IIAN_API int iian_rotary_table(const float * inv_freq, const int * positions, void * table, int N, int half,
+                               cudaStream_t stream) {
+    const long long total = (long long) N * half;
+    if (total <= 0) return IIAN_OK;
+    const int threads = 256;
+    return iian_launch(rotary_table_kernel, dim3((unsigned) ((total + threads - 1) / threads)), dim3(threads), 0, stream,
+                       inv_freq, positions, (float2 *) table, half, total);
+}
+
+// qkv: [N, (nh + 2 nkv) * hd].  q_weight / k_weight / inv_freq / bias / slots / table may be null.  With a
+// table (from iian_rotary_table for the same positions and rot_dim / 2 pairs) no sine or cosine is computed
+// here.
 IIAN_API int iian_qk_norm_rope_store(
     const void * qkv, const float * bias, void * q_out, void * k_cache, void * v_cache,
-    const float * q_weight, const float * k_weight, const float * inv_freq,
+    const float * q_weight, const float * k_weight, const float * inv_freq, const void * table,
     const int * positions, const int * slots, int act_dtype,
     int N, int nh, int nkv, int hd, int rot_dim, int rope_style, float eps,
     int page_size, int num_pages, int write_kv, cudaStream_t stream) {
@@ -143,16 +250,31 @@ IIAN_API int iian_qk_norm_rope_store(
     if (hd <= 0 || hd > kMaxHeadDim) return IIAN_ERR_SHAPE;
     if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return IIAN_ERR_SHAPE;
     if (write_kv && (slots == nullptr || k_cache == nullptr || v_cache == nullptr)) return IIAN_ERR_SHAPE;
-    const unsigned blocks = (unsigned) N;
+    if (act_dtype != IIAN_F32 && act_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
+    const long long items = (long long) N * (nh + 2 * nkv);
+    const unsigned blocks = (unsigned) ((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const int threads = kWarpsPerBlock * 32;
+    const bool no_rope = inv_freq == nullptr || rot_dim == 0;
+    const bool fast = bias == nullptr && hd % 4 == 0 && (no_rope || (rope_style == 0 && rot_dim == hd && table != nullptr)) &&
+                      ((uintptr_t) qkv & 7) == 0 && ((uintptr_t) q_out & 7) == 0 && ((uintptr_t) k_cache & 7) == 0 &&
+                      ((uintptr_t) v_cache & 7) == 0 && ((uintptr_t) q_weight & 7) == 0 && ((uintptr_t) k_weight & 7) == 0 &&
+                      ((uintptr_t) table & 15) == 0;
+    const float2 * tab = no_rope ? nullptr : (const float2 *) table;
+    if (fast) {
+        if (act_dtype == IIAN_F32)
+            return iian_launch(qk_norm_rope_store_fast_kernel<float>, dim3(blocks), dim3(threads), 0, stream,
+                (const float *) qkv, (float *) q_out, (float *) k_cache, (float *) v_cache, q_weight, k_weight, tab, slots,
+                N, nh, nkv, hd, eps, page_size, num_pages, write_kv);
+        return iian_launch(qk_norm_rope_store_fast_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
+            (const __nv_bfloat16 *) qkv, (__nv_bfloat16 *) q_out, (__nv_bfloat16 *) k_cache, (__nv_bfloat16 *) v_cache,
+            q_weight, k_weight, tab, slots, N, nh, nkv, hd, eps, page_size, num_pages, write_kv);
+    }
     if (act_dtype == IIAN_F32)
         return iian_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(threads), 0, stream,
             (const float *) qkv, bias, (float *) q_out, (float *) k_cache, (float *) v_cache, q_weight, k_weight,
-            inv_freq, positions, slots, N, nh, nkv, hd, rot_dim, rope_style, eps, page_size, num_pages, write_kv);
-    if (act_dtype == IIAN_BF16)
-        return iian_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
-            (const __nv_bfloat16 *) qkv, bias, (__nv_bfloat16 *) q_out, (__nv_bfloat16 *) k_cache,
-            (__nv_bfloat16 *) v_cache, q_weight, k_weight, inv_freq, positions, slots, N, nh, nkv, hd, rot_dim,
-            rope_style, eps, page_size, num_pages, write_kv);
-    return IIAN_ERR_DTYPE;
+            inv_freq, tab, positions, slots, N, nh, nkv, hd, rot_dim, rope_style, eps, page_size, num_pages, write_kv);
+    return iian_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
+        (const __nv_bfloat16 *) qkv, bias, (__nv_bfloat16 *) q_out, (__nv_bfloat16 *) k_cache,
+        (__nv_bfloat16 *) v_cache, q_weight, k_weight, inv_freq, tab, positions, slots, N, nh, nkv, hd, rot_dim,
+        rope_style, eps, page_size, num_pages, write_kv);
 }

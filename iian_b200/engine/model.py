@@ -159,6 +159,8 @@ class Model:
     def forward(self, ctx, storage) -> Optional[torch.Tensor]:
         """Run ``ctx.tokens`` through the model and return float32 logits ``[R, vocab]`` for
         ``ctx.out_rows`` (None if no row is wanted; the caches are still updated)."""
+        if hasattr(ctx, "step_cache"):
+            ctx.step_cache.clear()          # a context may be run twice (eagerly, then under graph capture)
         residual = self.embedding.forward(ctx.tokens, ctx)
         delta = None
         order = self.spec.order

@@ -88,6 +88,7 @@ class StepContext:
         self.tokens = self.positions = self.seq_of_token = self.cu_q = self.ctx_len = None
         self.state_slots = self.out_rows = None
         self.metas: List[AttentionMeta] = []
+        self.step_cache: Dict[object, object] = {}     # what parts compute once per forward pass and share (cleared by Model.forward)
         self.num_tokens = self.num_seqs = 0
         self.h_q_start: List[int] = []
         self.h_q_len: List[int] = []

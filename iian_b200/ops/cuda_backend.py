@@ -342,7 +342,7 @@ class CudaKernels:
                            q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                            inv_freq: Optional[torch.Tensor], rot_dim: int, rope_style: int,
                            positions: torch.Tensor, slots: Optional[torch.Tensor], write_kv: bool,
-                           bias: Optional[torch.Tensor] = None) -> None:
+                           bias: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None) -> None:
         n = qkv.shape[0]
         width = (num_heads + 2 * num_kv_heads) * head_dim
         if qkv.shape[1] != width or q_out.numel() != n * num_heads * head_dim or q_out.dtype != qkv.dtype:
@@ -359,15 +359,27 @@ class CudaKernels:
         if inv_freq is not None and inv_freq.numel() < rot_dim // 2:
             raise KernelError("qk_norm_rope_store: inv_freq is shorter than rot_dim / 2")
         fn = _fn("rope_kv", "iian_qk_norm_rope_store",
-                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+        if table is not None and (inv_freq is None or table.numel() < 2 * n * (rot_dim // 2)):
+            raise KernelError("qk_norm_rope_store: the rotary table does not cover these tokens")
         _check(fn(_cuda(qkv, "qkv"), _cuda(bias, "qkv bias", torch.float32), _cuda(q_out, "q out"),
                   _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"),
                   _cuda(q_weight, "q norm weight", torch.float32), _cuda(k_weight, "k norm weight", torch.float32),
-                  _cuda(inv_freq, "inv_freq", torch.float32), _cuda(positions, "positions", torch.int32),
+                  _cuda(inv_freq, "inv_freq", torch.float32), _cuda(table, "rotary table", torch.float32),
+                  _cuda(positions, "positions", torch.int32),
                   _cuda(slots, "slots", torch.int32), _code(qkv, "qkv"), n, num_heads, num_kv_heads, head_dim,
                   rot_dim if inv_freq is not None else 0, rope_style, eps, page_size, num_pages, 1 if write_kv else 0,
                   _stream()), "qk_norm_rope_store")
+
+    def rotary_table(self, inv_freq: torch.Tensor, positions: torch.Tensor, half: int, out: torch.Tensor) -> None:
+        """out[t, p] = (cos, sin)(positions[t] * inv_freq[p]), float32 [N, half, 2]."""
+        n = positions.shape[0]
+        if out.numel() < 2 * n * half or inv_freq.numel() < half:
+            raise KernelError("rotary_table: output or inv_freq too small")
+        fn = _fn("rope_kv", "iian_rotary_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+        _check(fn(_cuda(inv_freq, "inv_freq", torch.float32), _cuda(positions, "positions", torch.int32),
+                  _cuda(out, "rotary table", torch.float32), n, half, _stream()), "rotary_table")
 
     def paged_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                         meta, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,

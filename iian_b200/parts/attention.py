@@ -110,7 +110,8 @@ class Attention(Mixer):
             q_weight=self.q_norm_w, k_weight=self.k_norm_w, eps=self.eps,
             inv_freq=pos.inv_freq if pos.fused else None, rot_dim=pos.dim if pos.fused else 0,
             rope_style=pos.style if pos.fused else 0,
-            positions=ctx.positions, slots=meta.slots if writes_cache else None, write_kv=writes_cache, bias=bias)
+            positions=ctx.positions, slots=meta.slots if writes_cache else None, write_kv=writes_cache, bias=bias,
+            **({"table": pos.table(ctx)} if pos.fused and hasattr(pos, "table") and pos.inv_freq is not None else {}))
         attn = ctx.buf("attn", (n, self.q_size), self.dtype)
         k.paged_attention(q, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
                           head_dim=self.hd, scale=self.scale, window=self.window)

@@ -44,6 +44,23 @@ class Rotary(PositionEncoding):
         j = torch.arange(self.dim // 2, dtype=torch.float64)
         inv = scale * torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * j / self.dim)
         self.inv_freq = inv.to(torch.float32).to(device)
+        self.key = ("rotary", self.dim, self.base, scale)
+
+    def table(self, ctx):
+        """cos and sin of this step's angles, float32 [N, dim / 2, 2].  The angles depend on the positions
+        and on this part's constants only, so one table per step serves every layer that rotates alike."""
+        from .. import ops
+        tables = ctx.step_cache.setdefault("rotary_tables", {}) if hasattr(ctx, "step_cache") else {}
+        t = tables.get(self.key)
+        if t is None:
+            k = ops.kernels()
+            if not hasattr(k, "rotary_table"):
+                return None
+            n = ctx.positions.shape[0]
+            t = ctx.buf(f"rotary_table_{len(tables)}", (n, self.dim // 2, 2), torch.float32)
+            k.rotary_table(self.inv_freq, ctx.positions, self.dim // 2, t)
+            tables[self.key] = t
+        return t
 
 
 @register_position("none")

@@ -50,7 +50,7 @@ class FakeKernels:
         out.copy_((x.float() @ w.float().T).to(out.dtype))
 
     def qk_norm_rope_store(self, qkv, q_out, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim, q_weight,
-                           k_weight, eps, inv_freq, rot_dim, rope_style, positions, slots, write_kv, bias=None):
+                           k_weight, eps, inv_freq, rot_dim, rope_style, positions, slots, write_kv, bias=None, table=None):
         n = qkv.shape[0]
         x = qkv.float()
         if bias is not None:

@@ -207,9 +207,10 @@ def test_paged_attention_generic(dtype, case, standout):
 
 
 @pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("use_table", [False, True])
 @pytest.mark.parametrize("nh,nkv,hd,rot,style,ps", [(6, 2, 48, 48, 0, 8), (4, 4, 16, 8, 0, 16), (3, 1, 80, 80, 1, 12),
-                                                      (8, 2, 128, 128, 0, 16)])
-def test_qk_norm_rope_store(dtype, nh, nkv, hd, rot, style, ps):
+                                                      (8, 2, 128, 128, 0, 16), (2, 1, 256, 256, 0, 16)])
+def test_qk_norm_rope_store(dtype, use_table, nh, nkv, hd, rot, style, ps):
     N, n_pages = 11, 9
     width = (nh + 2 * nkv) * hd
     qkv = rnd(N, width, dtype=dtype, seed=12)
@@ -225,9 +226,15 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, rot, style, ps):
     vc = torch.zeros_like(kc)
     q_out = torch.empty(N, nh, hd, dtype=dtype).cuda()
     eps = 1e-5
+    table = None
+    if use_table:      # cos / sin from the per-step table (and, where the shape allows, the vectorised kernel)
+        table = torch.empty(N, rot // 2, 2, dtype=torch.float32).cuda()
+        K().rotary_table(inv_freq, positions, rot // 2, table)
+        th = positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]
+        assert (table[..., 0].cpu() - torch.cos(th.double()).float()).abs().max() < 2e-6
     K().qk_norm_rope_store(qkv, q_out, kc, vc, num_heads=nh, num_kv_heads=nkv, head_dim=hd, q_weight=qw, k_weight=kw,
                            eps=eps, inv_freq=inv_freq, rot_dim=rot, rope_style=style, positions=positions, slots=slots,
-                           write_kv=True)
+                           write_kv=True, table=table)
     x = qkv.double().cpu().view(N, nh + 2 * nkv, hd)
     q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
     q = plain.rms_norm(q, qw.double().cpu(), eps)
