@@ -1,0 +1,160 @@
+"""Times one of the engine's kernels alone, at the Qwen3-8B layer sizes by default.
+
+    python -m iian_b200.cli.kernel_bench gemm_skinny --shape gate_up --rows 8
+    python -m iian_b200.cli.kernel_bench gemm_tcgen05 --shape gate_up --rows 2048 --epilogue swiglu
+    python -m iian_b200.cli.kernel_bench attention_decode --batch 8 --ctx 1152
+    python -m iian_b200.cli.kernel_bench attention_prefill --tokens 2048
+    python -m iian_b200.cli.kernel_bench rope --rows 2048
+    python -m iian_b200.cli.kernel_bench norm --rows 2048
+
+Timing: CUDA events around ``--iters`` launches after ``--warmup`` launches, on the launching stream;
+the operands rotate through copies that together exceed the 126 MB L2, so every launch reads from HBM.
+The same command under ``ncu`` (with small ``--iters``) gives the counters kept under ``profiles/``.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+SHAPES = {  # name -> (out features, in features) at the Qwen3-8B sizes
+    "qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288), "head": (151936, 4096),
+}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="kernel_bench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "gemm_library", "attention_decode", "attention_prefill",
+                                       "rope", "norm", "swiglu"])
+    ap.add_argument("--shape", default="gate_up", choices=sorted(SHAPES))
+    ap.add_argument("--rows", type=int, default=8, help="rows of activations (tokens in the step)")
+    ap.add_argument("--epilogue", default="store", choices=["store", "swiglu"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0: the engine's choice)")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+
+    import torch
+    from ..ops.cuda_backend import CudaKernels
+
+    if not torch.cuda.is_available():
+        print("kernel_bench: no CUDA device", file=sys.stderr)
+        return 2
+    k = CudaKernels()
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, std=1.0, dtype=bf):
+        return (torch.randn(*shape, device=dev, generator=gen, dtype=torch.float32) * std).to(dtype)
+
+    def timeit(fn):
+        for i in range(args.warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(args.iters):
+            fn(i)
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / args.iters * 1e3       # microseconds
+
+    class Meta:
+        pass
+
+    if args.kernel.startswith("gemm"):
+        m, kd = SHAPES[args.shape]
+        n = args.rows
+        copies = max(2, int(300e6 // (m * kd * 2)) + 1)
+        ws = [rnd(m, kd, std=0.02) for _ in range(copies)]
+        x = rnd(n, kd)
+        swiglu = args.epilogue == "swiglu"
+        out = torch.empty(n, m // 2 if swiglu else m, device=dev, dtype=bf)
+        if args.kernel == "gemm_skinny":
+            us = timeit(lambda i: k.gemm_skinny(x, ws[i % copies], out, epilogue=1 if swiglu else 0))
+        elif args.kernel == "gemm_tcgen05":
+            us = timeit(lambda i: k.gemm_tcgen05(x, ws[i % copies], out, epilogue=1 if swiglu else 0))
+            k.tcgen05_check(dev)
+        else:
+            us = timeit(lambda i: torch.mm(x, ws[i % copies].t(), out=out))
+        gb, tf = m * kd * 2 / 1e9, 2.0 * n * m * kd / 1e12
+        print(f"{args.kernel} {args.shape} [{m} x {kd}] rows {n} epilogue {args.epilogue}: {us:.1f} us, "
+              f"{gb / (us * 1e-6):.0f} GB/s of weights, {tf / (us * 1e-6):.0f} TFLOP/s")
+        return 0
+
+    nh, nkv, hd, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
+    if args.kernel in ("attention_decode", "attention_prefill"):
+        decode = args.kernel == "attention_decode"
+        seqs = args.batch if decode else 1
+        ctx_len = args.ctx if decode else args.tokens
+        q_len = 1 if decode else args.tokens
+        blocks = math.ceil(ctx_len / ps)
+        n_pages = seqs * blocks
+        copies = max(2, int(300e6 // (n_pages * nkv * ps * hd * 4)) + 1) if decode else 1
+        caches = [(rnd(n_pages, nkv, ps, hd), rnd(n_pages, nkv, ps, hd)) for _ in range(copies)]
+        perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+        meta = Meta()
+        meta.block_table = perm.view(seqs, blocks).to(dev).contiguous()
+        meta.cu_q = torch.arange(0, seqs * q_len + 1, q_len, dtype=torch.int32, device=dev)
+        meta.ctx_len = torch.full((seqs,), ctx_len, dtype=torch.int32, device=dev)
+        meta.positions = torch.cat([torch.arange(ctx_len - q_len, ctx_len, dtype=torch.int32) for _ in range(seqs)]).to(dev)
+        meta.seq_of_token = torch.arange(seqs, dtype=torch.int32).repeat_interleave(q_len).to(dev)
+        meta.num_seqs, meta.num_tokens, meta.max_q_len, meta.max_ctx, meta.decode_only = seqs, seqs * q_len, q_len, ctx_len, decode
+        q = rnd(seqs * q_len, nh, hd)
+        out = torch.empty(seqs * q_len, nh * hd, device=dev, dtype=bf)
+        kw = dict(num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=1 / math.sqrt(hd), window=None)
+        if decode and args.splits:
+            kw.update(n_split=args.splits, small_tiles=True)
+        us = timeit(lambda i: k.paged_attention_mma(q, caches[i % copies][0], caches[i % copies][1], out, meta, **kw))
+        if decode:
+            gb = seqs * ctx_len * nkv * hd * 2 * 2 / 1e9
+            print(f"attention_decode batch {seqs} ctx {ctx_len} heads {nh}/{nkv} x {hd}: {us:.1f} us, {gb / (us * 1e-6):.0f} GB/s of K/V "
+                  f"(splits {args.splits or k.attention_splits(seqs, nkv, ctx_len)})")
+        else:
+            tf = 4.0 * nh * hd * q_len * (q_len + 1) / 2 / 1e12
+            print(f"attention_prefill tokens {q_len} heads {nh}/{nkv} x {hd}: {us:.1f} us, {tf / (us * 1e-6):.0f} TFLOP/s (causal)")
+        return 0
+
+    n = args.rows
+    hidden = SHAPES["o"][0]
+    if args.kernel == "norm":
+        res = [rnd(n, hidden, dtype=torch.float32) for _ in range(4)]
+        delta, w = rnd(n, hidden), torch.ones(hidden, device=dev)
+        out = torch.empty(n, hidden, device=dev, dtype=bf)
+        us = timeit(lambda i: k.add_rms_norm(res[i % 4], delta, w, 1e-6, out))
+        gb = n * hidden * (4 + 2 + 4 + 2) / 1e9
+        print(f"add_rms_norm rows {n} width {hidden}: {us:.1f} us, {gb / (us * 1e-6):.0f} GB/s")
+    elif args.kernel == "swiglu":
+        f = SHAPES["down"][1]
+        gu = rnd(n, 2 * f)
+        out = torch.empty(n, f, device=dev, dtype=bf)
+        us = timeit(lambda i: k.swiglu(gu, out, 8))
+        print(f"swiglu rows {n} width {f}: {us:.1f} us, {n * f * 6 / 1e9 / (us * 1e-6):.0f} GB/s")
+    else:
+        width = (nh + 2 * nkv) * hd
+        qkv = rnd(n, width)
+        n_pages = math.ceil(n / ps) + 1
+        kc, vc = torch.zeros(n_pages, nkv, ps, hd, device=dev, dtype=bf), torch.zeros(n_pages, nkv, ps, hd, device=dev, dtype=bf)
+        q_out = torch.empty(n, nh, hd, device=dev, dtype=bf)
+        qw, kw_ = torch.ones(hd, device=dev), torch.ones(hd, device=dev)
+        inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        table = torch.empty(n, hd // 2, 2, device=dev)
+        k.rotary_table(inv, pos, hd // 2, table)
+        us = timeit(lambda i: k.qk_norm_rope_store(qkv, q_out, kc, vc, num_heads=nh, num_kv_heads=nkv, head_dim=hd, q_weight=qw,
+                                                   k_weight=kw_, eps=1e-6, inv_freq=inv, rot_dim=hd, rope_style=0, positions=pos,
+                                                   slots=pos, write_kv=True, table=table))
+        print(f"qk_norm_rope_store rows {n} heads {nh}+2x{nkv} x {hd}: {us:.1f} us, {n * width * 4 / 1e9 / (us * 1e-6):.0f} GB/s")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
