@@ -9,7 +9,10 @@
 
 Timing: CUDA events around ``--iters`` launches after ``--warmup`` launches, on the launching stream;
 the operands rotate through copies that together exceed the 126 MB L2, so every launch reads from HBM.
-The same command under ``ncu`` (with small ``--iters``) gives the counters kept under ``profiles/``.
+With ``--graph`` the timed launches are captured into one CUDA graph and the graph is replayed: the
+engine's decode steps run that way, and kernels of a few microseconds are otherwise timed by the host's
+launch rate.  The same command under ``ncu`` (with small ``--iters``) gives the counters kept under
+``profiles/``.
 """
 from __future__ import annotations
 
@@ -39,6 +42,8 @@ def main(argv=None) -> int:
     ap.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0: the engine's choice)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--graph", action="store_true", help="time the launches as one replayed CUDA graph")
+    ap.add_argument("--cfg", type=int, default=0, help="gemm_skinny: tile configuration (0: the kernel's choice)")
     args = ap.parse_args(argv)
 
     import torch
@@ -60,6 +65,22 @@ def main(argv=None) -> int:
             fn(i)
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+                for i in range(args.iters):
+                    fn(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            reps = 5
+            s.record()
+            for _ in range(reps):
+                graph.replay()
+            e.record()
+            torch.cuda.synchronize()
+            return s.elapsed_time(e) / (args.iters * reps) * 1e3
         s.record()
         for i in range(args.iters):
             fn(i)
@@ -79,7 +100,7 @@ def main(argv=None) -> int:
         swiglu = args.epilogue == "swiglu"
         out = torch.empty(n, m // 2 if swiglu else m, device=dev, dtype=bf)
         if args.kernel == "gemm_skinny":
-            us = timeit(lambda i: k.gemm_skinny(x, ws[i % copies], out, epilogue=1 if swiglu else 0))
+            us = timeit(lambda i: k.gemm_skinny(x, ws[i % copies], out, cfg=args.cfg, epilogue=1 if swiglu else 0))
         elif args.kernel == "gemm_tcgen05":
             us = timeit(lambda i: k.gemm_tcgen05(x, ws[i % copies], out, epilogue=1 if swiglu else 0))
             k.tcgen05_check(dev)

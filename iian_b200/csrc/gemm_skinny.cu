@@ -249,6 +249,219 @@ static int launch_skinny(const void * x, const void * w, void * out, int B, int 
     return launch_nt<8, 0, OutT>(x, w, out, B, M, K, cfg, ksplit, part, counters, stream);
 }
 
+
+// ---- the same product with the work cut evenly over the SMs ------------------------------------------
+// A grid of row tiles leaves SMs idle whenever the number of tiles is not a multiple of what the GPU
+// holds at once (256 tiles of the output projection on 148 SMs: the slowest SM carries two, the mean is
+// 1.7).  Here the grid is exactly what the GPU holds, and the work, counted in steps (one step = every
+// warp of the CTA takes one 32-wide chunk of k of one 16-row tile), is cut into equal contiguous ranges:
+// a CTA takes the rest of one tile, some whole tiles, and the start of another.  A tile that is shared
+// leaves its parts in scratch memory; whichever CTA completes the tile's step count adds the parts in the
+// order of their position (not of their arrival) and writes the result, so there is no waiting between
+// CTAs and the sum does not depend on timing.  The cut depends on (M, K) and the device only, never on the
+// batch.
+template <int NT, int WARPS, int UNROLL, int EPI, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32, UNROLL >= 8 ? 2 : 3) gemm_stream_kernel(
+    const __nv_bfloat16 * __restrict__ x, const __nv_bfloat16 * __restrict__ w, OutT * __restrict__ out,
+    int B, int M, int K, float * __restrict__ part, int * __restrict__ counters, int max_parts) {
+    __shared__ float red[WARPS][16][NT * 8 + 1];
+    __shared__ int s_last;
+    constexpr int CELLS = 16 * NT * 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int spt = K / (32 * WARPS);                 // steps per tile
+    const int tiles = (M + 15) / 16;
+    const long long total = (long long) tiles * spt;
+    const long long P = min((long long) gridDim.x, total);      // every CTA that works has at least one step
+    if (blockIdx.x >= P) return;
+    long long u = total * blockIdx.x / P;
+    const long long u_end = total * (blockIdx.x + 1) / P;
+
+    const uint4 * xr[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int n = min(nt * 8 + g, B - 1);
+        xr[nt] = reinterpret_cast<const uint4 *>(x + (size_t) n * K) + t;
+    }
+    bool waited = false;
+    while (u < u_end) {
+        const int tile = (int) (u / spt), s_begin = (int) (u % spt);
+        const int s_end = (int) min((long long) spt, s_begin + (u_end - u));
+        const int m0 = tile * 16;
+        const uint4 * w0 = reinterpret_cast<const uint4 *>(w + (size_t) min(m0 + g, M - 1) * K) + t;
+        const uint4 * w1 = reinterpret_cast<const uint4 *>(w + (size_t) min(m0 + g + 8, M - 1) * K) + t;
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+        {
+            const size_t off = ((size_t) s_begin * WARPS + warp) * 4;   // in 16-byte units; a step is WARPS * 4 of them
+            const uint4 * p0 = w0 + off;
+            const uint4 * p1 = w1 + off;
+            const uint4 * px[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) px[nt] = xr[nt] + off;
+            for (int s = s_begin; s < s_end; s += UNROLL) {
+                uint4 a0[UNROLL], a1[UNROLL];
+#pragma unroll
+                for (int q = 0; q < UNROLL; q++)
+                    if (s + q < s_end) {
+                        a0[q] = ld_stream(p0 + q * WARPS * 4);
+                        a1[q] = ld_stream(p1 + q * WARPS * 4);
+                    }
+                // The weights do not depend on the kernel before this one: the first loads are in flight
+                // before this kernel waits for its activations.
+                if (!waited) { pdl_wait(); waited = true; }
+#pragma unroll
+                for (int q = 0; q < UNROLL; q++)
+                    if (s + q < s_end) {
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            const uint4 b = __ldg(px[nt] + q * WARPS * 4);
+                            mma_bf16_16816(acc[nt], a0[q].x, a1[q].x, a0[q].y, a1[q].y, b.x, b.y);
+                            mma_bf16_16816(acc[nt], a0[q].z, a1[q].z, a0[q].w, a1[q].w, b.z, b.w);
+                        }
+                    }
+                p0 += UNROLL * WARPS * 4;
+                p1 += UNROLL * WARPS * 4;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) px[nt] += UNROLL * WARPS * 4;
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+            red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+            red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+            red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+        }
+        __syncthreads();
+        // cell idx = n * 16 + r; the warps' sums are added in a fixed order
+        float mine[(CELLS + WARPS * 32 - 1) / (WARPS * 32)];
+#pragma unroll
+        for (int j = 0; j < (CELLS + WARPS * 32 - 1) / (WARPS * 32); j++) {
+            const int idx = threadIdx.x + j * WARPS * 32;
+            float v = 0.0f;
+            if (idx < CELLS) {
+#pragma unroll
+                for (int wv = 0; wv < WARPS; wv++) v += red[wv][idx % 16][idx / 16];
+            }
+            mine[j] = v;
+        }
+        __syncthreads();
+        bool finish = true;
+        if (s_begin != 0 || s_end != spt) {
+            // position of this CTA among those that share the tile: CTA i starts at floor(total * i / P), so
+            // the CTA that holds step v is floor(((v + 1) * P - 1) / total)
+            const long long first = (((long long) tile * spt + 1) * P - 1) / total;
+            const long long last = (((long long) (tile + 1) * spt) * P - 1) / total;
+            const int slot = (int) (blockIdx.x - first), n_parts = (int) (last - first + 1);
+            float * dst = part + ((size_t) tile * max_parts + slot) * CELLS;
+#pragma unroll
+            for (int j = 0; j < (CELLS + WARPS * 32 - 1) / (WARPS * 32); j++) {
+                const int idx = threadIdx.x + j * WARPS * 32;
+                if (idx < CELLS) dst[idx] = mine[j];
+            }
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) s_last = (atomicAdd(counters + tile, s_end - s_begin) + (s_end - s_begin) == spt);
+            __syncthreads();
+            finish = s_last != 0;
+            if (finish) {
+                __threadfence();
+                const float * all = part + (size_t) tile * max_parts * CELLS;
+#pragma unroll
+                for (int j = 0; j < (CELLS + WARPS * 32 - 1) / (WARPS * 32); j++) {
+                    const int idx = threadIdx.x + j * WARPS * 32;
+                    float v = 0.0f;
+                    if (idx < CELLS)
+                        for (int i = 0; i < n_parts; i++) v += __ldcg(all + (size_t) i * CELLS + idx);
+                    mine[j] = v;
+                }
+                if (threadIdx.x == 0) counters[tile] = 0;
+            }
+        }
+        if (finish) {
+            if (EPI == 1) {
+                // rows 0..7 of the tile are gate, 8..15 up, of the same 8 features (src/iian/graph.cpp:135)
+#pragma unroll
+                for (int j = 0; j < (CELLS + WARPS * 32 - 1) / (WARPS * 32); j++) {
+                    const int idx = threadIdx.x + j * WARPS * 32;
+                    if (idx < CELLS) red[0][idx % 16][idx / 16] = mine[j];
+                }
+                __syncthreads();
+                for (int idx = threadIdx.x; idx < CELLS / 2; idx += WARPS * 32) {
+                    const int n = idx / 8, f = idx % 8;
+                    if (n < B && m0 + 15 < M) {
+                        const float gv = red[0][f][n], uv = red[0][f + 8][n];
+                        out[(size_t) n * (M / 2) + (m0 / 2 + f)] = from_f32<OutT>(gv / (1.0f + expf(-gv)) * uv);
+                    }
+                }
+                __syncthreads();
+            } else {
+#pragma unroll
+                for (int j = 0; j < (CELLS + WARPS * 32 - 1) / (WARPS * 32); j++) {
+                    const int idx = threadIdx.x + j * WARPS * 32;
+                    const int n = idx / 16, m = m0 + idx % 16;
+                    if (idx < CELLS && n < B && m < M) out[(size_t) n * M + m] = from_f32<OutT>(mine[j]);
+                }
+            }
+        }
+        u += s_end - s_begin;
+    }
+    pdl_launch_dependents();
+}
+
+// CTAs the device holds at once for this instantiation (SMs x CTAs per SM), per device
+template <int NT, int WARPS, int UNROLL, int EPI, typename OutT>
+static int stream_grid(int * grid) {
+    static int cached[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return 1000 + (int) e;
+    if (dev < 0 || dev >= 64) return IIAN_ERR_LIMIT;
+    if (cached[dev] == 0) {
+        int sms = 0, per_sm = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return 1000 + (int) e;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_stream_kernel<NT, WARPS, UNROLL, EPI, OutT>, WARPS * 32, 0);
+        if (e != cudaSuccess) return 1000 + (int) e;
+        if (per_sm < 1) return IIAN_ERR_LIMIT;
+        cached[dev] = sms * per_sm;
+    }
+    *grid = cached[dev];
+    return IIAN_OK;
+}
+
+static int stream_max_parts(int M, int K, int warps, int grid) {
+    // a tile's parts are consecutive CTAs; all but the first and the last lie wholly inside the tile
+    const long long spt = K / (32 * warps), tiles = (M + 15) / 16, total = tiles * spt;
+    const long long P = grid < total ? grid : total;
+    const long long mp = (spt + 1) * P / total + 2;
+    return (int) (mp < spt ? mp : spt);
+}
+
+template <int NT, int WARPS, int UNROLL, int EPI, typename OutT>
+static int launch_stream(const void * x, const void * w, void * out, int B, int M, int K, float * part, size_t part_floats,
+                         int * counters, size_t counter_ints, size_t * need_floats, size_t * need_ints, cudaStream_t stream) {
+    int grid = 0;
+    const int rc = stream_grid<NT, WARPS, UNROLL, EPI, OutT>(&grid);
+    if (rc != IIAN_OK) return rc;
+    const int max_parts = stream_max_parts(M, K, WARPS, grid);
+    const size_t tiles = (size_t) (M + 15) / 16;
+    const size_t nf = tiles * max_parts * 16 * NT * 8;
+    if (need_floats != nullptr) { *need_floats = nf; *need_ints = tiles; return IIAN_OK; }
+    if (part == nullptr || counters == nullptr || part_floats < nf || counter_ints < tiles) return IIAN_ERR_LIMIT;
+    return iian_launch(gemm_stream_kernel<NT, WARPS, UNROLL, EPI, OutT>, dim3(grid), dim3(WARPS * 32), 0, stream,
+                       (const __nv_bfloat16 *) x, (const __nv_bfloat16 *) w, (OutT *) out, B, M, K, part, counters, max_parts);
+}
+
+template <int EPI, typename OutT>
+static int launch_stream_k(const void * x, const void * w, void * out, int B, int M, int K, float * part, size_t pf, int * counters,
+                           size_t ci, size_t * nf, size_t * ni, cudaStream_t stream) {
+    if (K >= 8192) return launch_stream<1, 8, 8, EPI, OutT>(x, w, out, B, M, K, part, pf, counters, ci, nf, ni, stream);
+    return launch_stream<1, 8, 4, EPI, OutT>(x, w, out, B, M, K, part, pf, counters, ci, nf, ni, stream);
+}
+
 }  // namespace iian
 
 using namespace iian;
@@ -281,4 +494,31 @@ IIAN_API int iian_gemm_skinny_cfg(const void * x, const void * w, void * out, in
 IIAN_API int iian_gemm_skinny(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K,
                               cudaStream_t stream) {
     return iian_gemm_skinny_cfg(x, w, out, out_dtype, B, M, K, 0, 1, nullptr, nullptr, 0, stream);
+}
+
+// The evenly cut form (up to 8 rows, K a multiple of 256).  part and counters are scratch of at least the
+// sizes that iian_gemm_stream_scratch reports; counters are zero before the first launch and left zero.
+IIAN_API int iian_gemm_stream(const void * x, const void * w, void * out, int out_dtype, int B, int M, int K, float * part,
+                              size_t part_floats, int * counters, size_t counter_ints, int epilogue, cudaStream_t stream) {
+    if (B <= 0 || M <= 0) return IIAN_OK;
+    if (B > 8) return IIAN_ERR_LIMIT;
+    if (K <= 0 || K % 256 != 0) return IIAN_ERR_SHAPE;
+    if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
+    if (epilogue == 1) {
+        if (M % 16 != 0 || out_dtype != IIAN_BF16) return IIAN_ERR_SHAPE;
+        return launch_stream_k<1, __nv_bfloat16>(x, w, out, B, M, K, part, part_floats, counters, counter_ints, nullptr, nullptr, stream);
+    }
+    if (epilogue != 0) return IIAN_ERR_SHAPE;
+    if (out_dtype == IIAN_BF16)
+        return launch_stream_k<0, __nv_bfloat16>(x, w, out, B, M, K, part, part_floats, counters, counter_ints, nullptr, nullptr, stream);
+    if (out_dtype == IIAN_F32)
+        return launch_stream_k<0, float>(x, w, out, B, M, K, part, part_floats, counters, counter_ints, nullptr, nullptr, stream);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_gemm_stream_scratch(int out_dtype, int M, int K, int epilogue, size_t * part_floats, size_t * counter_ints) {
+    if (M <= 0 || K <= 0 || K % 256 != 0 || part_floats == nullptr || counter_ints == nullptr) return IIAN_ERR_SHAPE;
+    if (epilogue == 1) return launch_stream_k<1, __nv_bfloat16>(nullptr, nullptr, nullptr, 1, M, K, nullptr, 0, nullptr, 0, part_floats, counter_ints, nullptr);
+    if (out_dtype == IIAN_F32) return launch_stream_k<0, float>(nullptr, nullptr, nullptr, 1, M, K, nullptr, 0, nullptr, 0, part_floats, counter_ints, nullptr);
+    return launch_stream_k<0, __nv_bfloat16>(nullptr, nullptr, nullptr, 1, M, K, nullptr, 0, nullptr, 0, part_floats, counter_ints, nullptr);
 }

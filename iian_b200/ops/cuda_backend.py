@@ -245,14 +245,47 @@ class CudaKernels:
         memory pipeline idle (a row block of 16 is one CTA)."""
         return 1       # measured on B200 at the Qwen3-8B sizes: one CTA per row block is fastest for every shape
 
+    # the evenly cut form of the streaming product (csrc/gemm_skinny.cu, gemm_stream_kernel); IIAN_STREAM_GEMM=0
+    # goes back to one CTA per row tile
+    STREAM_GEMM = os.environ.get("IIAN_STREAM_GEMM", "0") not in ("0", "false", "off")
+    _stream_need = {}
+
+    def gemm_stream(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
+        """The streaming product with the work cut evenly over the SMs: up to 8 rows, K a multiple of 256."""
+        n, k = x.shape
+        m = w.shape[0]
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise KernelError("gemm_stream: x and w must be bfloat16")
+        code = _code(out, "linear out")
+        key = (x.device, code, m, k, epilogue)
+        need = self._stream_need.get(key)
+        if need is None:
+            from ctypes import c_size_t
+            nf, ni = c_size_t(0), c_size_t(0)
+            q = _fn("gemm_skinny", "iian_gemm_stream_scratch", [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+            with torch.cuda.device(x.device):
+                _check(q(code, m, k, epilogue, ctypes.addressof(nf), ctypes.addressof(ni)), "gemm_stream")
+            need = self._stream_need[key] = (nf.value, ni.value)
+        part = self.gemm_scratch(x.device, need[0])
+        counters = self.gemm_counters(x.device, need[1])
+        fn = _fn("gemm_skinny", "iian_gemm_stream",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, ctypes.c_size_t, c_void_p, ctypes.c_size_t,
+                  c_int, c_void_p])
+        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), code, n, m, k,
+                  part.data_ptr(), part.numel(), counters.data_ptr(), counters.numel(), epilogue, _stream()), "gemm_stream")
+
     def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0, ksplit: int = 0,
                     epilogue: int = 0) -> None:
         """``cfg`` picks a tile configuration (rows-per-block tiles * 100 + warps * 10 + unroll); ``ksplit``
-        the number of CTAs that share K for one row block; 0: defaults."""
+        the number of CTAs that share K for one row block; 0: defaults.  With both at their defaults, up to 8
+        rows and K a multiple of 256 the evenly cut kernel runs instead (``cfg=-1`` asks for it by name)."""
         n, k = x.shape
         m = w.shape[0]
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: x and w must be bfloat16")
+        if cfg == -1 or (cfg == 0 and ksplit <= 0 and self.STREAM_GEMM and n <= 8 and k % 256 == 0):
+            self.gemm_stream(x, w, out, epilogue)
+            return
         if ksplit <= 0:
             ksplit = 1 if epilogue else self.skinny_ksplit(n, m, k)
         part = counters = 0
@@ -404,13 +437,12 @@ class CudaKernels:
 
     def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
         """How many parts the keys of a decode step are cut into, so that few long sequences still fill
-        the GPU."""
+        the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128): the CTAs of one launch should fit the
+        GPU at once (a second wave repeats the whole chain of dependent loads), and a CTA should keep about
+        three key tiles, since the last CTA of a row reads every part back."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
-        want = -(-2 * self.DECODE_SLOTS // base)                 # about two waves of CTAs
-        n = min(want, max(1, tiles // 2), self.MAX_SPLITS)       # at least two key tiles per CTA ...
-        if base * n < self.DECODE_SLOTS // 2:
-            n = min(want, tiles, self.MAX_SPLITS)                # ... unless the GPU would stay mostly empty
+        n = min(self.DECODE_SLOTS // base, -(-tiles // 3), self.MAX_SPLITS)
         return max(1, n)
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:

@@ -360,6 +360,60 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch():
         assert torch.equal(one[0], full[r])
 
 
+@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,M,K_", [(1, 16, 256), (3, 70, 512), (8, 257, 768), (5, 4096, 4096), (8, 1000, 12288), (2, 15, 256),
+                                    (8, 40000, 256)])
+def test_gemm_stream(od, B, M, K_):
+    """The evenly cut streaming product: tiles that several CTAs share (few rows of weights), tiles that one
+    CTA owns (many rows), a ragged last tile; three runs give the same bits and leave the counters at zero."""
+    x = rnd(B, K_, dtype=torch.bfloat16, seed=24)
+    w = rnd(M, K_, dtype=torch.bfloat16, seed=25)
+    want = x.double().cpu() @ w.double().cpu().T
+    outs = []
+    for _ in range(3):
+        out = torch.full((B, M), float("nan"), dtype=od).cuda()
+        K().gemm_skinny(x, w, out, cfg=-1)
+        outs.append(out.clone())
+    assert (outs[0].double().cpu() - want).abs().max() < tol(od if od == torch.bfloat16 else torch.float32, want.abs().max().item()) * \
+        (1 if od == torch.bfloat16 else 10)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    # the tile-per-CTA kernel stays available by configuration
+    out = torch.full((B, M), float("nan"), dtype=od).cuda()
+    K().gemm_skinny(x, w, out, cfg=184)
+    assert (out.double().cpu() - want).abs().max() < tol(od if od == torch.bfloat16 else torch.float32, want.abs().max().item()) * \
+        (1 if od == torch.bfloat16 else 10)
+
+
+@pytest.mark.parametrize("B,F,K_", [(1, 16, 256), (8, 160, 512), (5, 12288, 4096), (8, 8, 1024)])
+def test_gemm_stream_swiglu_epilogue(B, F, K_):
+    x = rnd(B, K_, dtype=torch.bfloat16, seed=43)
+    wg, wu = rnd(F, K_, dtype=torch.bfloat16, seed=44, std=0.05), rnd(F, K_, dtype=torch.bfloat16, seed=45, std=0.05)
+    inter = torch.stack([wg.view(F // 8, 8, K_), wu.view(F // 8, 8, K_)], dim=1).reshape(2 * F, K_).contiguous()
+    xd = x.double().cpu()
+    want = plain.silu(xd @ wg.double().cpu().T) * (xd @ wu.double().cpu().T)
+    for _ in range(2):
+        out = torch.full((B, F), float("nan"), dtype=torch.bfloat16).cuda()
+        K().gemm_skinny(x, inter, out, cfg=-1, epilogue=1)
+        assert (out.double().cpu() - want).abs().max() < tol(torch.bfloat16, max(1.0, want.abs().max().item()))
+
+
+def test_gemm_stream_rows_do_not_depend_on_the_batch():
+    """How the work is cut depends on the weight's shape and the device only, so a row's result is the same
+    bits whatever else is in the batch."""
+    for M, K_ in ((90, 512), (4096, 1024)):
+        x = rnd(8, K_, dtype=torch.bfloat16, seed=26)
+        w = rnd(M, K_, dtype=torch.bfloat16, seed=27)
+        full = torch.empty(8, M, dtype=torch.float32).cuda()
+        K().gemm_skinny(x, w, full, cfg=-1)
+        one = torch.empty(1, M, dtype=torch.float32).cuda()
+        for r in (0, 3, 7):
+            K().gemm_skinny(x[r:r + 1].contiguous(), w, one, cfg=-1)
+            assert torch.equal(one[0], full[r])
+        three = torch.empty(3, M, dtype=torch.float32).cuda()
+        K().gemm_skinny(x[2:5].contiguous(), w, three, cfg=-1)
+        assert torch.equal(three, full[2:5])
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do():
     from iian_b200.ops.cuda_backend import KernelError
     x = rnd(2, 40, dtype=torch.bfloat16)
