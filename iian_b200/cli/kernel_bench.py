@@ -6,6 +6,7 @@
     python -m iian_b200.cli.kernel_bench attention_prefill --tokens 2048
     python -m iian_b200.cli.kernel_bench rope --rows 2048
     python -m iian_b200.cli.kernel_bench norm --rows 2048
+    python -m iian_b200.cli.kernel_bench layer_decode --batch 8 --ctx 1152 --graph
 
 Timing: CUDA events around ``--iters`` launches after ``--warmup`` launches, on the launching stream;
 the operands rotate through copies that together exceed the 126 MB L2, so every launch reads from HBM.
@@ -28,7 +29,7 @@ SHAPES = {  # name -> (out features, in features) at the Qwen3-8B sizes
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "gemm_library", "attention_decode", "attention_prefill",
-                                       "rope", "norm", "swiglu"])
+                                       "rope", "norm", "swiglu", "layer_decode"])
     ap.add_argument("--shape", default="gate_up", choices=sorted(SHAPES))
     ap.add_argument("--rows", type=int, default=8, help="rows of activations (tokens in the step)")
     ap.add_argument("--epilogue", default="store", choices=["store", "swiglu"])
@@ -40,6 +41,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0: the engine's choice)")
+    ap.add_argument("--no-cluster", action="store_true", help="decode attention: merge key splits through scratch memory")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--graph", action="store_true", help="time the launches as one replayed CUDA graph")
@@ -112,6 +114,61 @@ def main(argv=None) -> int:
         return 0
 
     nh, nkv, hd, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
+    if args.kernel == "layer_decode":
+        # the kernels of one decoder layer of a decode step in their order, on buffers of the right sizes;
+        # the weights rotate through copies like above
+        b, ctx_len = args.batch, args.ctx
+        hidden, inter = SHAPES["o"][0], SHAPES["down"][1]
+        per_layer = sum(SHAPES[n][0] * SHAPES[n][1] * 2 for n in ("qkv", "o", "gate_up", "down"))
+        copies = max(2, int(300e6 // per_layer) + 1)
+        ws = [{n: rnd(*SHAPES[n], std=0.02) for n in ("qkv", "o", "gate_up", "down")} for _ in range(copies)]
+        blocks = math.ceil((ctx_len + 1) / ps)
+        n_pages = b * blocks
+        caches = [(rnd(n_pages, nkv, ps, hd), rnd(n_pages, nkv, ps, hd)) for _ in range(copies)]
+        meta = Meta()
+        perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+        meta.block_table = perm.view(b, blocks).to(dev).contiguous()
+        meta.cu_q = torch.arange(0, b + 1, dtype=torch.int32, device=dev)
+        meta.ctx_len = torch.full((b,), ctx_len, dtype=torch.int32, device=dev)
+        meta.positions = torch.full((b,), ctx_len - 1, dtype=torch.int32, device=dev)
+        meta.seq_of_token = torch.arange(b, dtype=torch.int32, device=dev)
+        meta.num_seqs, meta.num_tokens, meta.max_q_len, meta.max_ctx, meta.decode_only = b, b, 1, ctx_len, True
+        slots = (meta.block_table[:, (ctx_len - 1) // ps].to(torch.int64) * ps + (ctx_len - 1) % ps).to(torch.int32)
+        res = rnd(b, hidden, dtype=torch.float32)
+        delta = rnd(b, hidden, std=0.01)
+        h = torch.empty(b, hidden, device=dev, dtype=bf)
+        qkv = torch.empty(b, (nh + 2 * nkv) * hd, device=dev, dtype=bf)
+        qh = torch.empty(b, nh, hd, device=dev, dtype=bf)
+        attn = torch.empty(b, nh * hd, device=dev, dtype=bf)
+        act = torch.empty(b, inter, device=dev, dtype=bf)
+        nw, qw = torch.ones(hidden, device=dev), torch.ones(hd, device=dev)
+        inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(dev)
+        table = torch.empty(b, hd // 2, 2, device=dev)
+        k.rotary_table(inv, meta.positions, hd // 2, table)
+
+        def layer(i):
+            w, (kc, vc) = ws[i % copies], caches[i % copies]
+            k.add_rms_norm(res, delta, nw, 1e-6, h)
+            k.linear(h, w["qkv"], qkv)
+            k.qk_norm_rope_store(qkv, qh, kc, vc, num_heads=nh, num_kv_heads=nkv, head_dim=hd, q_weight=qw, k_weight=qw,
+                                 eps=1e-6, inv_freq=inv, rot_dim=hd, rope_style=0, positions=meta.positions, slots=slots,
+                                 write_kv=True, table=table)
+            k.paged_attention_mma(qh, kc, vc, attn, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                                  scale=1 / math.sqrt(hd), window=None)
+            k.linear(attn, w["o"], delta)
+            k.add_rms_norm(res, delta, nw, 1e-6, h)
+            if k.can_fuse_swiglu(h, w["gate_up"], 8):
+                k.linear_swiglu(h, w["gate_up"], act)
+            else:
+                gu = torch.empty(b, 2 * inter, device=dev, dtype=bf)
+                k.linear(h, w["gate_up"], gu)
+                k.swiglu(gu, act, 8)
+            k.linear(act, w["down"], delta)
+
+        us = timeit(layer)
+        gb = (per_layer + b * ctx_len * nkv * hd * 4) / 1e9
+        print(f"layer_decode batch {b} ctx {ctx_len}: {us:.1f} us a layer, {gb / (us * 1e-6):.0f} GB/s of weights and K/V")
+        return 0
     if args.kernel in ("attention_decode", "attention_prefill"):
         decode = args.kernel == "attention_decode"
         seqs = args.batch if decode else 1
@@ -134,6 +191,8 @@ def main(argv=None) -> int:
         kw = dict(num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=1 / math.sqrt(hd), window=None)
         if decode and args.splits:
             kw.update(n_split=args.splits, small_tiles=True)
+        if args.no_cluster:
+            kw.update(cluster=False)
         us = timeit(lambda i: k.paged_attention_mma(q, caches[i % copies][0], caches[i % copies][1], out, meta, **kw))
         if decode:
             gb = seqs * ctx_len * nkv * hd * 2 * 2 / 1e9

@@ -16,8 +16,11 @@
 // each sequence's cells into a contiguous buffer and calling a dense flash-attention kernel
 // (src/iian/graph.cpp:474-518); here the gather happens inside the kernel.
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 namespace iian {
+
+namespace cg = cooperative_groups;
 
 constexpr int BN = 64;   // keys per tile
 
@@ -34,6 +37,16 @@ struct AttnParams {
     const int * block_table;        // [S, max_blocks]
     int max_blocks, nh, nkv, page_size, num_pages, window, n_split;
     float scale_log2;               // scale * log2(e)
+    // fused form of the decode kernel: Q, K and V of the step's tokens come straight from the projection
+    __nv_bfloat16 * k_cache_w;      // the caches again, writable
+    __nv_bfloat16 * v_cache_w;
+    const __nv_bfloat16 * qkv;      // [N, (nh + 2 nkv) * HD]
+    const float * q_weight;         // [HD] or null: per-head RMSNorm weights
+    const float * k_weight;
+    const float2 * table;           // [N, HD / 2] (cos, sin) of the tokens' angles, or null: no rotation
+    const int * slots;              // [N] cache cell of each token (page * page_size + offset), < 0: not stored
+    float eps;
+    int write_kv;
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -336,7 +349,18 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
 // of its use.  With n_split > 1 the CTA that finishes last for its rows (a counter per row tile, bumped
 // after the partial results are fenced out) merges the parts and writes the output, so there is no
 // second launch; it leaves the counter at zero for the next launch.
-template <int HD>
+// CLUSTER: the n_split (2 to 8) CTAs of a row tile are one thread-block cluster.  Each leaves its
+// (max, sum, unnormalised output) in its own shared memory; after a cluster barrier every CTA merges a
+// slice of the head's columns, reading the others' shared memory directly, and writes it out.  No scratch
+// memory, no fence, no counter: the merge costs two cluster barriers instead of three trips through L2.
+// FUSED (steps in which every sequence has one token): the kernel takes the output of the Q|K|V projection
+// instead of prepared heads.  Every CTA normalises and rotates the query heads of its KV head itself
+// (src/iian/arch/qwen3.cpp:80-87: RMSNorm over the head, then NEOX rotation), with the arithmetic of
+// rope_kv.cu in the same order, so both routes give the same bits.  The CTA whose key range holds the
+// token's own position also normalises and rotates the new key, writes it and the new value to the cache,
+// fences, and only then copies that tile: it reads its own write.  This saves a launch and a round trip of
+// Q through memory.
+template <int HD, bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams p) {
     constexpr int NW = 4, BM = 16, STAGES = 3;
     constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
@@ -376,29 +400,35 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     // Row bases (element offset of a key's row in the cache, -1: nothing to load) are looked up once per
     // row into a ring of shared-memory slots, a tile ahead of the copies that use them; the copies run
     // over consecutive 16-byte chunks, so that a warp's request covers whole contiguous rows.
+    const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? __ffs(p.page_size) - 1 : -1;
     auto lookup_rows = [&](int tile, int slot) {
         if (tid < BN) {
             const int j = tile * BN + tid;
             long long cell = -1;
             if (tile < tile_end && j <= k_hi) {
-                const int page = bt[j / p.page_size];
+                const int blk = page_shift >= 0 ? j >> page_shift : j / p.page_size;
+                const int page = bt[blk];
                 if (page >= 0 && page < p.num_pages)
-                    cell = (((long long) page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+                    cell = (((long long) page * p.nkv + kvh) * p.page_size + (j - blk * p.page_size)) * HD;
             }
             s_cell[slot][tid] = cell;
         }
     };
+    // A thread copies the same 16-byte column of rows tid / CH, tid / CH + ROWS_PER_PASS, ...: the swizzled
+    // column is the same in every pass (ROWS_PER_PASS is a multiple of 8), so only the row base changes.
+    constexpr int ROWS_PER_PASS = NW * 32 / CH;
+    const int ld_row = tid / CH, ld_ch = tid % CH;
+    const unsigned ld_dst = swz<HD>(ld_row, ld_ch);
     auto load_kv = [&](int stage) {                          // the slot of a tile is its stage
-        unsigned char * dK = sK + stage * TILE_BYTES;
-        unsigned char * dV = sV + stage * TILE_BYTES;
+        const unsigned dK = smem_u32(sK + stage * TILE_BYTES) + ld_dst;
+        const unsigned dV = smem_u32(sV + stage * TILE_BYTES) + ld_dst;
 #pragma unroll
-        for (int c = tid; c < BN * CH; c += NW * 32) {
-            const int r = c / CH, ch = c % CH;
-            const long long cell = s_cell[stage][r];
+        for (int i = 0; i < BN / ROWS_PER_PASS; i++) {
+            const long long cell = s_cell[stage][ld_row + i * ROWS_PER_PASS];
             const bool valid = cell >= 0;
-            const size_t off = valid ? (size_t) cell + ch * 8 : 0;
-            cp_async16(smem_u32(dK + swz<HD>(r, ch)), p.k_cache + off, valid);
-            cp_async16(smem_u32(dV + swz<HD>(r, ch)), p.v_cache + off, valid);
+            const size_t off = valid ? (size_t) cell + ld_ch * 8 : 0;
+            cp_async16(dK + i * ROWS_PER_PASS * HD * 2, p.k_cache + off, valid);
+            cp_async16(dV + i * ROWS_PER_PASS * HD * 2, p.v_cache + off, valid);
         }
     };
 
@@ -426,17 +456,97 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     pdl_wait();
     if (n_my > 0) {
         __syncthreads();
-        for (int c = tid; c < BM * CH; c += NW * 32) {          // Q rows
-            const int r = c / CH, ch = c % CH;
-            const int R = row0 + r;
-            const bool valid = R < rows_total;
-            const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
-            cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
+        if (!FUSED) {
+            for (int c = tid; c < BM * CH; c += NW * 32) {          // Q rows
+                const int r = c / CH, ch = c % CH;
+                const int R = row0 + r;
+                const bool valid = R < rows_total;
+                const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
+                cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
+            }
+            load_kv(0);
+            cp_async_commit();
+            if (n_my > 1) load_kv(1);
+            cp_async_commit();
+        } else {
+            // (one token per sequence: q_len 1, rows_total G <= 16, row0 0, k_hi the token's position)
+            const int new_tile = k_hi / BN - tile_begin;              // which of this CTA's tiles holds the new key
+            const bool owner = new_tile >= 0 && new_tile < n_my;
+            const bool late = owner && new_tile < 2;                  // that tile is among the two copied up front
+            if (!late) {
+                load_kv(0);
+                cp_async_commit();
+                if (n_my > 1) load_kv(1);
+                cp_async_commit();
+            }
+            constexpr int half = HD / 2;
+            const int heads_total = p.nh + 2 * p.nkv;
+            const __nv_bfloat16 * tok_in = p.qkv + (size_t) q0 * heads_total * HD;
+            const float2 * tab = p.table != nullptr ? p.table + (size_t) q0 * half : nullptr;
+            const int p0 = 2 * lane;                                  // a lane owns pairs p0 and p0 + 1 (HD <= 128)
+            // normalise and rotate one head; dst0/dst1 receive elements (p0, p0 + 1) and (half + p0, half + p0 + 1)
+            auto norm_rope = [&](const __nv_bfloat16 * src, const float * w, bool rotate, __nv_bfloat16 * dst0, __nv_bfloat16 * dst1) {
+                float2 a = make_float2(0.0f, 0.0f), c = make_float2(0.0f, 0.0f);
+                float ss = 0.0f;
+                if (p0 < half) {
+                    a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(src + p0));
+                    c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(src + half + p0));
+                    ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+                }
+                float inv = 1.0f;
+                if (w != nullptr) {
+                    ss = warp_sum(ss);
+                    inv = rsqrtf(ss / (float) HD + p.eps);
+                }
+                if (p0 < half) {
+                    if (w != nullptr) {
+                        const float2 wl = *reinterpret_cast<const float2 *>(w + p0), wh = *reinterpret_cast<const float2 *>(w + half + p0);
+                        a.x = a.x * inv * wl.x; a.y = a.y * inv * wl.y;
+                        c.x = c.x * inv * wh.x; c.y = c.y * inv * wh.y;
+                    }
+                    if (rotate) {
+                        const float4 cssn = *reinterpret_cast<const float4 *>(tab + p0);      // cos0 sin0 cos1 sin1
+                        const float2 r0 = make_float2(a.x * cssn.x - c.x * cssn.y, a.y * cssn.z - c.y * cssn.w);
+                        const float2 r1 = make_float2(a.x * cssn.y + c.x * cssn.x, a.y * cssn.w + c.y * cssn.z);
+                        a = r0; c = r1;
+                    }
+                    *reinterpret_cast<__nv_bfloat162 *>(dst0) = __floats2bfloat162_rn(a.x, a.y);
+                    *reinterpret_cast<__nv_bfloat162 *>(dst1) = __floats2bfloat162_rn(c.x, c.y);
+                }
+            };
+            for (int c = tid; c < BM * CH; c += NW * 32) {              // rows beyond the G heads are zero
+                const int r = c / CH, ch = c % CH;
+                if (r >= rows_total) *reinterpret_cast<uint4 *>(sQ + swz<HD>(r, ch)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            for (int r = warp; r < rows_total; r += NW) {
+                const __nv_bfloat16 * src = tok_in + (size_t) (kvh * G + r) * HD;
+                __nv_bfloat16 * d0 = reinterpret_cast<__nv_bfloat16 *>(sQ + swz<HD>(r, p0 >> 3)) + (p0 & 7);
+                __nv_bfloat16 * d1 = reinterpret_cast<__nv_bfloat16 *>(sQ + swz<HD>(r, (half + p0) >> 3)) + (p0 & 7);
+                norm_rope(src, p.q_weight, tab != nullptr, d0, d1);
+            }
+            if (owner && p.write_kv) {
+                const int slot = p.slots[q0];
+                if (slot >= 0 && slot < p.num_pages * p.page_size) {
+                    const int page = slot / p.page_size, off = slot - page * p.page_size;
+                    const size_t cell = (((size_t) page * p.nkv + kvh) * p.page_size + off) * HD;
+                    if (warp == 0) {
+                        const __nv_bfloat16 * src = tok_in + (size_t) (p.nh + kvh) * HD;
+                        norm_rope(src, p.k_weight, tab != nullptr, p.k_cache_w + cell + p0, p.k_cache_w + cell + half + p0);
+                    } else if (warp == 1) {
+                        const __nv_bfloat16 * src = tok_in + (size_t) (p.nh + p.nkv + kvh) * HD;
+                        if (lane < CH) *reinterpret_cast<uint4 *>(p.v_cache_w + cell + lane * 8) = *reinterpret_cast<const uint4 *>(src + lane * 8);
+                    }
+                    __threadfence();          // the copies below read these rows back through L2
+                }
+            }
+            __syncthreads();
+            if (late) {
+                load_kv(0);
+                cp_async_commit();
+                if (n_my > 1) load_kv(1);
+                cp_async_commit();
+            }
         }
-        load_kv(0);
-        cp_async_commit();
-        if (n_my > 1) load_kv(1);
-        cp_async_commit();
 
         unsigned qf[KS][4];
         for (int i = 0; i < n_my; i++) {
@@ -557,6 +667,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     const int mR = row0 + mr;
     const bool m_ok = mR < rows_total;
     const size_t row_idx = m_ok ? (size_t) (q0 + mR / G) * p.nh + kvh * G + mR % G : 0;
+    float * cO = ml + NW * BM * 2;                           // [16][HD] unnormalised output of this CTA (cluster form)
+    float * cML = cO + BM * HD;                              // [16][2]  its max and sum
     if (m_ok) {
         float mw[NW], m = -INFINITY;
 #pragma unroll
@@ -578,13 +690,47 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
                 v0 += sw[w] * x.x;
                 v1 += sw[w] * x.y;
             }
-            if (p.n_split == 1)
+            if (CLUSTER)
+                *reinterpret_cast<float2 *>(cO + mr * HD + d) = make_float2(v0, v1);
+            else if (p.n_split == 1)
                 *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
             else
                 *reinterpret_cast<float2 *>(p.part_o + (row_idx * p.n_split + split) * HD + d) = make_float2(v0 * inv, v1 * inv);
         }
-        if (p.n_split > 1 && mpart == 0)        // log-sum-exp in base 2; -inf marks a part that saw no key
+        if (CLUSTER) {
+            if (mpart == 0) { cML[mr * 2] = m; cML[mr * 2 + 1] = l; }
+        } else if (p.n_split > 1 && mpart == 0)        // log-sum-exp in base 2; -inf marks a part that saw no key
             p.part_lse[row_idx * p.n_split + split] = l > 0.0f ? m * p.scale_log2 + log2f(l) : -INFINITY;
+    }
+    if (CLUSTER) {
+        // Every CTA of the cluster gets here (none returns early: they share the row tile), so the barriers
+        // are complete.  CTA `rank` merges columns [rank, rank + 1) * ceil(HD / n_split) of every row.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int ns = p.n_split, rank = (int) cluster.block_rank();
+        const int cols = (HD + ns - 1) / ns;
+        const int n_rows = min(BM, rows_total - row0);
+        for (int idx = tid; idx < n_rows * cols; idx += NW * 32) {
+            const int r = idx / cols, d = rank * cols + idx % cols;
+            if (d >= HD) continue;
+            float mc[8], m = -INFINITY;
+            for (int c = 0; c < ns; c++) {
+                mc[c] = cluster.map_shared_rank(cML, c)[r * 2];
+                m = fmaxf(m, mc[c]);
+            }
+            float l = 0.0f, v = 0.0f;
+            for (int c = 0; c < ns; c++) {                   // in the order of the parts, whatever their timing
+                if (mc[c] == -INFINITY) continue;
+                const float f = exp2f((mc[c] - m) * p.scale_log2);
+                l += f * cluster.map_shared_rank(cML, c)[r * 2 + 1];
+                v += f * cluster.map_shared_rank(cO, c)[r * HD + d];
+            }
+            const int R = row0 + r;
+            const size_t ri = (size_t) (q0 + R / G) * p.nh + kvh * G + R % G;
+            p.out[ri * HD + d] = __float2bfloat16_rn(l > 0.0f ? v / l : 0.0f);
+        }
+        cluster.sync();                                      // nobody leaves while its shared memory is being read
+        return;
     }
     if (p.n_split == 1) return;
 
@@ -626,17 +772,31 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     if (tid == 0) *counter = 0;
 }
 
-template <int HD>
+template <int HD, bool CLUSTER, bool FUSED = false>
 static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
     const size_t smem = (size_t) 16 * HD * 2 + 2 * 3 * BN * HD * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
         configured = true;
     }
     dim3 grid((max_rows + 15) / 16, p.nkv, S * p.n_split);
-    return iian_launch(attention_decode_kernel<HD>, grid, dim3(128), smem, stream, p);
+    if (!CLUSTER) return iian_launch(attention_decode_kernel<HD, CLUSTER, FUSED>, grid, dim3(128), smem, stream, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned) p.n_split;       // the parts of one row tile are consecutive in z
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, CLUSTER, FUSED>, p);
+    return e == cudaSuccess ? IIAN_OK : 1000 + (int) e;
 }
 
 // merge the n_split partial results of every (token, head): one warp per row
@@ -688,8 +848,9 @@ static int launch_attention(const AttnParams & p, int S, int max_rows, cudaStrea
 using namespace iian;
 
 // Scratch needed for n_split > 1: part_o = N * nh * n_split * hd floats, part_lse = N * nh * n_split floats,
-// and for the decode form (small_tiles) counters = S * nkv * ceil(max_q_len * nh / nkv / 16) ints that are
-// zero before the first launch (the kernel leaves them zero).
+// and for the decode form (small_tiles 1) counters = S * nkv * ceil(max_q_len * nh / nkv / 16) ints that are
+// zero before the first launch (the kernel leaves them zero).  small_tiles 2 is the decode form with the parts
+// of a row tile merged inside a thread-block cluster: n_split 2 to 8, no scratch at all.
 IIAN_API int iian_attention_mma(
     const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
     int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
@@ -698,8 +859,10 @@ IIAN_API int iian_attention_mma(
     if (N <= 0 || S <= 0) return IIAN_OK;
     if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
-    if (n_split > 1 && (part_o == nullptr || part_lse == nullptr)) return IIAN_ERR_SHAPE;
-    if (n_split > 1 && small_tiles && counters == nullptr) return IIAN_ERR_SHAPE;
+    const bool cluster = small_tiles == 2 && n_split > 1;   // decode form, parts merged inside a thread-block cluster
+    if (cluster && n_split > 8) return IIAN_ERR_SHAPE;
+    if (n_split > 1 && !cluster && (part_o == nullptr || part_lse == nullptr)) return IIAN_ERR_SHAPE;
+    if (n_split > 1 && !cluster && small_tiles && counters == nullptr) return IIAN_ERR_SHAPE;
     if ((long long) S * n_split > 65535 || nkv > 65535) return IIAN_ERR_LIMIT;
     AttnParams p;
     p.q = (const __nv_bfloat16 *) q; p.k_cache = (const __nv_bfloat16 *) k_cache; p.v_cache = (const __nv_bfloat16 *) v_cache;
@@ -707,16 +870,55 @@ IIAN_API int iian_attention_mma(
     p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_blocks = max_blocks;
     p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.n_split = n_split;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.k_cache_w = nullptr; p.v_cache_w = nullptr; p.qkv = nullptr; p.q_weight = nullptr; p.k_weight = nullptr;
+    p.table = nullptr; p.slots = nullptr; p.eps = 0.0f; p.write_kv = 0;
     const int max_rows = max_q_len * (nh / nkv);
     int rc;
-    if (hd == 128) rc = small_tiles ? launch_decode<128>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
-    else rc = small_tiles ? launch_decode<64>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
+    if (cluster) rc = hd == 128 ? launch_decode<128, true>(p, S, max_rows, stream) : launch_decode<64, true>(p, S, max_rows, stream);
+    else if (hd == 128) rc = small_tiles ? launch_decode<128, false>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
+    else rc = small_tiles ? launch_decode<64, false>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
     if (rc != IIAN_OK || n_split == 1 || small_tiles) return rc;      // the decode form merges its parts itself
     const int rows = N * nh;
     const int warps = 4;
     if (hd == 128) attention_combine_kernel<128><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(part_o, part_lse, (__nv_bfloat16 *) out, rows, n_split);
     else attention_combine_kernel<64><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(part_o, part_lse, (__nv_bfloat16 *) out, rows, n_split);
     return iian_launch_status();
+}
+
+// Decode attention straight from the Q|K|V projection, for steps in which every sequence has exactly one
+// token (token i belongs to sequence i, N == S): per-head RMSNorm (weights may be null: no norm), NEOX
+// rotation over the whole head with the (cos, sin) table [N, hd / 2] (null: no rotation), the write of the
+// new key and value to cache cell slots[i] (write_kv; a negative slot stores nothing), and attention over
+// the cache, in one launch.  Scratch as for iian_attention_mma's decode form; cluster != 0 (n_split 2..8)
+// needs none.  Up to 16 query heads per KV head.
+IIAN_API int iian_attention_decode_fused(
+    const void * qkv, void * k_cache, void * v_cache, void * out, float * part_o, float * part_lse, int * counters,
+    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int S, int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window, int n_split, int cluster,
+    const float * q_weight, const float * k_weight, const float * table, const int * slots, float eps, int write_kv,
+    cudaStream_t stream) {
+    if (S <= 0) return IIAN_OK;
+    if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
+    if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
+    const bool cl = cluster != 0 && n_split > 1;
+    if (cl && n_split > 8) return IIAN_ERR_SHAPE;
+    if (n_split > 1 && !cl && (part_o == nullptr || part_lse == nullptr || counters == nullptr)) return IIAN_ERR_SHAPE;
+    if (write_kv && slots == nullptr) return IIAN_ERR_SHAPE;
+    if ((long long) S * n_split > 65535 || nkv > 65535) return IIAN_ERR_LIMIT;
+    if (((uintptr_t) qkv & 15) || ((uintptr_t) k_cache & 15) || ((uintptr_t) v_cache & 15) || ((uintptr_t) table & 15) ||
+        ((uintptr_t) q_weight & 7) || ((uintptr_t) k_weight & 7)) return IIAN_ERR_ALIGN;
+    AttnParams p;
+    p.q = nullptr; p.k_cache = (const __nv_bfloat16 *) k_cache; p.v_cache = (const __nv_bfloat16 *) v_cache;
+    p.out = (__nv_bfloat16 *) out; p.part_o = part_o; p.part_lse = part_lse; p.counters = counters;
+    p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.n_split = n_split;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.k_cache_w = (__nv_bfloat16 *) k_cache; p.v_cache_w = (__nv_bfloat16 *) v_cache;
+    p.qkv = (const __nv_bfloat16 *) qkv; p.q_weight = q_weight; p.k_weight = k_weight;
+    p.table = (const float2 *) table; p.slots = slots; p.eps = eps; p.write_kv = write_kv;
+    const int max_rows = nh / nkv;
+    if (cl) return hd == 128 ? launch_decode<128, true, true>(p, S, max_rows, stream) : launch_decode<64, true, true>(p, S, max_rows, stream);
+    return hd == 128 ? launch_decode<128, false, true>(p, S, max_rows, stream) : launch_decode<64, false, true>(p, S, max_rows, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

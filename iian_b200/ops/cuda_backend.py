@@ -71,7 +71,10 @@ _sigs_done = set()
 
 # Programmatic dependent launch for the decode-path kernels (see csrc/common.cuh).  Measured on the whole
 # decode step it does not pay (4.57 ms against 4.33 ms at batch 8), so it is off unless IIAN_PDL=1.
-PDL = os.environ.get("IIAN_PDL", "0") not in ("0", "false", "off")
+# IIAN_PDL may also name the kernel libraries whose launches get the attribute ("gemm_skinny,attention_mma").
+_PDL_ENV = os.environ.get("IIAN_PDL", "0")
+PDL = _PDL_ENV not in ("0", "false", "off")
+_PDL_LIBS = None if _PDL_ENV in ("0", "false", "off", "1", "true", "on") else {n.strip() for n in _PDL_ENV.split(",")}
 _pdl_set = set()
 
 
@@ -82,7 +85,7 @@ def _fn(lib_name: str, fn_name: str, argtypes):
         if hasattr(lib, "iian_set_pdl"):
             lib.iian_set_pdl.argtypes = [c_int]
             lib.iian_set_pdl.restype = None
-            lib.iian_set_pdl(1 if PDL else 0)
+            lib.iian_set_pdl(1 if PDL and (_PDL_LIBS is None or lib_name in _PDL_LIBS) else 0)
     fn = getattr(lib, fn_name)
     key = (lib_name, fn_name)
     if key not in _sigs_done:
@@ -431,6 +434,7 @@ class CudaKernels:
                                          scale=scale, window=window)
 
     DECODE_SLOTS = 148 * 2         # SMs x resident CTAs of the decode kernel
+    CLUSTER_MERGE = os.environ.get("IIAN_ATTENTION_CLUSTER", "1") not in ("0", "false", "off")
     MAX_SPLITS = 32
     _scratch = {}
     _scratch_keep = []
@@ -442,8 +446,10 @@ class CudaKernels:
         three key tiles, since the last CTA of a row reads every part back."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
-        n = min(self.DECODE_SLOTS // base, -(-tiles // 3), self.MAX_SPLITS)
-        return max(1, n)
+        n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 3), self.MAX_SPLITS))
+        if n <= 8:                       # 2, 4 or 8 parts merge inside a thread-block cluster
+            n = 1 << (n.bit_length() - 1)
+        return n
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
         t = self._scratch.get(device)
@@ -465,7 +471,11 @@ class CudaKernels:
         return t
 
     def paged_attention_mma(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
-                            n_split: Optional[int] = None, small_tiles: Optional[bool] = None) -> None:
+                            n_split: Optional[int] = None, small_tiles: Optional[bool] = None,
+                            cluster: Optional[bool] = None) -> None:
+        """``small_tiles``: the decode form (rows of one token, keys split over the warps); ``cluster``: its
+        parts merge through the shared memory of a thread-block cluster (2, 4 or 8 parts) instead of scratch
+        memory.  None: chosen from the step."""
         n = q.shape[0]
         if k_cache.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("paged_attention_mma: bfloat16 only")
@@ -476,8 +486,11 @@ class CudaKernels:
             small_tiles = decode
         if n_split is None:
             n_split = getattr(meta, "n_split", None) or (self.attention_splits(meta.num_seqs, num_kv_heads, meta.max_ctx) if decode else 1)
+        if cluster is None:
+            cluster = self.CLUSTER_MERGE
+        cluster = bool(cluster and small_tiles and n_split in (2, 4, 8))
         part_o = part_lse = counters = 0
-        if n_split > 1:
+        if n_split > 1 and not cluster:
             rows = n * num_heads
             scratch = self.attention_scratch(q.device, rows * n_split * (head_dim + 1))
             part_o = scratch.data_ptr()
@@ -493,9 +506,59 @@ class CudaKernels:
                   part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
                   num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split,
-                  1 if small_tiles else 0, _stream()), "attention_mma")
+                  (2 if cluster else 1) if small_tiles else 0, _stream()), "attention_mma")
         if n_split > 1 and not small_tiles:
             LAUNCHES[0] += 1
+
+    FUSED_DECODE = os.environ.get("IIAN_FUSED_DECODE_ATTENTION", "1") not in ("0", "false", "off")
+
+    def can_fuse_decode_attention(self, qkv, meta, *, num_heads, num_kv_heads, head_dim, rot_dim, rope_style, bias) -> bool:
+        """Whether ``attention_decode_fused`` covers this step: one token per sequence, bfloat16, heads of 64 or
+        128, NEOX rotation over the whole head (or none), no projection bias, at most 16 heads per KV head."""
+        return (self.FUSED_DECODE and meta.decode_only and meta.num_tokens == meta.num_seqs and qkv.dtype == torch.bfloat16
+                and head_dim in (64, 128) and bias is None and rot_dim in (0, head_dim) and (rope_style == 0 or rot_dim == 0)
+                and num_kv_heads > 0 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16)
+
+    def attention_decode_fused(self, qkv, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
+                               q_weight, k_weight, eps, table, slots, write_kv: bool,
+                               n_split: Optional[int] = None, cluster: Optional[bool] = None) -> None:
+        """Per-head RMSNorm, rotation, the write of the new K and V to the cache and attention over the cache in
+        one launch, from the Q|K|V projection ``qkv`` [S, (nh + 2 nkv) * hd] of a step with one token per sequence.
+        Without ``write_kv`` the projection holds Q only ([S, nh * hd] is not accepted: pass the full width)."""
+        s_ = meta.num_seqs
+        width = (num_heads + 2 * num_kv_heads) * head_dim
+        if qkv.shape != (s_, width) or out.shape != (s_, num_heads * head_dim):
+            raise KernelError(f"attention_decode_fused: qkv {tuple(qkv.shape)} / out {tuple(out.shape)} do not fit {s_} sequences")
+        if qkv.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            raise KernelError("attention_decode_fused: bfloat16 only")
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+            raise KernelError("attention_decode_fused: cache shape does not match the head counts")
+        if table is not None and (table.dtype != torch.float32 or table.numel() != s_ * head_dim):
+            raise KernelError("attention_decode_fused: the rotation table must be float32 [S, hd / 2, 2]")
+        if n_split is None:
+            n_split = getattr(meta, "n_split", None) or self.attention_splits(s_, num_kv_heads, meta.max_ctx)
+        if cluster is None:
+            cluster = self.CLUSTER_MERGE
+        cluster = bool(cluster and 2 <= n_split <= 8)
+        part_o = part_lse = counters = 0
+        if n_split > 1 and not cluster:
+            rows = s_ * num_heads
+            scratch = self.attention_scratch(qkv.device, rows * n_split * (head_dim + 1))
+            part_o = scratch.data_ptr()
+            part_lse = part_o + rows * n_split * head_dim * 4
+            counters = self.attention_counters(qkv.device, s_ * num_kv_heads).data_ptr()
+        bt = meta.block_table
+        fn = _fn("attention_mma", "iian_attention_decode_fused",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
+        _check(fn(_cuda(qkv, "qkv"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
+                  part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], s_, num_heads, num_kv_heads, head_dim,
+                  k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split, 1 if cluster else 0,
+                  _cuda(q_weight, "q norm weight", torch.float32), _cuda(k_weight, "k norm weight", torch.float32),
+                  _cuda(table, "rotation table", torch.float32), _cuda(slots, "slots", torch.int32), eps,
+                  1 if write_kv else 0, _stream()), "attention_decode_fused")
 
     def paged_attention_generic(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale,
                                 window) -> None:

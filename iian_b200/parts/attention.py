@@ -102,8 +102,24 @@ class Attention(Mixer):
         k.linear(x, w, qkv)
         if not pos.fused:
             pos.apply(qkv, self.nh, nkv, self.hd, ctx)
-        q = ctx.buf("q", (n, self.nh, self.hd), self.dtype)
         meta = ctx.attention_meta(cache.group)
+        attn = ctx.buf("attn", (n, self.q_size), self.dtype)
+        rot_dim = pos.dim if pos.fused else 0
+        table = pos.table(ctx) if pos.fused and hasattr(pos, "table") and pos.inv_freq is not None else None
+        if (writes_cache and hasattr(k, "can_fuse_decode_attention") and (rot_dim == 0 or table is not None)
+                and k.can_fuse_decode_attention(qkv, meta, num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.hd,
+                                                rot_dim=rot_dim, rope_style=pos.style if pos.fused else 0, bias=bias)):
+            # a decode step: norm, rotation, cache write and attention in one kernel
+            k.attention_decode_fused(qkv, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
+                                     head_dim=self.hd, scale=self.scale, window=self.window,
+                                     q_weight=self.q_norm_w, k_weight=self.k_norm_w, eps=self.eps,
+                                     table=table if rot_dim else None, slots=meta.slots, write_kv=True)
+            out = ctx.buf("mixer_out", (n, self.hidden), self.dtype)
+            k.linear(attn, self.w_o, out)
+            if self.b_o is not None:
+                k.add_bias(out, self.b_o)
+            return out
+        q = ctx.buf("q", (n, self.nh, self.hd), self.dtype)
         k.qk_norm_rope_store(
             qkv, q, cache.k if writes_cache else None, cache.v if writes_cache else None,
             num_heads=self.nh, num_kv_heads=nkv, head_dim=self.hd,
@@ -111,8 +127,7 @@ class Attention(Mixer):
             inv_freq=pos.inv_freq if pos.fused else None, rot_dim=pos.dim if pos.fused else 0,
             rope_style=pos.style if pos.fused else 0,
             positions=ctx.positions, slots=meta.slots if writes_cache else None, write_kv=writes_cache, bias=bias,
-            **({"table": pos.table(ctx)} if pos.fused and hasattr(pos, "table") and pos.inv_freq is not None else {}))
-        attn = ctx.buf("attn", (n, self.q_size), self.dtype)
+            **({"table": table} if table is not None else {}))
         k.paged_attention(q, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
                           head_dim=self.hd, scale=self.scale, window=self.window)
         out = ctx.buf("mixer_out", (n, self.hidden), self.dtype)

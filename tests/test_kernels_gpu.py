@@ -426,6 +426,77 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
         K().gemm_skinny(x, w, torch.empty(65, 8, dtype=torch.bfloat16).cuda())     # more than 64 rows
 
 
+FUSED_DECODE_CASES = [
+    # nh, nkv, hd, page, ctx_lens (one new token each), window, qk_norm, rotate
+    (8, 2, 128, 16, [300, 257, 31, 1], None, True, True),
+    (32, 8, 128, 16, [1152, 64, 65], None, True, True),
+    (6, 3, 64, 8, [37, 5, 64, 129], None, True, True),
+    (16, 1, 64, 16, [500, 16], 100, False, True),
+    (4, 4, 128, 32, [2100, 33], None, True, False),
+    (12, 4, 128, 12, [130, 90, 12, 13], 33, False, False),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_DECODE_CASES)
+@pytest.mark.parametrize("mode", ["auto", "one", "cluster3", "cluster8", "scratch5"])
+def test_attention_decode_fused(case, mode):
+    """Norm, rotation, cache write and attention in one launch: the same bits as the two-kernel route (same
+    arithmetic in the same order), the same cache contents, and right against the plain formulas."""
+    nh, nkv, hd, ps, ctx_lens, window, qk_norm, rotate = case
+    S = len(ctx_lens)
+    bf = torch.bfloat16
+    # the cache holds every key but the newest; the step brings one token per sequence
+    q, kc, vc, m, _, scale = attention_case(bf, nh, nkv, hd, ps, ctx_lens, [1] * S, window, seed=9)
+    g = torch.Generator().manual_seed(77)
+    qkv = (torch.randn(S, (nh + 2 * nkv) * hd, generator=g) * 1.5).to(bf).cuda()
+    qw = (1 + 0.2 * torch.randn(hd, generator=g)).cuda() if qk_norm else None
+    kw_ = (1 + 0.2 * torch.randn(hd, generator=g)).cuda() if qk_norm else None
+    inv = torch.pow(torch.tensor(1e4, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().cuda()
+    table = None
+    if rotate:
+        table = torch.empty(S, hd // 2, 2).cuda()
+        K().rotary_table(inv, m.positions, hd // 2, table)
+    slots = torch.tensor([int(m.block_table[i, (c - 1) // ps]) * ps + (c - 1) % ps for i, c in enumerate(ctx_lens)],
+                         dtype=torch.int32).cuda()
+    # route A: two kernels
+    kc_a, vc_a = kc.clone(), vc.clone()
+    qa = torch.empty(S, nh, hd, dtype=bf).cuda()
+    K().qk_norm_rope_store(qkv, qa, kc_a, vc_a, num_heads=nh, num_kv_heads=nkv, head_dim=hd, q_weight=qw, k_weight=kw_,
+                           eps=1e-6, inv_freq=inv if rotate else None, rot_dim=hd if rotate else 0, rope_style=0,
+                           positions=m.positions, slots=slots, write_kv=True, **({"table": table} if rotate else {}))
+    out_a = torch.empty(S, nh * hd, dtype=bf).cuda()
+    K().paged_attention_mma(qa, kc_a, vc_a, out_a, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale, window=window,
+                            n_split=1, small_tiles=True)
+    # route B: fused
+    kw = {"auto": {}, "one": dict(n_split=1), "cluster3": dict(n_split=3, cluster=True), "cluster8": dict(n_split=8, cluster=True),
+          "scratch5": dict(n_split=5, cluster=False)}[mode]
+    for _ in range(2):       # twice: the scratch route leaves its counters at zero
+        kc_b, vc_b = kc.clone(), vc.clone()
+        out_b = torch.full((S, nh * hd), float("nan"), dtype=bf).cuda()
+        K().attention_decode_fused(qkv, kc_b, vc_b, out_b, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale,
+                                   window=window, q_weight=qw, k_weight=kw_, eps=1e-6, table=table, slots=slots, write_kv=True, **kw)
+        assert torch.equal(kc_a, kc_b) and torch.equal(vc_a, vc_b)
+        if kw.get("n_split") == 1:
+            assert torch.equal(out_a, out_b)
+        assert (out_a.float() - out_b.float()).abs().max() < tol(bf, max(1.0, out_a.float().abs().max().item()))
+    # against the plain formulas in float64, from the caches route A left
+    x = qkv.double().cpu().view(S, nh + 2 * nkv, hd)
+    for i, c in enumerate(ctx_lens):
+        qh = x[i, :nh]
+        if qk_norm:
+            qh = plain.rms_norm(qh, qw.double().cpu(), 1e-6)
+        if rotate:
+            qh = plain.rope_neox(qh.unsqueeze(0), torch.tensor([c - 1]), 1e4, hd).squeeze(0)
+        qh = qh.to(bf).double()
+        cells = [int(m.block_table[i, j // ps]) * ps + j % ps for j in range(c)]
+        kk = torch.stack([kc_a.view(-1, nkv, ps, hd)[cell // ps, :, cell % ps] for cell in cells]).double().cpu()
+        vv = torch.stack([vc_a.view(-1, nkv, ps, hd)[cell // ps, :, cell % ps] for cell in cells]).double().cpu()
+        qfull = torch.zeros(c, nh, hd, dtype=torch.float64)
+        qfull[-1] = qh
+        want = plain.attention(qfull, kk, vv, scale, window)[-1].reshape(nh * hd)
+        assert (out_b[i].double().cpu() - want).abs().max() < tol(bf, max(1.0, want.abs().max().item()))
+
+
 MMA_CASES = [
     # nh, nkv, hd, page, ctx_lens, q_lens, window
     (8, 2, 128, 16, [300, 257, 31], [1, 1, 1], None),
@@ -441,7 +512,7 @@ MMA_CASES = [
 
 @pytest.mark.parametrize("case", MMA_CASES)
 @pytest.mark.parametrize("standout", [False, True])
-@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles"])
+@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles", "cluster2", "cluster4", "cluster8", "split4_scratch"])
 def test_paged_attention_mma(case, standout, mode):
     nh, nkv, hd, ps, ctx_lens, q_lens, window = case
     dtype = torch.bfloat16
@@ -452,6 +523,10 @@ def test_paged_attention_mma(case, standout, mode):
         kw = dict(n_split=5, small_tiles=True)
     elif mode == "big_tiles":
         kw = dict(n_split=1, small_tiles=False)
+    elif mode.startswith("cluster"):      # the parts of a row tile merge through a cluster's shared memory
+        kw = dict(n_split=int(mode[7:]), small_tiles=True, cluster=True)
+    elif mode == "split4_scratch":        # the same split merged through scratch memory by the last CTA
+        kw = dict(n_split=4, small_tiles=True, cluster=False)
     K().paged_attention_mma(q, kc, vc, out, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale, window=window, **kw)
     err = (out.double().cpu() - want).abs().max().item()
     assert err < tol(dtype, max(1.0, want.abs().max().item())), err
