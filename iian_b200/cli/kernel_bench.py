@@ -41,6 +41,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0: the engine's choice)")
+    ap.add_argument("--stages", type=int, default=0, help="decode attention: shared-memory tiles per CTA (2 or 3; 0: the default)")
     ap.add_argument("--no-cluster", action="store_true", help="decode attention: merge key splits through scratch memory")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -55,6 +56,8 @@ def main(argv=None) -> int:
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 2
     k = CudaKernels()
+    if args.stages:
+        k.set_decode_stages(args.stages)
     dev = torch.device("cuda:0")
     bf = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(0)

@@ -360,9 +360,11 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
 // token's own position also normalises and rotates the new key, writes it and the new value to the cache,
 // fences, and only then copies that tile: it reads its own write.  This saves a launch and a round trip of
 // Q through memory.
-template <int HD, bool CLUSTER, bool FUSED>
-__global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams p) {
-    constexpr int NW = 4, BM = 16, STAGES = 3;
+// STAGES: tiles of shared memory per CTA.  Three keep two tiles in flight; two leave room for a third CTA
+// on the SM, which pays when a step's CTAs then fit the GPU at once with fewer tiles each.
+template <int HD, bool CLUSTER, bool FUSED, int STAGES>
+__global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_kernel(const AttnParams p) {
+    constexpr int NW = 4, BM = 16;
     constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
     constexpr int TILE_BYTES = BN * HD * 2;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -432,6 +434,14 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
         }
     };
 
+    auto load_ahead = [&]() {                                // the first STAGES - 1 tiles, one copy group each
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; st++) {
+            if (st < n_my) load_kv(st);
+            cp_async_commit();
+        }
+    };
+
     float o[DT][4];
 #pragma unroll
     for (int i = 0; i < DT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -449,9 +459,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     // Everything up to here reads only the step's integer buffers, which were uploaded before the first
     // kernel of the step; Q and the newest K/V rows come from the kernel before this one.
     if (n_my > 0) {
-        lookup_rows(tile_begin, 0);
-        lookup_rows(tile_begin + 1, 1);
-        lookup_rows(tile_begin + 2, 2);
+#pragma unroll
+        for (int st = 0; st < STAGES; st++) lookup_rows(tile_begin + st, st);
     }
     pdl_wait();
     if (n_my > 0) {
@@ -464,21 +473,13 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
                 const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
                 cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
             }
-            load_kv(0);
-            cp_async_commit();
-            if (n_my > 1) load_kv(1);
-            cp_async_commit();
+            load_ahead();
         } else {
             // (one token per sequence: q_len 1, rows_total G <= 16, row0 0, k_hi the token's position)
             const int new_tile = k_hi / BN - tile_begin;              // which of this CTA's tiles holds the new key
             const bool owner = new_tile >= 0 && new_tile < n_my;
-            const bool late = owner && new_tile < 2;                  // that tile is among the two copied up front
-            if (!late) {
-                load_kv(0);
-                cp_async_commit();
-                if (n_my > 1) load_kv(1);
-                cp_async_commit();
-            }
+            const bool late = owner && new_tile < STAGES - 1;         // that tile is among those copied up front
+            if (!late) load_ahead();
             constexpr int half = HD / 2;
             const int heads_total = p.nh + 2 * p.nkv;
             const __nv_bfloat16 * tok_in = p.qkv + (size_t) q0 * heads_total * HD;
@@ -540,21 +541,16 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
                 }
             }
             __syncthreads();
-            if (late) {
-                load_kv(0);
-                cp_async_commit();
-                if (n_my > 1) load_kv(1);
-                cp_async_commit();
-            }
+            if (late) load_ahead();
         }
 
         unsigned qf[KS][4];
         for (int i = 0; i < n_my; i++) {
-            if (i + 2 < n_my) load_kv((i + 2) % STAGES);
+            if (i + STAGES - 1 < n_my) load_kv((i + STAGES - 1) % STAGES);
             cp_async_commit();
-            cp_async_wait<2>();
+            cp_async_wait<STAGES - 1>();
             __syncthreads();
-            lookup_rows(tile_begin + i + 3, i % STAGES);         // this tile's copies were issued two iterations ago
+            lookup_rows(tile_begin + i + STAGES, i % STAGES);    // this tile's copies were issued earlier
             if (i == 0) {
 #pragma unroll
                 for (int ks = 0; ks < KS; ks++)
@@ -772,17 +768,17 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     if (tid == 0) *counter = 0;
 }
 
-template <int HD, bool CLUSTER, bool FUSED = false>
-static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
-    const size_t smem = (size_t) 16 * HD * 2 + 2 * 3 * BN * HD * 2;
+template <int HD, bool CLUSTER, bool FUSED, int STAGES>
+static int launch_decode_st(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
+    const size_t smem = (size_t) 16 * HD * 2 + 2 * STAGES * BN * HD * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
         configured = true;
     }
     dim3 grid((max_rows + 15) / 16, p.nkv, S * p.n_split);
-    if (!CLUSTER) return iian_launch(attention_decode_kernel<HD, CLUSTER, FUSED>, grid, dim3(128), smem, stream, p);
+    if (!CLUSTER) return iian_launch(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES>, grid, dim3(128), smem, stream, p);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(128);
@@ -795,8 +791,16 @@ static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t
     attr[0].val.clusterDim.z = (unsigned) p.n_split;       // the parts of one row tile are consecutive in z
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, CLUSTER, FUSED>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, CLUSTER, FUSED, STAGES>, p);
     return e == cudaSuccess ? IIAN_OK : 1000 + (int) e;
+}
+
+static int g_decode_stages = 2;
+template <int HD, bool CLUSTER, bool FUSED = false>
+static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
+    // unsplit keys mean many sequences, each CTA walking a whole context: the deeper pipeline pays there
+    if (g_decode_stages == 3 || p.n_split == 1) return launch_decode_st<HD, CLUSTER, FUSED, 3>(p, S, max_rows, stream);
+    return launch_decode_st<HD, CLUSTER, FUSED, 2>(p, S, max_rows, stream);
 }
 
 // merge the n_split partial results of every (token, head): one warp per row
@@ -851,6 +855,13 @@ using namespace iian;
 // and for the decode form (small_tiles 1) counters = S * nkv * ceil(max_q_len * nh / nkv / 16) ints that are
 // zero before the first launch (the kernel leaves them zero).  small_tiles 2 is the decode form with the parts
 // of a row tile merged inside a thread-block cluster: n_split 2 to 8, no scratch at all.
+// Tiles of shared memory per CTA of the decode form: 2 (three CTAs per SM) or 3 (two CTAs, two tiles in flight).
+IIAN_API int iian_attention_decode_stages(int stages) {
+    if (stages != 2 && stages != 3) return IIAN_ERR_SHAPE;
+    g_decode_stages = stages;
+    return IIAN_OK;
+}
+
 IIAN_API int iian_attention_mma(
     const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
     int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,

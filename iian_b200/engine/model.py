@@ -166,8 +166,14 @@ class Model:
         order = self.spec.order
         for idx, call in enumerate(order):
             select = ctx.out_rows if idx == len(order) - 1 else None
-            residual, delta = self.blocks[call.layer].forward(
-                residual, delta, ctx, storage.view(call.cache), call.writes_cache, select)
+            block = self.blocks[call.layer]
+            extra = {}
+            if idx + 1 < len(order) and getattr(block, "accepts_next_norm", False):
+                # the block after this one: its first norm may ride in this block's last product
+                nxt = self.blocks[order[idx + 1].layer]
+                if getattr(nxt, "accepts_next_norm", False):
+                    extra = {"next_norm": nxt.mixer_norm, "next_consumer": nxt.mixer}
+            residual, delta = block.forward(residual, delta, ctx, storage.view(call.cache), call.writes_cache, select, **extra)
         if not order:
             from .. import ops
             sel = ctx.buf("residual_rows", (ctx.out_rows.shape[0], residual.shape[1]), residual.dtype)

@@ -163,15 +163,61 @@ class CudaKernels:
                "add_bias")
 
     # ---- matrix products -----------------------------------------------------------------
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-        """out[n, m] = sum_k x[n, k] * w[m, k]."""
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_scale=None, residual_norm=None) -> None:
+        """out[n, m] = sum_k x[n, k] * w[m, k].  ``row_scale`` (ops.fused.RowScale) and ``residual_norm``
+        (ops.fused.ResidualNorm) ask for the fused forms; ``can_fuse_norm`` says whether they are available."""
         n, k = x.shape
         m = w.shape[0]
         if w.shape[1] != k or out.shape != (n, m):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
         if n == 0:
             return
+        if row_scale is not None or residual_norm is not None:
+            self.gemm_skinny_fused(x, w, out, 2 if residual_norm is not None else 0, row_scale, residual_norm)
+            return
         self._linear_dispatch(x, w, out, n, m, k)
+
+    FUSE_NORM = os.environ.get("IIAN_FUSE_NORM", "1") not in ("0", "false", "off")
+
+    def can_fuse_norm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether the product of ``x`` with ``w`` can carry a RowScale or a ResidualNorm (the weight-streaming
+        kernel's range: up to 8 rows of bfloat16)."""
+        n, k = x.shape
+        return self.FUSE_NORM and self._skinny_ok(x, w, n, k)
+
+    def norm_parts(self, w: torch.Tensor) -> int:
+        """Parts in which a ResidualNorm product with weight ``w`` leaves the sums of squares."""
+        return -(-w.shape[0] // 16)
+
+    def gemm_skinny_fused(self, x, w, out, epilogue: int, row_scale=None, residual_norm=None) -> None:
+        n, k = x.shape
+        m = w.shape[0]
+        if not self._skinny_ok(x, w, n, k):
+            raise KernelError("linear: the fused forms need up to 8 rows of bfloat16, K a multiple of 32")
+        in_p = in_tiles = 0
+        inv_w = eps = 0.0
+        if row_scale is not None:
+            if row_scale.partials.dtype != torch.float32 or row_scale.partials.shape[0] != n:
+                raise KernelError("linear: RowScale partials must be float32 [rows, parts]")
+            in_p, in_tiles = _cuda(row_scale.partials, "row-scale partials"), row_scale.partials.shape[1]
+            inv_w, eps = 1.0 / row_scale.width, row_scale.eps
+        res = nw = out_p = 0
+        if residual_norm is not None:
+            rn = residual_norm
+            if (rn.residual.shape != (n, m) or rn.residual.dtype != torch.float32 or rn.weight.numel() != m
+                    or rn.partials.shape != (n, self.norm_parts(w)) or out.dtype != torch.bfloat16):
+                raise KernelError("linear: ResidualNorm operands do not fit the product")
+            res, nw = _cuda(rn.residual, "residual", torch.float32), _cuda(rn.weight, "norm weight", torch.float32)
+            out_p = _cuda(rn.partials, "norm partials", torch.float32)
+        fn = _fn("gemm_skinny", "iian_gemm_skinny_fused",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_float,
+                  c_void_p, c_void_p, c_void_p, c_void_p])
+        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"), n, m, k,
+                  epilogue, in_p, in_tiles, inv_w, eps, res, nw, out_p, _stream()), "gemm_skinny_fused")
+        if self.weight_log is not None:
+            self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
+        if self.prefetcher is not None:
+            self.prefetcher.after_product(self)
 
     # rows up to which the weight-streaming kernel is used; above it the library GEMM takes over
     # (measured on B200 at the Qwen3-8B sizes: the streaming kernel wins up to 8 rows, cuBLAS from 16)
@@ -200,9 +246,12 @@ class CudaKernels:
         n, k = x.shape
         return interleave == 8 and w.shape[0] % 16 == 0 and (self._tcgen05_ok(x, w, n, k) or self._skinny_ok(x, w, n, k))
 
-    def linear_swiglu(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    def linear_swiglu(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_scale=None) -> None:
         """out[t, f] = silu(x . w_gate_f) * (x . w_up_f) for w with gate and up rows interleaved in groups of 8."""
         n, k = x.shape
+        if row_scale is not None:
+            self.gemm_skinny_fused(x, w, out, 1, row_scale, None)
+            return
         if self._tcgen05_ok(x, w, n, k):
             self.gemm_tcgen05(x, w, out, epilogue=1)
             return
@@ -248,47 +297,14 @@ class CudaKernels:
         memory pipeline idle (a row block of 16 is one CTA)."""
         return 1       # measured on B200 at the Qwen3-8B sizes: one CTA per row block is fastest for every shape
 
-    # the evenly cut form of the streaming product (csrc/gemm_skinny.cu, gemm_stream_kernel); IIAN_STREAM_GEMM=0
-    # goes back to one CTA per row tile
-    STREAM_GEMM = os.environ.get("IIAN_STREAM_GEMM", "0") not in ("0", "false", "off")
-    _stream_need = {}
-
-    def gemm_stream(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
-        """The streaming product with the work cut evenly over the SMs: up to 8 rows, K a multiple of 256."""
-        n, k = x.shape
-        m = w.shape[0]
-        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-            raise KernelError("gemm_stream: x and w must be bfloat16")
-        code = _code(out, "linear out")
-        key = (x.device, code, m, k, epilogue)
-        need = self._stream_need.get(key)
-        if need is None:
-            from ctypes import c_size_t
-            nf, ni = c_size_t(0), c_size_t(0)
-            q = _fn("gemm_skinny", "iian_gemm_stream_scratch", [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-            with torch.cuda.device(x.device):
-                _check(q(code, m, k, epilogue, ctypes.addressof(nf), ctypes.addressof(ni)), "gemm_stream")
-            need = self._stream_need[key] = (nf.value, ni.value)
-        part = self.gemm_scratch(x.device, need[0])
-        counters = self.gemm_counters(x.device, need[1])
-        fn = _fn("gemm_skinny", "iian_gemm_stream",
-                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, ctypes.c_size_t, c_void_p, ctypes.c_size_t,
-                  c_int, c_void_p])
-        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), code, n, m, k,
-                  part.data_ptr(), part.numel(), counters.data_ptr(), counters.numel(), epilogue, _stream()), "gemm_stream")
-
     def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, cfg: int = 0, ksplit: int = 0,
                     epilogue: int = 0) -> None:
         """``cfg`` picks a tile configuration (rows-per-block tiles * 100 + warps * 10 + unroll); ``ksplit``
-        the number of CTAs that share K for one row block; 0: defaults.  With both at their defaults, up to 8
-        rows and K a multiple of 256 the evenly cut kernel runs instead (``cfg=-1`` asks for it by name)."""
+        the number of CTAs that share K for one row block; 0: defaults."""
         n, k = x.shape
         m = w.shape[0]
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: x and w must be bfloat16")
-        if cfg == -1 or (cfg == 0 and ksplit <= 0 and self.STREAM_GEMM and n <= 8 and k % 256 == 0):
-            self.gemm_stream(x, w, out, epilogue)
-            return
         if ksplit <= 0:
             ksplit = 1 if epilogue else self.skinny_ksplit(n, m, k)
         part = counters = 0
@@ -433,7 +449,19 @@ class CudaKernels:
             self.paged_attention_generic(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                                          scale=scale, window=window)
 
-    DECODE_SLOTS = 148 * 2         # SMs x resident CTAs of the decode kernel
+    DECODE_STAGES = int(os.environ.get("IIAN_DECODE_STAGES", "2"))     # shared-memory tiles per CTA of the decode kernel
+    DECODE_SLOTS = 148 * (3 if DECODE_STAGES == 2 else 2)              # SMs x resident CTAs of the decode kernel
+    _stages_set = None
+
+    def set_decode_stages(self, stages: int) -> None:
+        """2: three CTAs per SM with one tile in flight each; 3: two CTAs with two tiles in flight."""
+        fn = _fn("attention_mma", "iian_attention_decode_stages", [c_int])
+        code = fn(stages)
+        if code != 0:
+            raise KernelError("attention: the decode kernel has 2 or 3 stages")
+        type(self)._stages_set = stages
+        type(self).DECODE_STAGES = stages
+        type(self).DECODE_SLOTS = 148 * (3 if stages == 2 else 2)
     CLUSTER_MERGE = os.environ.get("IIAN_ATTENTION_CLUSTER", "1") not in ("0", "false", "off")
     MAX_SPLITS = 32
     _scratch = {}
@@ -447,9 +475,7 @@ class CudaKernels:
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
         n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 3), self.MAX_SPLITS))
-        if n <= 8:                       # 2, 4 or 8 parts merge inside a thread-block cluster
-            n = 1 << (n.bit_length() - 1)
-        return n
+        return n                         # up to 8 parts merge inside a thread-block cluster
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
         t = self._scratch.get(device)
@@ -481,6 +507,8 @@ class CudaKernels:
             raise KernelError("paged_attention_mma: bfloat16 only")
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or q.numel() != n * num_heads * head_dim:
             raise KernelError("paged_attention_mma: cache / q shapes do not match the head counts")
+        if self._stages_set != self.DECODE_STAGES:
+            self.set_decode_stages(self.DECODE_STAGES)
         decode = meta.max_q_len * (num_heads // num_kv_heads) <= 16
         if small_tiles is None:
             small_tiles = decode
@@ -535,6 +563,8 @@ class CudaKernels:
             raise KernelError("attention_decode_fused: cache shape does not match the head counts")
         if table is not None and (table.dtype != torch.float32 or table.numel() != s_ * head_dim):
             raise KernelError("attention_decode_fused: the rotation table must be float32 [S, hd / 2, 2]")
+        if self._stages_set != self.DECODE_STAGES:
+            self.set_decode_stages(self.DECODE_STAGES)
         if n_split is None:
             n_split = getattr(meta, "n_split", None) or self.attention_splits(s_, num_kv_heads, meta.max_ctx)
         if cluster is None:

@@ -18,7 +18,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import KVNeed, Mixer, POSITIONS, register_mixer
+from .base import KVNeed, Mixer, POSITIONS, Prenormed, register_mixer
 
 
 @register_mixer("attention")
@@ -88,8 +88,28 @@ class Attention(Mixer):
     def kernel_libraries(self):
         return ("rope_kv", "attention_generic", "gemm_simt")
 
-    def forward(self, x: torch.Tensor, ctx, cache, writes_cache: bool) -> torch.Tensor:
+    folds_norm_out = True
+
+    def takes_prenormed(self, n_rows: int) -> bool:
         k = ops.kernels()
+        return (getattr(k, "FUSE_NORM", False) and n_rows <= getattr(k, "SKINNY_MAX_ROWS", 0) and self.hidden % 32 == 0
+                and self.dtype == torch.bfloat16 and self.w_qkv.dtype == torch.bfloat16)
+
+    def _project_out(self, k, attn: torch.Tensor, ctx, norm_out):
+        if (norm_out is not None and self.b_o is None and hasattr(k, "can_fuse_norm")
+                and k.can_fuse_norm(attn, self.w_o)):
+            return norm_out.take(k, attn, self.w_o, ctx)
+        out = ctx.buf("mixer_out", (attn.shape[0], self.hidden), self.dtype)
+        k.linear(attn, self.w_o, out)
+        if self.b_o is not None:
+            k.add_bias(out, self.b_o)
+        return out
+
+    def forward(self, x, ctx, cache, writes_cache: bool, norm_out=None):
+        k = ops.kernels()
+        scale = None
+        if isinstance(x, Prenormed):
+            x, scale = x.x, x.scale
         n = x.shape[0]
         pos = self.position
         if writes_cache:
@@ -99,7 +119,10 @@ class Attention(Mixer):
             bias = self.b_qkv[: self.q_size] if self.b_qkv is not None else None
         width = self.q_size + 2 * nkv * self.hd
         qkv = ctx.buf("qkv", (n, width), self.dtype)
-        k.linear(x, w, qkv)
+        if scale is not None:
+            k.linear(x, w, qkv, row_scale=scale)
+        else:
+            k.linear(x, w, qkv)
         if not pos.fused:
             pos.apply(qkv, self.nh, nkv, self.hd, ctx)
         meta = ctx.attention_meta(cache.group)
@@ -114,11 +137,7 @@ class Attention(Mixer):
                                      head_dim=self.hd, scale=self.scale, window=self.window,
                                      q_weight=self.q_norm_w, k_weight=self.k_norm_w, eps=self.eps,
                                      table=table if rot_dim else None, slots=meta.slots, write_kv=True)
-            out = ctx.buf("mixer_out", (n, self.hidden), self.dtype)
-            k.linear(attn, self.w_o, out)
-            if self.b_o is not None:
-                k.add_bias(out, self.b_o)
-            return out
+            return self._project_out(k, attn, ctx, norm_out)
         q = ctx.buf("q", (n, self.nh, self.hd), self.dtype)
         k.qk_norm_rope_store(
             qkv, q, cache.k if writes_cache else None, cache.v if writes_cache else None,
@@ -130,8 +149,4 @@ class Attention(Mixer):
             **({"table": table} if table is not None else {}))
         k.paged_attention(q, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
                           head_dim=self.hd, scale=self.scale, window=self.window)
-        out = ctx.buf("mixer_out", (n, self.hidden), self.dtype)
-        k.linear(attn, self.w_o, out)
-        if self.b_o is not None:
-            k.add_bias(out, self.b_o)
-        return out
+        return self._project_out(k, attn, ctx, norm_out)

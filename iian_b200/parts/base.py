@@ -26,6 +26,20 @@ Interfaces
 ``PositionEncoding``
     owned by the mixer that needs positions; the attention mixer asks it for the rotation table.
 ``Embedding.forward(tokens, ctx) -> residual`` and ``Head.forward(x, ctx) -> logits`` (float32).
+
+Optional: a norm folded into its neighbours
+-------------------------------------------
+A norm that is a factor per row and a weight per column (RMSNorm) can be carried by the matrix products on
+either side of it (``iian_b200.ops.fused``).  The arrangement offers this to parts that declare support:
+
+* a norm with ``foldable() -> (weight, eps)`` may be folded;
+* a mixer or feed-forward with ``folds_norm_out = True`` accepts ``forward(..., norm_out=request)`` where
+  ``request`` is a :class:`NormOut`; if its last product can carry it, it calls ``request.take(...)`` and returns
+  a :class:`Prenormed` instead of rows; otherwise it ignores the request and returns rows as usual;
+* a mixer or feed-forward with ``takes_prenormed(n_rows) -> bool`` true may be handed a :class:`Prenormed` as
+  ``x``: rows that still lack the factor per row, with the sums of squares from which its first product takes it.
+
+A part that declares none of this (the default) is always called with plain rows.
 """
 from __future__ import annotations
 
@@ -73,12 +87,51 @@ class Part:
         return ()
 
 
+@dataclass
+class Prenormed:
+    """The input of a sub-layer whose norm rides in the surrounding products: ``x`` = residual * norm weight in
+    the activation dtype, ``scale`` the ``ops.fused.RowScale`` that completes it, ``norm`` the norm part it
+    stands for (the residual stream already holds the sum that norm would have added)."""
+    x: torch.Tensor
+    scale: object
+    norm: object
+
+
+@dataclass
+class NormOut:
+    """A request to the part that ends a sub-layer: add your output to ``residual`` and prepare the input of
+    ``norm`` (weight ``weight``, ``eps``) in your last product."""
+    residual: torch.Tensor
+    norm: object
+    weight: torch.Tensor
+    eps: float
+    name: str                   # distinguishes the buffers of the two sub-layers of a block
+
+    def take(self, k, x: torch.Tensor, w: torch.Tensor, ctx) -> "Prenormed":
+        """Run ``x @ w.T`` with the folded epilogue and return what the next sub-layer gets."""
+        from ..ops.fused import ResidualNorm, RowScale
+        n, width = x.shape[0], w.shape[0]
+        out = ctx.buf(f"prenormed_{self.name}", (n, width), x.dtype)
+        partials = ctx.buf(f"norm_partials_{self.name}", (n, k.norm_parts(w)), torch.float32)
+        k.linear(x, w, out, residual_norm=ResidualNorm(self.residual, self.weight, partials))
+        return Prenormed(out, RowScale(partials, width, self.eps), self.norm)
+
+
 class Norm(Part):
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
+    def foldable(self):
+        """(weight float32 [H], eps) if this norm is ``x * rsqrt(mean(x^2) + eps) * weight``, else None."""
+        return None
+
 
 class Mixer(Part):
+    folds_norm_out = False
+
+    def takes_prenormed(self, n_rows: int) -> bool:
+        return False
+
     def cache_need(self):
         return None
 
@@ -87,6 +140,11 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    folds_norm_out = False
+
+    def takes_prenormed(self, n_rows: int) -> bool:
+        return False
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 

@@ -17,7 +17,7 @@ import torch
 
 from .. import ops
 from ..config.spec import LayerSpec
-from .base import FEED_FORWARDS, MIXERS, NORMS, register_block
+from .base import FEED_FORWARDS, MIXERS, NORMS, NormOut, Prenormed, register_block
 
 
 @register_block("pre_norm_residual")
@@ -35,11 +35,38 @@ class PreNormResidualBlock:
         return (("mixer_norm", self.mixer_norm), ("mixer", self.mixer),
                 ("feed_forward_norm", self.feed_forward_norm), ("feed_forward", self.feed_forward))
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx, cache, writes_cache: bool,
-                select_rows: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
-        h = self.mixer_norm.forward(residual, delta, ctx)
-        y = self.mixer.forward(h, ctx, cache, writes_cache)
-        if select_rows is not None and not getattr(ctx, "rows_identity", False):
+    accepts_next_norm = True
+
+    @staticmethod
+    def _norm_out(norm, consumer, residual: torch.Tensor, n_rows: int, name: str) -> Optional[NormOut]:
+        """A request to fold ``norm`` into the products around it, if the norm allows it and ``consumer`` (the part
+        that follows it) can take rows that still lack the factor per row."""
+        if norm is None or consumer is None:
+            return None
+        fold = norm.foldable()
+        if fold is None or not consumer.takes_prenormed(n_rows):
+            return None
+        return NormOut(residual, norm, fold[0], fold[1], name)
+
+    def forward(self, residual: torch.Tensor, delta, ctx, cache, writes_cache: bool,
+                select_rows: Optional[torch.Tensor], next_norm=None, next_consumer=None):
+        """``delta`` is the not-yet-added output of the sub-layer before this block, or a ``Prenormed`` for this
+        block's first norm (then the sum is already in ``residual``).  ``next_norm`` / ``next_consumer``: the norm
+        and the part that follow this block's feed-forward, if its last product may prepare their input."""
+        if isinstance(delta, Prenormed):
+            if delta.norm is not self.mixer_norm:
+                raise RuntimeError("block: received rows prepared for another norm")
+            h = delta
+        else:
+            h = self.mixer_norm.forward(residual, delta, ctx)
+        n_rows = residual.shape[0]
+        gathers = select_rows is not None and not getattr(ctx, "rows_identity", False)
+        request = None
+        if not gathers and self.mixer.folds_norm_out:
+            request = self._norm_out(self.feed_forward_norm, self.feed_forward, residual, n_rows, "mixer")
+        y = self.mixer.forward(h, ctx, cache, writes_cache, norm_out=request) if request is not None \
+            else self.mixer.forward(h, ctx, cache, writes_cache)
+        if gathers:
             k = ops.kernels()
             r = select_rows.shape[0]
             res_sel = ctx.buf("residual_rows", (r, residual.shape[1]), residual.dtype)
@@ -47,6 +74,9 @@ class PreNormResidualBlock:
             k.gather_rows(residual, select_rows, res_sel)
             k.gather_rows(y, select_rows, y_sel)
             residual, y = res_sel, y_sel
-        h2 = self.feed_forward_norm.forward(residual, y, ctx)
-        d = self.feed_forward.forward(h2, ctx)
+        h2 = y if isinstance(y, Prenormed) else self.feed_forward_norm.forward(residual, y, ctx)
+        request = None
+        if self.feed_forward.folds_norm_out:
+            request = self._norm_out(next_norm, next_consumer, residual, residual.shape[0], "feed_forward")
+        d = self.feed_forward.forward(h2, ctx, norm_out=request) if request is not None else self.feed_forward.forward(h2, ctx)
         return residual, d

@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import FeedForward, register_feed_forward
+from .base import FeedForward, Prenormed, register_feed_forward
 
 
 @register_feed_forward("gated_mlp")
@@ -56,16 +56,31 @@ class GatedMLP(FeedForward):
     def kernel_libraries(self):
         return ("elementwise", "gemm_simt")
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    folds_norm_out = True
+
+    def takes_prenormed(self, n_rows: int) -> bool:
         k = ops.kernels()
+        if not getattr(k, "FUSE_NORM", False) or self.interleave != 8 or self.w_gate_up.dtype != self.dtype:
+            return False
+        return n_rows <= getattr(k, "SKINNY_MAX_ROWS", 0) and self.hidden % 32 == 0 and self.dtype == torch.bfloat16
+
+    def forward(self, x, ctx, norm_out=None):
+        k = ops.kernels()
+        scale = None
+        if isinstance(x, Prenormed):
+            x, scale = x.x, x.scale
         n = x.shape[0]
         act = ctx.buf("ffn_act", (n, self.inter), self.dtype)
-        if hasattr(k, "can_fuse_swiglu") and k.can_fuse_swiglu(x, self.w_gate_up, self.interleave):
+        if scale is not None:
+            k.linear_swiglu(x, self.w_gate_up, act, row_scale=scale)
+        elif hasattr(k, "can_fuse_swiglu") and k.can_fuse_swiglu(x, self.w_gate_up, self.interleave):
             k.linear_swiglu(x, self.w_gate_up, act)            # the activation rides in the product's epilogue
         else:
             gate_up = ctx.buf("gate_up", (n, 2 * self.inter), self.dtype)
             k.linear(x, self.w_gate_up, gate_up)
             k.swiglu(gate_up, act, self.interleave)
+        if norm_out is not None and hasattr(k, "can_fuse_norm") and k.can_fuse_norm(act, self.w_down):
+            return norm_out.take(k, act, self.w_down, ctx)
         out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
         k.linear(act, self.w_down, out)
         return out

@@ -33,6 +33,9 @@ class RMSNorm(Norm):
     def kernel_libraries(self):
         return ("elementwise",)
 
+    def foldable(self):
+        return (self.weight, self.eps) if self.weight is not None else None
+
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
         out = ctx.buf("normed", residual.shape, self.dtype)
         ops.kernels().add_rms_norm(residual, delta, self.weight, self.eps, out)

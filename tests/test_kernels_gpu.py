@@ -360,58 +360,62 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch():
         assert torch.equal(one[0], full[r])
 
 
-@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,M,K_", [(1, 16, 256), (3, 70, 512), (8, 257, 768), (5, 4096, 4096), (8, 1000, 12288), (2, 15, 256),
-                                    (8, 40000, 256)])
-def test_gemm_stream(od, B, M, K_):
-    """The evenly cut streaming product: tiles that several CTAs share (few rows of weights), tiles that one
-    CTA owns (many rows), a ragged last tile; three runs give the same bits and leave the counters at zero."""
-    x = rnd(B, K_, dtype=torch.bfloat16, seed=24)
-    w = rnd(M, K_, dtype=torch.bfloat16, seed=25)
-    want = x.double().cpu() @ w.double().cpu().T
-    outs = []
-    for _ in range(3):
-        out = torch.full((B, M), float("nan"), dtype=od).cuda()
-        K().gemm_skinny(x, w, out, cfg=-1)
-        outs.append(out.clone())
-    assert (outs[0].double().cpu() - want).abs().max() < tol(od if od == torch.bfloat16 else torch.float32, want.abs().max().item()) * \
-        (1 if od == torch.bfloat16 else 10)
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
-    # the tile-per-CTA kernel stays available by configuration
-    out = torch.full((B, M), float("nan"), dtype=od).cuda()
-    K().gemm_skinny(x, w, out, cfg=184)
-    assert (out.double().cpu() - want).abs().max() < tol(od if od == torch.bfloat16 else torch.float32, want.abs().max().item()) * \
-        (1 if od == torch.bfloat16 else 10)
+@pytest.mark.parametrize("B,H,M2,K_", [(1, 64, 48, 96), (8, 4096, 6144, 4096), (5, 288, 100, 160), (3, 1024, 32, 2048)])
+def test_gemm_skinny_folded_norm(B, H, M2, K_):
+    """A product that ends a sub-layer adds to the residual, prepares residual * norm weight and leaves the sums
+    of squares in parts; the next product multiplies its rows by rsqrt(mean + eps).  Together they equal the
+    residual add, the RMSNorm and the two plain products."""
+    from iian_b200.ops.fused import ResidualNorm, RowScale
+    k = K()
+    eps = 1e-5
+    a = rnd(B, K_, dtype=torch.bfloat16, seed=50)
+    w1 = rnd(H, K_, dtype=torch.bfloat16, seed=51, std=0.05)
+    res0 = rnd(B, H, dtype=torch.float32, seed=52)
+    nw = (1 + 0.3 * rnd(H, dtype=torch.float32, seed=53)).contiguous()
+    w2 = rnd(M2, H, dtype=torch.bfloat16, seed=54, std=0.05)
+    # folded route
+    res = res0.clone()
+    xt = torch.full((B, H), float("nan"), dtype=torch.bfloat16).cuda()
+    partials = torch.full((B, k.norm_parts(w1)), float("nan")).cuda()
+    k.linear(a, w1, xt, residual_norm=ResidualNorm(res, nw, partials))
+    out = torch.full((B, M2), float("nan"), dtype=torch.bfloat16).cuda()
+    k.linear(xt, w2, out, row_scale=RowScale(partials, H, eps))
+    # plain route, float64 except for the roundings the engine makes
+    delta = (a.double().cpu() @ w1.double().cpu().T).to(torch.bfloat16).double()
+    want_res = res0.double().cpu() + delta
+    assert (res.double().cpu() - want_res).abs().max() < 1e-5 * max(1.0, want_res.abs().max().item()) + \
+        tol(torch.bfloat16, delta.abs().max().item())          # one bfloat16 rounding of the product may fall the other way
+    assert (partials.double().cpu().sum(1) - (res.double().cpu() ** 2).sum(1)).abs().max() < 1e-4 * (res.double().cpu() ** 2).sum(1).max()
+    assert (xt.double().cpu() - res.double().cpu() * nw.double().cpu()).abs().max() < tol(torch.bfloat16, (res.abs().max() * nw.abs().max()).item())
+    normed = plain.rms_norm(res.double().cpu(), nw.double().cpu(), eps)
+    want = normed @ w2.double().cpu().T
+    assert (out.double().cpu() - want).abs().max() < 2 * tol(torch.bfloat16, max(1.0, want.abs().max().item()))
+    # and the unfused kernels give the same within the same tolerance
+    res_b = res0.clone()
+    d = torch.empty(B, H, dtype=torch.bfloat16).cuda()
+    k.linear(a, w1, d)
+    h = torch.empty(B, H, dtype=torch.bfloat16).cuda()
+    k.add_rms_norm(res_b, d, nw, eps, h)
+    out_b = torch.empty(B, M2, dtype=torch.bfloat16).cuda()
+    k.linear(h, w2, out_b)
+    assert torch.equal(res_b, res)          # the residual stream is the same bits on both routes
+    assert (out.float() - out_b.float()).abs().max() < 2 * tol(torch.bfloat16, max(1.0, want.abs().max().item()))
 
 
-@pytest.mark.parametrize("B,F,K_", [(1, 16, 256), (8, 160, 512), (5, 12288, 4096), (8, 8, 1024)])
-def test_gemm_stream_swiglu_epilogue(B, F, K_):
-    x = rnd(B, K_, dtype=torch.bfloat16, seed=43)
-    wg, wu = rnd(F, K_, dtype=torch.bfloat16, seed=44, std=0.05), rnd(F, K_, dtype=torch.bfloat16, seed=45, std=0.05)
-    inter = torch.stack([wg.view(F // 8, 8, K_), wu.view(F // 8, 8, K_)], dim=1).reshape(2 * F, K_).contiguous()
+def test_gemm_skinny_row_scale_with_swiglu():
+    from iian_b200.ops.fused import RowScale
+    k = K()
+    B, H, F = 6, 512, 160
+    x = rnd(B, H, dtype=torch.bfloat16, seed=60)
+    wg, wu = rnd(F, H, dtype=torch.bfloat16, seed=61, std=0.05), rnd(F, H, dtype=torch.bfloat16, seed=62, std=0.05)
+    inter = torch.stack([wg.view(F // 8, 8, H), wu.view(F // 8, 8, H)], dim=1).reshape(2 * F, H).contiguous()
+    partials = (rnd(B, 7, dtype=torch.float32, seed=63).abs() * 100).contiguous()
+    out = torch.full((B, F), float("nan"), dtype=torch.bfloat16).cuda()
+    k.linear_swiglu(x, inter, out, row_scale=RowScale(partials, H, 1e-6))
+    rs = 1.0 / torch.sqrt(partials.double().cpu().sum(1) / H + 1e-6)
     xd = x.double().cpu()
-    want = plain.silu(xd @ wg.double().cpu().T) * (xd @ wu.double().cpu().T)
-    for _ in range(2):
-        out = torch.full((B, F), float("nan"), dtype=torch.bfloat16).cuda()
-        K().gemm_skinny(x, inter, out, cfg=-1, epilogue=1)
-        assert (out.double().cpu() - want).abs().max() < tol(torch.bfloat16, max(1.0, want.abs().max().item()))
-
-
-def test_gemm_stream_rows_do_not_depend_on_the_batch():
-    """How the work is cut depends on the weight's shape and the device only, so a row's result is the same
-    bits whatever else is in the batch."""
-    for M, K_ in ((90, 512), (4096, 1024)):
-        x = rnd(8, K_, dtype=torch.bfloat16, seed=26)
-        w = rnd(M, K_, dtype=torch.bfloat16, seed=27)
-        full = torch.empty(8, M, dtype=torch.float32).cuda()
-        K().gemm_skinny(x, w, full, cfg=-1)
-        one = torch.empty(1, M, dtype=torch.float32).cuda()
-        for r in (0, 3, 7):
-            K().gemm_skinny(x[r:r + 1].contiguous(), w, one, cfg=-1)
-            assert torch.equal(one[0], full[r])
-        three = torch.empty(3, M, dtype=torch.float32).cuda()
-        K().gemm_skinny(x[2:5].contiguous(), w, three, cfg=-1)
-        assert torch.equal(three, full[2:5])
+    want = plain.silu((xd @ wg.double().cpu().T) * rs[:, None]) * ((xd @ wu.double().cpu().T) * rs[:, None])
+    assert (out.double().cpu() - want).abs().max() < tol(torch.bfloat16, max(1.0, want.abs().max().item()))
 
 
 def test_gemm_skinny_refuses_what_it_cannot_do():
