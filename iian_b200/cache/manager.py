@@ -47,6 +47,7 @@ class RequestCache:
     committed: List[int] = field(default_factory=list)         # per group: leading blocks offered to the prefix index
     state_slot: int = -1
     state_fresh: bool = False                                   # slot was just allotted and must start from zero
+    epoch: int = 0                                              # bumped whenever a table changes other than by growing
 
     def holds_pages(self) -> bool:
         return any(any(p >= 0 for p in t) for t in self.tables)
@@ -200,6 +201,8 @@ class CacheManager:
                 for i in gone:
                     table[i] = -1
                 released += len(gone)
+        if released:
+            rc.epoch += 1
         return released
 
     def allocate(self, rc: RequestCache, n_computed: int, n_new: int,
@@ -246,6 +249,7 @@ class CacheManager:
                 pool.free_blocks(held)
             table.clear()
             rc.committed[g] = 0
+        rc.epoch += 1
         if rc.state_slot >= 0:
             self.slots.release(rc.state_slot)
             rc.state_slot = -1

@@ -89,15 +89,18 @@ template <int HD> __device__ __forceinline__ unsigned swz(int row, int chunk) {
 }
 
 template <int HD, int NW>
-__global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnParams p) {
     constexpr int BM = 16 * NW;
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
     constexpr int KS = HD / 16;                // k-steps of QK^T
     constexpr int DT = HD / 8;                 // d-tiles of the output
+    static_assert(BM <= BN, "the Q tile borrows the second V stage");
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char * sQ = smem;
-    unsigned char * sK = sQ + BM * HD * 2;                 // [2][BN][HD]
+    unsigned char * sK = smem;                             // [2][BN][HD]
     unsigned char * sV = sK + 2 * BN * HD * 2;             // [2][BN][HD]
+    // Q lives in shared memory only until its fragments are in registers: it borrows the second V stage, which
+    // is first filled after that (three CTAs of 64 KB fit an SM, two of 80 KB did).
+    unsigned char * sQ = sV + BN * HD * 2;
     __shared__ long long s_cell[2][BN];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
     const int ctx = p.ctx_len[s];
     const int pos0 = ctx - q_len;
     const int rows_total = q_len * G;
-    const int row0 = blockIdx.x * BM;
+    const int row0 = (gridDim.x - 1 - blockIdx.x) * BM;   // late rows see the most keys: they start first
     if (row0 >= rows_total) return;
 
     const int tok_min = row0 / G;
@@ -188,11 +191,20 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
         lookup_rows(tile_begin + 1, 1);
         __syncthreads();
         load_q();
+        cp_async_commit();
         load_kv(0, 0);
         cp_async_commit();
 
         unsigned qf[KS][4];
-        bool q_loaded = false;
+        cp_async_wait<1>();                         // Q has landed (the first K/V tile may still be in flight)
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const int r = warp * 16 + (lane & 15);
+            const int ch = ks * 2 + (lane >> 4);
+            ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], smem_u32(sQ + swz<HD>(r, ch)));
+        }
+        __syncthreads();                            // the borrowed stage may be overwritten from here on
 
         for (int tile = tile_begin; tile < tile_end; tile++) {
             const int stage = (tile - tile_begin) & 1;
@@ -205,15 +217,6 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
             }
             __syncthreads();
             lookup_rows(tile + 2, stage);           // slot `stage` held this tile's rows; its copies are issued
-            if (!q_loaded) {
-#pragma unroll
-                for (int ks = 0; ks < KS; ks++) {
-                    const int r = warp * 16 + (lane & 15);
-                    const int ch = ks * 2 + (lane >> 4);
-                    ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], smem_u32(sQ + swz<HD>(r, ch)));
-                }
-                q_loaded = true;
-            }
             const unsigned char * tK = sK + stage * BN * HD * 2;
             const unsigned char * tV = sV + stage * BN * HD * 2;
 
@@ -281,10 +284,12 @@ __global__ void __launch_bounds__(NW * 32) attention_mma_kernel(const AttnParams
                 l_run[h] = l_run[h] * corr[h] + sum[h];     // per-thread partial; reduced over the quad at the end
                 m_run[h] = m_new[h];
             }
+            if (corr[0] != 1.0f || corr[1] != 1.0f) {       // the maximum of long rows settles early
 #pragma unroll
-            for (int dt = 0; dt < DT; dt++) {
-                o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
-                o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+                for (int dt = 0; dt < DT; dt++) {
+                    o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+                    o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+                }
             }
             // ---- O += P V ------------------------------------------------------------------------
 #pragma unroll
@@ -835,7 +840,7 @@ __global__ void attention_combine_kernel(const float * __restrict__ part_o, cons
 template <int HD, int NW>
 static int launch_attention(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
     constexpr int BM = 16 * NW;
-    const size_t smem = (size_t) BM * HD * 2 + 4 * BN * HD * 2;
+    const size_t smem = (size_t) 4 * BN * HD * 2;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);

@@ -278,6 +278,120 @@ class ModelRunner:
                 n_split=slot.n_split if slot is not None else None))
         return ctx
 
+    def build_decode_context(self, entries: Sequence[StepEntry], slot: "_GraphSlot") -> StepContext:
+        """``build_context`` for a captured decode graph, written for the step that comes thousands of times:
+        every entry brings one token, the shape is the slot's.  What does not change from step to step is not
+        written again: the padding behind the real sequences, and the rows of the block tables, of which a
+        step only appends a page now and then (a row is rewritten when another request takes it or when its
+        request's table changed otherwise, which the table's epoch tells)."""
+        mgr, bs = self.manager, self.block_size
+        n, S, mb = len(entries), slot.num_seqs, slot.max_blocks
+        n_groups = len(mgr.groups)
+        if slot.copy_done is not None:
+            slot.copy_done.synchronize()
+        lay = slot.layout
+        if lay is None:
+            off = 0
+            lay = {}
+            for name, size in (("tok", S), ("pos", S), ("seq", S), ("cu", S + 1), ("ctx", S), ("state", S), ("rows", S)):
+                lay[name] = off
+                off += size
+            lay["slots"] = []
+            for _ in range(n_groups):
+                lay["slots"].append(off)
+                off += S
+            lay["bt"] = []
+            for _ in range(n_groups):
+                lay["bt"].append(off)
+                off += S * mb
+            lay["total"] = off
+            slot.layout = lay
+            slot.host = slot.pinned.numpy()
+            slot.arange = np.arange(S + 1, dtype=np.int32)
+        host = slot.host
+        if slot.n_last != n:          # the padding: sequences of one token that is stored nowhere
+            host[lay["tok"]: lay["tok"] + S] = 0
+            host[lay["pos"]: lay["pos"] + S] = 0
+            host[lay["seq"]: lay["seq"] + S] = -1
+            host[lay["cu"]: lay["cu"] + S + 1] = slot.arange
+            host[lay["ctx"]: lay["ctx"] + S] = 1
+            host[lay["state"]: lay["state"] + S] = -1
+            host[lay["rows"]: lay["rows"] + S] = slot.arange[:S]
+            for g in range(n_groups):
+                host[lay["slots"][g]: lay["slots"][g] + S] = -1
+                host[lay["bt"][g]: lay["bt"][g] + S * mb] = 0
+            slot.row_sig = [[None] * S for _ in range(n_groups)]
+            slot.n_last = n
+        starts = np.fromiter((e.start for e in entries), dtype=np.int32, count=n)
+        host[lay["tok"]: lay["tok"] + n] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
+        host[lay["pos"]: lay["pos"] + n] = starts
+        host[lay["seq"]: lay["seq"] + n] = slot.arange[:n]
+        host[lay["ctx"]: lay["ctx"] + n] = starts + 1
+        host[lay["state"]: lay["state"] + n] = np.fromiter((e.cache.state_slot for e in entries), dtype=np.int32, count=n)
+        fresh: List[int] = []
+        blocks = (starts // bs).tolist()
+        for g in range(n_groups):
+            sigs = slot.row_sig[g]
+            base = lay["bt"][g]
+            pages = []
+            for s, e in enumerate(entries):
+                rc = e.cache
+                table = rc.tables[g]
+                need = blocks[s] + 1
+                if len(table) < need:
+                    raise ValueError(f"request holds {len(table)} pages in group {g}, needs {need}")
+                sig = sigs[s]
+                row0 = base + s * mb
+                if sig is None or sig[0] is not rc or sig[1] != rc.epoch or sig[2] > need:
+                    host[row0: row0 + mb] = -1
+                    host[row0: row0 + need] = table[:need]
+                elif sig[2] < need:
+                    host[row0 + sig[2]: row0 + need] = table[sig[2]:need]
+                sigs[s] = (rc, rc.epoch, need)
+                page = table[need - 1]
+                if page < 0:
+                    raise ValueError("a token of this step lies in a page that was given back")
+                pages.append(page)
+                if g == 0 and rc.state_fresh:
+                    fresh.append(rc.state_slot)
+                    rc.state_fresh = False
+            host[lay["slots"][g]: lay["slots"][g] + n] = np.asarray(pages, dtype=np.int32) * bs + starts % bs
+        total = lay["total"]
+        slot.staging[:total].copy_(slot.pinned[:total], non_blocking=True)
+        if slot.copy_done is None:
+            slot.copy_done = torch.cuda.Event()
+        slot.copy_done.record()
+        self.storage.zero_state(fresh)
+        ctx = slot.ctx
+        if ctx is None:
+            dev = slot.staging
+
+            def view(start, size, shape=None):
+                t = dev[start: start + size]
+                return t.view(*shape) if shape is not None else t
+
+            ctx = StepContext(slot.workspace)
+            ctx.tokens, ctx.positions, ctx.seq_of_token = view(lay["tok"], S), view(lay["pos"], S), view(lay["seq"], S)
+            ctx.cu_q, ctx.ctx_len = view(lay["cu"], S + 1), view(lay["ctx"], S)
+            ctx.state_slots, ctx.out_rows = view(lay["state"], S), view(lay["rows"], S)
+            ctx.num_tokens = ctx.num_seqs = S
+            ctx.max_q_len, ctx.max_ctx = 1, slot.ctx_bucket
+            ctx.decode_only = True
+            ctx.rows_identity = True
+            ctx.upload_bytes = total * 4
+            for g in range(n_groups):
+                ctx.metas.append(AttentionMeta(
+                    positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
+                    block_table=view(lay["bt"][g], S * mb, (S, mb)), slots=view(lay["slots"][g], S),
+                    num_seqs=S, num_tokens=S, max_q_len=1, max_ctx=slot.ctx_bucket, decode_only=True,
+                    h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len, n_split=slot.n_split))
+            slot.ctx = ctx
+        ctx.h_q_start[:] = range(n)
+        ctx.h_q_len[:] = [1] * n
+        ctx.h_ctx_len[:] = (starts + 1).tolist()
+        ctx.h_state_slots[:] = [e.cache.state_slot for e in entries]
+        return ctx
+
     # ---- the step -----------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Logits ``[sum(len(want)), vocab]`` in the order of the entries and of their ``want`` lists
@@ -315,7 +429,7 @@ class ModelRunner:
         if slot is None:
             slot = self._capture(bucket, ctx_bucket, entries)
             self._graphs[key] = slot
-        ctx = self.build_context(entries, slot)
+        ctx = self.build_decode_context(entries, slot)
         slot.graph.replay()
         self.launches += slot.launches
         self.last_upload_bytes = ctx.upload_bytes
@@ -372,6 +486,8 @@ class _GraphSlot:
 
     num_seqs = ctx_bucket = max_blocks = n_split = launches = 0
     staging = pinned = workspace = copy_done = graph = logits = None
+    layout = host = arange = row_sig = ctx = None      # what build_decode_context keeps between steps
+    n_last = -1
 
 
 def _launch_count() -> int:

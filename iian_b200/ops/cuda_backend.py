@@ -450,7 +450,7 @@ class CudaKernels:
                                          scale=scale, window=window)
 
     DECODE_STAGES = int(os.environ.get("IIAN_DECODE_STAGES", "2"))     # shared-memory tiles per CTA of the decode kernel
-    DECODE_SLOTS = 148 * (3 if DECODE_STAGES == 2 else 2)              # SMs x resident CTAs of the decode kernel
+    DECODE_SLOTS = 148 * 2                                             # CTAs of the decode kernel one launch should not exceed
     _stages_set = None
 
     def set_decode_stages(self, stages: int) -> None:
@@ -461,7 +461,6 @@ class CudaKernels:
             raise KernelError("attention: the decode kernel has 2 or 3 stages")
         type(self)._stages_set = stages
         type(self).DECODE_STAGES = stages
-        type(self).DECODE_SLOTS = 148 * (3 if stages == 2 else 2)
     CLUSTER_MERGE = os.environ.get("IIAN_ATTENTION_CLUSTER", "1") not in ("0", "false", "off")
     MAX_SPLITS = 32
     _scratch = {}
@@ -469,13 +468,14 @@ class CudaKernels:
 
     def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
         """How many parts the keys of a decode step are cut into, so that few long sequences still fill
-        the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128): the CTAs of one launch should fit the
-        GPU at once (a second wave repeats the whole chain of dependent loads), and a CTA should keep about
-        three key tiles, since the last CTA of a row reads every part back."""
+        the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128, contexts of 1k and 8k, batches 1 to
+        64): the CTAs of one launch should number at most two per SM (more slow each other down, and a second
+        wave repeats the whole chain of dependent loads), and a CTA should keep at least two key tiles.  Up to
+        8 parts merge inside a thread-block cluster, so 9 to 11 are rounded down to 8."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
-        n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 3), self.MAX_SPLITS))
-        return n                         # up to 8 parts merge inside a thread-block cluster
+        n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 2), self.MAX_SPLITS))
+        return 8 if 8 < n < 12 else n
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
         t = self._scratch.get(device)

@@ -149,3 +149,61 @@ def test_command_line(setup, tmp_path):
     assert [r["concurrency"] for r in rows] == [1, 3] and all(r["gen_tps"] > 0 and r["ttft_ms"] > 0 for r in rows)
     proc = subprocess.run([sys.executable, exe, "complete", str(tmp_path), "-p", "1"], capture_output=True, text=True, timeout=600)
     assert proc.returncode == 1 and "config.json" in proc.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_decode_steps_from_graphs_match_eager_steps(setup, name, dtype):
+    """Decode-only steps replayed from captured graphs (padded batch, buffers kept between steps, block-table
+    rows only appended to) against the same steps run eagerly: requests leave, a new one takes a freed row,
+    the order of the batch changes, pages fill up and new ones are taken, a freed request's cache object
+    comes back with other pages."""
+    from iian_b200.engine.model import Model
+    from iian_b200.engine.replay import TraceReplayer
+    d, cfg, w = setup[name]
+    v = TINY[name]["vocab_size"]
+    bs = BLOCK_SIZE[name]
+    model = Model.from_folder(d, dtype, "cuda:0")
+    reps = [TraceReplayer(model, 1024, bs, 8), TraceReplayer(model, 1024, bs, 8)]
+    reps[1].runner.cuda_graphs = True
+    prompts = {k: random_tokens(v, n, 40 + i) for i, (k, n) in enumerate([("a", 2 * bs - 1), ("b", 5), ("c", 3 * bs), ("d", bs + 2)])}
+    script, step = [], 0
+    for k in ("a", "b", "c"):                                   # whole prompts, one step each
+        script.append({"step": step, "entries": [{"id": k, "tokens": prompts[k], "want": [len(prompts[k]) - 1]}], "end": []})
+        step += 1
+    nxt = {k: random_tokens(v, 6 * bs + 40, 90 + i) for i, k in enumerate("abcd")}
+    used = {k: 0 for k in "abcd"}
+
+    def decode(ids, end=()):
+        nonlocal step
+        ents = []
+        for k in ids:
+            ents.append({"id": k, "tokens": [nxt[k][used[k]]], "want": [0]})
+            used[k] += 1
+        script.append({"step": step, "entries": ents, "end": list(end)})
+        step += 1
+
+    for _ in range(bs + 2):
+        decode("abc")
+    decode("abc", end="b")
+    for _ in range(3):
+        decode("ac")
+    script.append({"step": step, "entries": [{"id": "d", "tokens": prompts["d"], "want": [len(prompts["d"]) - 1]}], "end": []})
+    step += 1
+    for _ in range(bs):
+        decode("dac")
+    decode("cda", end="a")
+    script.append({"step": step, "entries": [{"id": "a", "tokens": prompts["b"], "want": [4]}], "end": []})   # "a" again, new pages
+    step += 1
+    for _ in range(4):
+        decode("acd")
+    tol_ = 1e-5 if dtype == "float32" else 0.05
+    for rec in script:
+        outs = [r.run_step(rec) for r in reps]
+        if outs[0] is None:
+            assert outs[1] is None
+            continue
+        err = (outs[0].float() - outs[1].float()).abs().max().item()
+        scale = max(1.0, outs[0].float().abs().max().item())
+        assert err <= tol_ * scale, f"step {rec['step']}: graph and eager logits differ by {err} (scale {scale})"
+    assert reps[1].runner._graphs, "no decode graph was captured"
