@@ -1,31 +1,20 @@
-"""The cache manager: pages per group of layers, a block table per request and group,
-prefix reuse, and slots for per-request state of fixed size.
+"""The cache manager: pages per group of layers, a block table per request and group, prefix reuse, and
+slots for per-request state of fixed size.
 
-The reference has one group (every layer shares one block table,
-src/iian/kv_cache.cpp:156-169) and no fixed-size state; its per-request record is
-``KVRequestState`` (include/iian/kv_cache.h:93-97) and its operations are
-``get_computed_blocks`` (kv_cache.cpp:199-212), ``allocate_slots`` (:214-229, all or
-nothing), ``cache_blocks`` (:231-238), ``free`` in reverse order (:240-246) and
-``update_hashes`` (:190-197).  Those semantics are kept per group.  New here:
-
-* several groups, each with a pool of its own; a group with a ``window`` needs only the
-  last ``window`` keys, so pages the window has passed are given back while the request
-  is still running ("free out-of-window blocks" is an open item in the reference,
-  docs/ROADMAP.md:33);
-* a prefix hit must be usable by every group: all leading pages for a group that needs all
-  keys, the pages inside the window for a windowed one;
-* :class:`StateSlots`: one fixed-size slot per running request for mixers that keep a
-  summary instead of per-token entries.
-
-Everything here is host bookkeeping on page numbers; device tensors live in
-``iian_b200.cache.storage``.
+The manager is C++ (``include/iian_b200/cache_manager.h``; what it keeps of the reference and what is new
+is said there); the classes here are handles on it.  Everything is host bookkeeping on page numbers; device
+tensors live in ``iian_b200.cache.storage``.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from ctypes import c_int, c_longlong, c_uint64
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
 
+from . import native
 from .block_pool import HASH_NONE, BlockPool, PoolError, hash_block
+
+__all__ = ["CacheManager", "PageGroup", "RequestCache", "StateSlots", "PoolError", "hash_block", "HASH_NONE"]
 
 
 @dataclass(frozen=True)
@@ -38,47 +27,75 @@ class PageGroup:
     num_blocks: int
 
 
-@dataclass
 class RequestCache:
-    """What one request holds."""
+    """What one request holds: per group the page of each logical block (-1 = not held), the chained hashes
+    of its full pages, its state slot.  A handle on the native record; ``_owner`` is what keeps that record
+    alive when it is not this object (a scheduler's request)."""
 
-    tables: List[List[int]] = field(default_factory=list)      # per group: page of logical block i, -1 = not held
-    hashes: List[int] = field(default_factory=list)            # chained hashes of full pages of its tokens
-    committed: List[int] = field(default_factory=list)         # per group: leading blocks offered to the prefix index
-    state_slot: int = -1
-    state_fresh: bool = False                                   # slot was just allotted and must start from zero
-    epoch: int = 0                                              # bumped whenever a table changes other than by growing
+    __slots__ = ("_h", "_owner", "_n_groups", "__weakref__")
+
+    def __init__(self, handle, n_groups: int, owner=None):
+        self._h, self._n_groups, self._owner = handle, n_groups, owner
+
+    def __del__(self):
+        if getattr(self, "_owner", None) is None and getattr(self, "_h", None):
+            try:
+                native.lib().iian_rc_delete(self._h)
+            except Exception:           # the interpreter is shutting down
+                pass
+            self._h = None
+
+    def _get(self, what: int, g: int = 0) -> int:
+        return native.lib().iian_rc_get(self._h, what, g)
+
+    def table(self, g: int) -> List[int]:
+        n = self._get(3, g)
+        return list(native.lib().iian_rc_table(self._h, g)[:n]) if n > 0 else []
+
+    tables = property(lambda self: [self.table(g) for g in range(self._n_groups)])
+    committed = property(lambda self: [self._get(5, g) for g in range(self._n_groups)])
+    state_slot = property(lambda self: self._get(0))
+    epoch = property(lambda self: self._get(2))
+
+    @property
+    def hashes(self) -> List[int]:
+        n = self._get(4)
+        return list(native.lib().iian_rc_hashes(self._h)[:n]) if n > 0 else []
+
+    @property
+    def state_fresh(self) -> bool:
+        return bool(self._get(1))
+
+    @state_fresh.setter
+    def state_fresh(self, v: bool) -> None:
+        native.lib().iian_rc_set_state_fresh(self._h, int(bool(v)))
 
     def holds_pages(self) -> bool:
-        return any(any(p >= 0 for p in t) for t in self.tables)
+        return bool(self._get(6))
 
 
 class StateSlots:
     """Fixed-size per-request state: slot numbers handed out at admission, taken back at the end."""
 
-    def __init__(self, num_slots: int):
-        self.num_slots = num_slots
-        self._free = list(range(num_slots - 1, -1, -1))
-        self._held = [False] * num_slots
+    def __init__(self, mgr):
+        """``mgr``: the cache manager whose slots these are, or a number of slots for a set of its own."""
+        if isinstance(mgr, int):
+            mgr = CacheManager([PageGroup("none", (), None, 1)], 1, False, mgr)
+        self._mgr = mgr
 
-    @property
-    def num_free(self) -> int:
-        return len(self._free)
+    def _call(self, what: int, arg: int = 0) -> int:
+        out = c_int(0)
+        native.check(native.lib().iian_cache_slots(self._mgr._h, what, arg, out))
+        return out.value
+
+    num_slots = property(lambda self: self._call(0))
+    num_free = property(lambda self: self._call(1))
 
     def allot(self) -> int:
-        if not self._free:
-            return -1
-        s = self._free.pop()
-        self._held[s] = True
-        return s
+        return self._call(2)
 
     def release(self, slot: int) -> None:
-        if slot < 0:
-            return
-        if not self._held[slot]:
-            raise PoolError(f"StateSlots: slot {slot} released twice")
-        self._held[slot] = False
-        self._free.append(slot)
+        self._call(3, slot)
 
 
 class CacheManager:
@@ -89,187 +106,115 @@ class CacheManager:
         self.groups = list(groups)
         self.block_size = block_size
         self.prefix_caching = enable_prefix_caching
-        self.pools = [BlockPool(g.num_blocks, block_size, enable_prefix_caching) for g in self.groups]
-        self.slots = StateSlots(num_state_slots)
-        self.prefix_queries = 0        # pages asked for / found, as in kv_cache.h:86
-        self.prefix_hits = 0
+        L = native.lib()
+        windows, n = native.int_array([-1 if g.window is None else int(g.window) for g in self.groups])
+        blocks, _ = native.int_array([int(g.num_blocks) for g in self.groups])
+        self._h = L.iian_cache_new(windows, blocks, n, block_size, int(enable_prefix_caching), num_state_slots)
+        if not self._h:
+            raise ValueError(L.iian_host_last_error().decode())
+        self.pools = [BlockPool(g.num_blocks, block_size, enable_prefix_caching, _handle=L.iian_cache_pool(self._h, i), _owner=self)
+                      for i, g in enumerate(self.groups)]
+        self.slots = StateSlots(self)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            try:
+                native.lib().iian_cache_delete(self._h)
+            except Exception:           # the interpreter is shutting down
+                pass
+            self._h = None
+
+    prefix_queries = property(lambda self: native.lib().iian_cache_counter(self._h, 0, 0))
+    prefix_hits = property(lambda self: native.lib().iian_cache_counter(self._h, 1, 0))
 
     # ---- requests --------------------------------------------------------------------
     def new_request(self) -> RequestCache:
-        n = len(self.groups)
-        return RequestCache(tables=[[] for _ in range(n)], committed=[0] * n)
+        return RequestCache(native.lib().iian_rc_new(self._h), len(self.groups))
 
     def allot_state(self, rc: RequestCache) -> bool:
         """Give the request a state slot (no-op if it has one).  False if none is free."""
-        if rc.state_slot >= 0:
-            return True
-        if self.slots.num_slots == 0:
-            return True
-        s = self.slots.allot()
-        if s < 0:
-            return False
-        rc.state_slot = s
-        rc.state_fresh = True
-        return True
+        return bool(native.lib().iian_cache_allot_state(self._h, rc._h))
 
     # ---- geometry --------------------------------------------------------------------
     def first_needed_block(self, g: int, n_computed: int) -> int:
         """First logical block a group still needs once ``n_computed`` tokens are done: the next
         query sits at position ``n_computed`` and sees keys ``> n_computed - window``."""
-        w = self.groups[g].window
-        if w is None:
-            return 0
-        return max(0, n_computed - w + 1) // self.block_size
+        return native.lib().iian_cache_first_needed_block(self._h, g, n_computed)
 
     def blocks_for(self, n_tokens: int) -> int:
         return (n_tokens + self.block_size - 1) // self.block_size
 
     # ---- prefix reuse ----------------------------------------------------------------
-    def update_hashes(self, hashes: List[int], tokens: Sequence[int], salt: int = 0) -> None:
-        bs = self.block_size
-        n_full = len(tokens) // bs
-        while len(hashes) < n_full:
-            i = len(hashes)
-            parent = HASH_NONE if i == 0 else hashes[i - 1]
-            hashes.append(hash_block(parent, tokens[i * bs:(i + 1) * bs], salt))
+    def update_hashes(self, rc: RequestCache, tokens: Sequence[int], salt: int = 0) -> None:
+        """Extend the request's chained hashes to cover every full page of ``tokens``."""
+        arr, n = native.i32_array(list(tokens))
+        native.check(native.lib().iian_cache_update_hashes(self._h, rc._h, arr, n, salt & ((1 << 64) - 1)))
+
+    def _table_buffers(self, cap: int):
+        return (c_int * (len(self.groups) * max(cap, 1)))(), (c_int * len(self.groups))()
 
     def find_cached_prefix(self, tokens: Sequence[int], hashes: Sequence[int]) -> Tuple[int, List[List[int]]]:
-        """Longest reusable prefix, in tokens (a multiple of the page size, at most
-        ``len(tokens) - 1`` so that the last token is always computed for its logits), and
-        per group the table to start from.  Nothing is referenced yet."""
-        empty = [[] for _ in self.groups]
-        if not self.prefix_caching or len(tokens) < 2:
-            return 0, empty
-        bs = self.block_size
-        max_blocks = min((len(tokens) - 1) // bs, len(hashes))
-        found: List[List[int]] = [[] for _ in self.groups]
-        for g, pool in enumerate(self.pools):
-            for i in range(max_blocks):
-                found[g].append(pool.get_cached_block(hashes[i], tokens[i * bs:(i + 1) * bs]))
-        n = max_blocks
-        for g, grp in enumerate(self.groups):
-            if grp.window is None:
-                k = 0
-                while k < n and found[g][k] >= 0:
-                    k += 1
-                n = k
-        while n > 0:
-            ok = True
-            for g, grp in enumerate(self.groups):
-                if grp.window is None:
-                    continue
-                first = self.first_needed_block(g, n * bs)
-                if any(found[g][i] < 0 for i in range(first, n)):
-                    ok = False
-                    break
-            if ok:
-                break
-            n -= 1
-        if n == 0:
-            return 0, empty
-        tables = []
-        for g, grp in enumerate(self.groups):
-            first = self.first_needed_block(g, n * bs)
-            tables.append([-1] * first + [found[g][i] for i in range(first, n)])
-        return n * bs, tables
+        """Longest reusable prefix, in tokens (a multiple of the page size, at most ``len(tokens) - 1`` so
+        that the last token is always computed for its logits), and per group the table to start from.
+        Nothing is referenced yet."""
+        arr, n = native.i32_array(list(tokens))
+        hs = (c_uint64 * max(len(hashes), 1))(*hashes)
+        cap = max(1, self.blocks_for(n))
+        tables, lens = self._table_buffers(cap)
+        found = native.lib().iian_cache_find_prefix(self._h, arr, n, hs, len(hashes), tables, lens, cap)
+        if found < 0:
+            native.check(2)
+        return found, [list(tables[g * cap: g * cap + lens[g]]) for g in range(len(self.groups))]
 
     def commit(self, rc: RequestCache, tokens: Sequence[int], n_computed: int) -> None:
         """Offer the full pages covering ``tokens[:n_computed]`` to the prefix index."""
-        if not self.prefix_caching:
-            return
-        bs = self.block_size
-        n_full = min(min(n_computed, len(tokens)) // bs, len(rc.hashes))
-        for g, pool in enumerate(self.pools):
-            table = rc.tables[g]
-            for i in range(rc.committed[g], min(n_full, len(table))):
-                if table[i] >= 0:
-                    pool.cache_block(table[i], rc.hashes[i], tokens[i * bs:(i + 1) * bs])
-            rc.committed[g] = max(rc.committed[g], min(n_full, len(table)))
+        arr, n = native.i32_array(list(tokens))
+        native.check(native.lib().iian_cache_commit(self._h, rc._h, arr, n, n_computed))
 
     # ---- pages -----------------------------------------------------------------------
     def release_passed(self, rc: RequestCache, n_computed: int) -> int:
         """Give back pages that a group's window has passed.  Returns how many."""
-        released = 0
-        for g, pool in enumerate(self.pools):
-            if self.groups[g].window is None:
-                continue
-            table = rc.tables[g]
-            first = min(self.first_needed_block(g, n_computed), len(table))
-            gone = [i for i in range(first) if table[i] >= 0]
-            if gone:
-                pool.free_blocks([table[i] for i in reversed(gone)])
-                for i in gone:
-                    table[i] = -1
-                released += len(gone)
-        if released:
-            rc.epoch += 1
-        return released
+        out = c_int(0)
+        native.check(native.lib().iian_cache_release_passed(self._h, rc._h, n_computed, out))
+        return out.value
 
     def allocate(self, rc: RequestCache, n_computed: int, n_new: int,
                  computed: Optional[List[List[int]]] = None) -> bool:
-        """Make sure the request holds pages for tokens ``[0, n_computed + n_new)`` in every
-        group (for a windowed group: from the first block its window still reaches).  Pages
-        of a prefix hit (``computed``, from :meth:`find_cached_prefix`) are referenced and put
-        first if the request holds nothing yet.  Either every group gets what it needs or
-        nothing is taken and False is returned."""
-        self.release_passed(rc, n_computed)
-        need_total = self.blocks_for(n_computed + n_new)
-        plans = []
-        for g, pool in enumerate(self.pools):
-            table = rc.tables[g]
-            use_computed = computed is not None and not table and bool(computed[g])
-            have = len(computed[g]) if use_computed else len(table)
-            n_fresh = max(0, need_total - have)
-            n_touch_free = 0
-            if use_computed:
-                n_touch_free = sum(1 for p in computed[g] if p >= 0 and pool.ref[p] == 0)
-            if n_fresh + n_touch_free > pool.num_free:
-                return False
-            plans.append((use_computed, n_fresh))
-        for g, pool in enumerate(self.pools):
-            use_computed, n_fresh = plans[g]
-            table = rc.tables[g]
-            if use_computed:
-                for p in computed[g]:
-                    if p >= 0:
-                        pool.touch(p)
-                    table.append(p)
-                rc.committed[g] = len(table)
-            if n_fresh:
-                table.extend(pool.get_new_blocks(n_fresh))
-        return True
+        """Make sure the request holds pages for tokens ``[0, n_computed + n_new)`` in every group (for a
+        windowed group: from the first block its window still reaches).  Pages of a prefix hit
+        (``computed``, from :meth:`find_cached_prefix`) are referenced and put first if the request holds
+        nothing yet.  Either every group gets what it needs or nothing is taken and False is returned."""
+        ok = c_int(0)
+        if computed is None:
+            native.check(native.lib().iian_cache_allocate(self._h, rc._h, n_computed, n_new, None, None, 0, ok))
+        else:
+            cap = max(1, max(len(t) for t in computed))
+            tables, lens = self._table_buffers(cap)
+            for g, t in enumerate(computed):
+                lens[g] = len(t)
+                tables[g * cap: g * cap + len(t)] = t
+            native.check(native.lib().iian_cache_allocate(self._h, rc._h, n_computed, n_new, tables, lens, cap, ok))
+        return bool(ok.value)
 
     def free(self, rc: RequestCache) -> None:
-        """Give back everything the request holds: pages in reverse order, so that the tail of
-        a chain is evicted before its head, and the state slot."""
-        for g, pool in enumerate(self.pools):
-            table = rc.tables[g]
-            held = [p for p in reversed(table) if p >= 0]
-            if held:
-                pool.free_blocks(held)
-            table.clear()
-            rc.committed[g] = 0
-        rc.epoch += 1
-        if rc.state_slot >= 0:
-            self.slots.release(rc.state_slot)
-            rc.state_slot = -1
-            rc.state_fresh = False
+        """Give back everything the request holds: pages in reverse order, so that the tail of a chain is
+        evicted before its head, and the state slot."""
+        native.check(native.lib().iian_cache_free(self._h, rc._h))
 
     def slot_of(self, rc: RequestCache, g: int, token_idx: int) -> int:
         """Flat cache cell of a token: page * page size + offset (include/iian/kv_cache.h:135-137)."""
-        page = rc.tables[g][token_idx // self.block_size]
-        if page < 0:
-            raise PoolError(f"token {token_idx} lies in a page that was given back")
-        return page * self.block_size + token_idx % self.block_size
+        out = c_longlong(0)
+        native.check(native.lib().iian_cache_slot_of(self._h, rc._h, g, token_idx, out))
+        return out.value
 
     # ---- figures ---------------------------------------------------------------------
     @property
     def usage(self) -> float:
-        return max(p.usage for p in self.pools) if self.pools else 0.0
+        return native.lib().iian_cache_usage(self._h)
 
     def num_free(self, g: int = 0) -> int:
         return self.pools[g].num_free
 
     def check_invariants(self) -> None:
-        for p in self.pools:
-            p.check_invariants()
+        if native.lib().iian_cache_check(self._h) != 0:
+            raise AssertionError(native.lib().iian_host_last_error().decode())

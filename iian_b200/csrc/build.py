@@ -143,11 +143,83 @@ def _compile(name: str, verbose: bool = True) -> str:
     return out
 
 
+# ---- the host runtime (block pool, cache manager, scheduler, step packing): plain C++17, no CUDA --------
+HOST_NAME = "host"
+HOST_DIR = os.path.join(HERE, "host")
+INCLUDE_DIR = os.path.join(os.path.dirname(os.path.dirname(HERE)), "include")
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
+
+
+def _host_sources() -> List[str]:
+    return sorted(os.path.join(HOST_DIR, f) for f in os.listdir(HOST_DIR) if f.endswith(".cc"))
+
+
+def _host_hash() -> str:
+    h = hashlib.sha256()
+    headers = sorted(os.path.join(INCLUDE_DIR, "iian_b200", f) for f in os.listdir(os.path.join(INCLUDE_DIR, "iian_b200")))
+    for p in _host_sources() + headers:
+        with open(p, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def _cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise KernelBuildError("no C++ compiler found (set CXX or put g++ on PATH); the host runtime is native code")
+
+
+def _compile_host(verbose: bool = True) -> str:
+    out = os.path.join(build_dir(), f"{HOST_NAME}.{_host_hash()}.so")
+    if os.path.isfile(out):
+        return out
+    tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
+    cmd = [_cxx()] + HOST_FLAGS + ["-I", INCLUDE_DIR, "-o", tmp] + _host_sources()
+    t0 = time.time()
+    if verbose:
+        print("[iian_b200] compiling the host runtime ...", file=sys.stderr, flush=True)
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+        raise KernelBuildError(f"compiling the host runtime failed (exit {proc.returncode}):\n{' '.join(cmd)}\n{proc.stdout}")
+    os.replace(tmp, out)
+    for fn in os.listdir(os.path.dirname(out)):
+        if fn.startswith(f"{HOST_NAME}.") and fn.endswith(".so") and os.path.join(os.path.dirname(out), fn) != out:
+            try:
+                os.remove(os.path.join(os.path.dirname(out), fn))
+            except OSError:
+                pass
+    if verbose:
+        print(f"[iian_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    return out
+
+
+def load_host() -> ctypes.CDLL:
+    """The host runtime library, compiled first if needed (needs a C++ compiler, no GPU and no nvcc)."""
+    with _lock:
+        lib = _loaded.get(HOST_NAME)
+        if lib is None:
+            path = _compile_host()
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelBuildError(f"cannot load {path}: {e}") from None
+            _loaded[HOST_NAME] = lib
+        return lib
+
+
 def build(names: Optional[Iterable[str]] = None, verbose: bool = True) -> List[str]:
     """Compile the named libraries (all by default), in parallel.  Needs no GPU."""
+    everything = names is None
     names = list(names) if names is not None else list(SOURCES)
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(names)))) as pool:
-        return list(pool.map(lambda n: _compile(n, verbose), names))
+        built = list(pool.map(lambda n: _compile(n, verbose), names))
+    if everything:
+        built.append(_compile_host(verbose))
+    return built
 
 
 def load(name: str) -> ctypes.CDLL:

@@ -94,6 +94,7 @@ class Engine:
                                   cuda_graphs=c.cuda_graphs, max_model_len=self.max_model_len)
         self.cache = self.runner.manager
         self.scheduler = Scheduler(c.sched, self.cache)
+        self._preemptions_before = 0
         self.sampler = Sampler(model.device)
         self.eos_token_ids = tuple(getattr(model.config, "eos_token_ids", ()) or ())
         self._stats = EngineStats()
@@ -158,7 +159,7 @@ class Engine:
         if not self.scheduler.has_requests:
             return False
         so = self.scheduler.schedule()
-        self._stats.preemptions = self.scheduler.num_preemptions
+        self._stats.preemptions = self.scheduler.num_preemptions - self._preemptions_before
         if not so.scheduled:
             if so.preempted:
                 return True
@@ -291,7 +292,7 @@ class Engine:
             self._next_id = 1
             for pool in self.cache.pools:
                 pool.reset_prefix_cache()
-            self.scheduler.num_preemptions = 0
+            self._preemptions_before = self.scheduler.num_preemptions      # the warm-up's do not count
             del saved
 
     def stats(self) -> EngineStats:
@@ -301,7 +302,7 @@ class Engine:
         s.kv_usage = self.cache.usage
         s.prefix_cache_queries = self.cache.prefix_queries
         s.prefix_cache_hits = self.cache.prefix_hits
-        s.preemptions = self.scheduler.num_preemptions
+        s.preemptions = self.scheduler.num_preemptions - self._preemptions_before
         return s
 
     # ---- background loop (include/iian/engine.h:71-72) ------------------------------------------

@@ -16,6 +16,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import ctypes
 import os
 
 import numpy as np
@@ -280,11 +281,13 @@ class ModelRunner:
 
     def build_decode_context(self, entries: Sequence[StepEntry], slot: "_GraphSlot") -> StepContext:
         """``build_context`` for a captured decode graph, written for the step that comes thousands of times:
-        every entry brings one token, the shape is the slot's.  What does not change from step to step is not
+        every entry brings one token, the shape is the slot's.  The packing is native
+        (``iian_pack_decode_step``, include/iian_b200/c_api.h).  What does not change from step to step is not
         written again: the padding behind the real sequences, and the rows of the block tables, of which a
         step only appends a page now and then (a row is rewritten when another request takes it or when its
         request's table changed otherwise, which the table's epoch tells)."""
-        mgr, bs = self.manager, self.block_size
+        from ..cache import native
+        mgr = self.manager
         n, S, mb = len(entries), slot.num_seqs, slot.max_blocks
         n_groups = len(mgr.groups)
         if slot.copy_done is not None:
@@ -306,56 +309,24 @@ class ModelRunner:
                 off += S * mb
             lay["total"] = off
             slot.layout = lay
-            slot.host = slot.pinned.numpy()
-            slot.arange = np.arange(S + 1, dtype=np.int32)
-        host = slot.host
-        if slot.n_last != n:          # the padding: sequences of one token that is stored nowhere
-            host[lay["tok"]: lay["tok"] + S] = 0
-            host[lay["pos"]: lay["pos"] + S] = 0
-            host[lay["seq"]: lay["seq"] + S] = -1
-            host[lay["cu"]: lay["cu"] + S + 1] = slot.arange
-            host[lay["ctx"]: lay["ctx"] + S] = 1
-            host[lay["state"]: lay["state"] + S] = -1
-            host[lay["rows"]: lay["rows"] + S] = slot.arange[:S]
-            for g in range(n_groups):
-                host[lay["slots"][g]: lay["slots"][g] + S] = -1
-                host[lay["bt"][g]: lay["bt"][g] + S * mb] = 0
-            slot.row_sig = [[None] * S for _ in range(n_groups)]
-            slot.n_last = n
-        starts = np.fromiter((e.start for e in entries), dtype=np.int32, count=n)
-        host[lay["tok"]: lay["tok"] + n] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
-        host[lay["pos"]: lay["pos"] + n] = starts
-        host[lay["seq"]: lay["seq"] + n] = slot.arange[:n]
-        host[lay["ctx"]: lay["ctx"] + n] = starts + 1
-        host[lay["state"]: lay["state"] + n] = np.fromiter((e.cache.state_slot for e in entries), dtype=np.int32, count=n)
-        fresh: List[int] = []
-        blocks = (starts // bs).tolist()
-        for g in range(n_groups):
-            sigs = slot.row_sig[g]
-            base = lay["bt"][g]
-            pages = []
-            for s, e in enumerate(entries):
-                rc = e.cache
-                table = rc.tables[g]
-                need = blocks[s] + 1
-                if len(table) < need:
-                    raise ValueError(f"request holds {len(table)} pages in group {g}, needs {need}")
-                sig = sigs[s]
-                row0 = base + s * mb
-                if sig is None or sig[0] is not rc or sig[1] != rc.epoch or sig[2] > need:
-                    host[row0: row0 + mb] = -1
-                    host[row0: row0 + need] = table[:need]
-                elif sig[2] < need:
-                    host[row0 + sig[2]: row0 + need] = table[sig[2]:need]
-                sigs[s] = (rc, rc.epoch, need)
-                page = table[need - 1]
-                if page < 0:
-                    raise ValueError("a token of this step lies in a page that was given back")
-                pages.append(page)
-                if g == 0 and rc.state_fresh:
-                    fresh.append(rc.state_slot)
-                    rc.state_fresh = False
-            host[lay["slots"][g]: lay["slots"][g] + n] = np.asarray(pages, dtype=np.int32) * bs + starts % bs
+            slot.host_ptr = slot.pinned.data_ptr()
+            slot.sig = (ctypes.c_longlong * (n_groups * S * 3))()
+            slot.c_caches = (ctypes.c_void_p * S)()
+            slot.c_tokens = (ctypes.c_int32 * S)()
+            slot.c_starts = (ctypes.c_int32 * S)()
+            slot.c_fresh = (ctypes.c_int * S)()
+        caches, toks, starts = slot.c_caches, slot.c_tokens, slot.c_starts
+        for s, e in enumerate(entries):
+            caches[s] = e.cache._h
+            toks[s] = e.tokens[0]
+            starts[s] = e.start
+        n_fresh = native.lib().iian_pack_decode_step(mgr._h, caches, toks, starts, n, S, mb, slot.host_ptr,
+                                                     ctypes.addressof(slot.sig), int(slot.n_last != n), slot.c_fresh)
+        if n_fresh < 0:
+            slot.n_last = -1                 # the buffer may be half written
+            native.check(2)
+        slot.n_last = n
+        fresh = list(slot.c_fresh[:n_fresh])
         total = lay["total"]
         slot.staging[:total].copy_(slot.pinned[:total], non_blocking=True)
         if slot.copy_done is None:
@@ -388,8 +359,8 @@ class ModelRunner:
             slot.ctx = ctx
         ctx.h_q_start[:] = range(n)
         ctx.h_q_len[:] = [1] * n
-        ctx.h_ctx_len[:] = (starts + 1).tolist()
-        ctx.h_state_slots[:] = [e.cache.state_slot for e in entries]
+        ctx.h_ctx_len[:] = [e.start + 1 for e in entries]
+        ctx.h_state_slots[:] = [e.cache.state_slot for e in entries] if self.manager.slots.num_slots else [-1] * n
         return ctx
 
     # ---- the step -----------------------------------------------------------------------------
@@ -486,7 +457,7 @@ class _GraphSlot:
 
     num_seqs = ctx_bucket = max_blocks = n_split = launches = 0
     staging = pinned = workspace = copy_done = graph = logits = None
-    layout = host = arange = row_sig = ctx = None      # what build_decode_context keeps between steps
+    layout = host_ptr = sig = c_caches = c_tokens = c_starts = c_fresh = ctx = None      # kept between steps by build_decode_context
     n_last = -1
 
 

@@ -68,13 +68,13 @@ def test_prefix_reuse_full_pages_only_and_never_the_last_token():
     m = manager(blocks=16, bs=4)
     toks = list(range(100, 113))                   # 13 tokens: 3 full pages
     a = m.new_request()
-    m.update_hashes(a.hashes, toks)
+    m.update_hashes(a, toks)
     assert len(a.hashes) == 3
     assert m.find_cached_prefix(toks, a.hashes)[0] == 0
     assert m.allocate(a, 0, 13)
     m.commit(a, toks, 13)
     b = m.new_request()
-    m.update_hashes(b.hashes, toks)
+    m.update_hashes(b, toks)
     n, tables = m.find_cached_prefix(toks, b.hashes)
     assert n == 12 and tables[0] == a.tables[0][:3]
     # 12 tokens that are all cached: the last token must still be computed
@@ -88,12 +88,12 @@ def test_prefix_reuse_full_pages_only_and_never_the_last_token():
     assert m.num_free() == 16
     # freed but cached: a third request finds them and takes them off the free list
     c = m.new_request()
-    m.update_hashes(c.hashes, toks)
+    m.update_hashes(c, toks)
     n, tables = m.find_cached_prefix(toks, c.hashes)
     assert n == 12 and m.allocate(c, n, 1, tables) and m.num_free() == 12
     other = toks[:4] + [1, 2, 3, 4, 5]
     d = m.new_request()
-    m.update_hashes(d.hashes, other)
+    m.update_hashes(d, other)
     assert m.find_cached_prefix(other, d.hashes)[0] == 4            # stops at the first page that differs
     m.check_invariants()
 
@@ -102,7 +102,7 @@ def test_prefix_reuse_with_a_window_needs_only_the_pages_in_the_window():
     m = manager(blocks=16, bs=4, window=6)
     toks = list(range(50, 71))                     # 21 tokens: 5 full pages
     a = m.new_request()
-    m.update_hashes(a.hashes, toks)
+    m.update_hashes(a, toks)
     pos = 0
     for n in (9, 8, 4):
         assert m.allocate(a, pos, n)
@@ -110,7 +110,7 @@ def test_prefix_reuse_with_a_window_needs_only_the_pages_in_the_window():
         m.commit(a, toks, pos)
     m.free(a)
     b = m.new_request()
-    m.update_hashes(b.hashes, toks)
+    m.update_hashes(b, toks)
     n, tables = m.find_cached_prefix(toks, b.hashes)
     assert n == 20
     first = m.first_needed_block(1, 20)
@@ -165,7 +165,7 @@ def test_random_orders_lose_no_page(seed, window):
             rc = m.new_request()
             if not m.allot_state(rc):
                 continue
-            m.update_hashes(rc.hashes, toks)
+            m.update_hashes(rc, toks)
             n, tables = m.find_cached_prefix(toks, rc.hashes)
             n_new = min(len(toks) - n, rng.randrange(1, 9))
             if m.allocate(rc, n, n_new, tables):
@@ -181,7 +181,7 @@ def test_random_orders_lose_no_page(seed, window):
             n_new = min(len(toks) - done, rng.randrange(1, 7))
             if m.allocate(rc, done, n_new):
                 ent[2] = done + n_new
-                m.update_hashes(rc.hashes, toks)
+                m.update_hashes(rc, toks)
                 m.commit(rc, toks, ent[2])
             else:                                       # out of pages: drop this request (a preemption)
                 m.free(rc)
