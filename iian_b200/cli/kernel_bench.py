@@ -42,6 +42,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0: the engine's choice)")
     ap.add_argument("--stages", type=int, default=0, help="decode attention: shared-memory tiles per CTA (2 or 3; 0: the default)")
+    ap.add_argument("--tc", action="store_true", help="attention_prefill: the tcgen05 kernel instead of the mma.sync kernel")
     ap.add_argument("--no-cluster", action="store_true", help="decode attention: merge key splits through scratch memory")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -196,7 +197,11 @@ def main(argv=None) -> int:
             kw.update(n_split=args.splits, small_tiles=True)
         if args.no_cluster:
             kw.update(cluster=False)
-        us = timeit(lambda i: k.paged_attention_mma(q, caches[i % copies][0], caches[i % copies][1], out, meta, **kw))
+        if not decode and args.tc:
+            us = timeit(lambda i: k.paged_attention_tc(q, caches[i % copies][0], caches[i % copies][1], out, meta, **kw))
+            k.tcgen05_check(dev)
+        else:
+            us = timeit(lambda i: k.paged_attention_mma(q, caches[i % copies][0], caches[i % copies][1], out, meta, **kw))
         if decode:
             gb = seqs * ctx_len * nkv * hd * 2 * 2 / 1e9
             print(f"attention_decode batch {seqs} ctx {ctx_len} heads {nh}/{nkv} x {hd}: {us:.1f} us, {gb / (us * 1e-6):.0f} GB/s of K/V "

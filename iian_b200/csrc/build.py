@@ -29,9 +29,10 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 SHARED_HEADERS = ["common.cuh"]
 
 # every library of the engine; build_all() compiles them all
-SOURCES = ["elementwise", "rope_kv", "attention_generic", "gemm_simt", "sampling", "gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05"]
+SOURCES = ["elementwise", "rope_kv", "attention_generic", "gemm_simt", "sampling", "gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05",
+           "attention_tc"]
 # libraries only the bfloat16 serving path uses
-BF16_SOURCES: List[str] = ["gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05"]
+BF16_SOURCES: List[str] = ["gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05", "attention_tc"]
 # extra link flags per source
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 

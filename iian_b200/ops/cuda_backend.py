@@ -364,8 +364,7 @@ class CudaKernels:
         code, where = t.tolist()
         if code != 0:
             t.zero_()
-            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "an epilogue warp"}.get(code, f"role {code}")
-            raise KernelError(f"gemm_tcgen05: {role} gave up waiting on its barrier (at {where}); the result is not valid")
+            raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (wait {code}, iteration {where}); its result is not valid")
 
     def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, bn: int = 0) -> None:
         """``epilogue`` 0: out[t, n] = x . w; 1: w holds gate and up rows interleaved in groups of 8 and
@@ -441,7 +440,38 @@ class CudaKernels:
         ``decode_only``)."""
         self._attention_dispatch(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale, window)
 
+    # prefill portions on tcgen05 (csrc/attention_tc.cu); IIAN_ATTENTION_TC=0 keeps them on the mma.sync kernel
+    ATTENTION_TC = os.environ.get("IIAN_ATTENTION_TC", "1") not in ("0", "false", "off")
+    TC_ATTENTION_MIN_ROWS = 64        # rows (tokens x heads per KV head) of the longest portion from which it is used
+
+    def _attention_tc_ok(self, q, k_cache, meta, nh, nkv, hd) -> bool:
+        return (self.ATTENTION_TC and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and hd == 128
+                and k_cache.shape[2] in (8, 16, 32, 64, 128) and nkv > 0 and nh % nkv == 0
+                and meta.max_q_len * (nh // nkv) >= self.TC_ATTENTION_MIN_ROWS)
+
+    def paged_attention_tc(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window) -> None:
+        """Prefill attention on tcgen05 + TMA: head size 128, bfloat16, pages of 8 to 128 tokens."""
+        n = q.shape[0]
+        if k_cache.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            raise KernelError("paged_attention_tc: bfloat16 only")
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or q.numel() != n * num_heads * head_dim:
+            raise KernelError("paged_attention_tc: cache / q shapes do not match the head counts")
+        status = self.tcgen05_status_buffer(q.device)
+        bt = meta.block_table
+        fn = _fn("attention_tc", "iian_attention_tc",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+        _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
+                  _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
+                  num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0,
+                  status.data_ptr(), _stream()), "attention_tc")
+
     def _attention_dispatch(self, q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, window) -> None:
+        if self._attention_tc_ok(q, k_cache, meta, nh, nkv, hd):
+            self.paged_attention_tc(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                                    scale=scale, window=window)
+            return
         if q.dtype == torch.bfloat16 and hd in (64, 128):
             self.paged_attention_mma(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                                      scale=scale, window=window)

@@ -511,18 +511,28 @@ MMA_CASES = [
     (12, 2, 128, 16, [700, 65, 64, 63], [300, 65, 1, 63], None),
     (6, 1, 64, 16, [500], [1], 100),
     (16, 2, 128, 32, [2100], [2048], None),
+    (8, 8, 128, 8, [700, 129], [257, 129], 200),
+    (24, 4, 128, 64, [1000, 300, 40], [130, 300, 7], None),
 ]
 
 
 @pytest.mark.parametrize("case", MMA_CASES)
 @pytest.mark.parametrize("standout", [False, True])
-@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles", "cluster2", "cluster4", "cluster8", "split4_scratch"])
+@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles", "cluster2", "cluster4", "cluster8", "split4_scratch", "tc"])
 def test_paged_attention_mma(case, standout, mode):
     nh, nkv, hd, ps, ctx_lens, q_lens, window = case
     dtype = torch.bfloat16
     q, kc, vc, m, want, scale = attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=5, standout=standout)
     out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=dtype).cuda()
     kw = {}
+    if mode == "tc":                      # tcgen05 + TMA: head size 128, pages that are whole swizzle atoms
+        if hd != 128 or ps % 8 != 0 or 128 % ps != 0:
+            pytest.skip("outside the tcgen05 attention kernel's range")
+        K().paged_attention_tc(q, kc, vc, out, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale, window=window)
+        K().tcgen05_check(q.device)
+        err = (out.double().cpu() - want).abs().max().item()
+        assert err < tol(dtype, max(1.0, want.abs().max().item())), err
+        return
     if mode == "split5":
         kw = dict(n_split=5, small_tiles=True)
     elif mode == "big_tiles":
