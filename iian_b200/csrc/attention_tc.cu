@@ -1,19 +1,21 @@
 // Paged causal attention for prefill portions on the fifth-generation tensor cores (head size 128, bf16).
 //
-// One CTA owns 128 rows of one (sequence, KV head): the rows are the (token, head) pairs of the query heads
-// that share the KV head, so a K/V tile fetched once serves all of them.  Keys are walked in tiles of 128.
-// Per tile: S = Q K^T by tcgen05.mma into tensor memory (128 lanes x 128 columns of float32); the softmax
-// warps read S with tcgen05.ld -- thread i owns row i, so maxima and sums need no shuffles --, write
-// P = exp2(S * scale - max) as bf16 into shared memory, and O += P V is a second tcgen05.mma into another
-// 128 columns of tensor memory.  K and V tiles come through the block table by TMA, one box per page and
-// half head (page_size rows x 64 values, 128-byte swizzle), into a two-stage ring; pages past the context
-// are asked for at an out-of-range coordinate, which TMA fills with zeros.
+// One CTA owns 256 rows of one (sequence, KV head), as two groups of 128: the rows are the (token, head) pairs
+// of the query heads that share the KV head, so a K/V tile fetched once serves all of them.  Keys are walked in
+// tiles of 128.  Per tile and group: S = Q K^T by tcgen05.mma into tensor memory (128 lanes x 128 columns of
+// float32); the group's four softmax warps read S with tcgen05.ld -- thread i owns row i, so maxima and sums
+// need no shuffles --, write P = exp2(S * scale - max) as bf16 into shared memory, and O += P V is a second
+// tcgen05.mma into another 128 columns of tensor memory (512 columns in all: S and O of both groups).  K and V
+// tiles come through the block table by TMA, one box per page and half head (page_size rows x 64 values,
+// 128-byte swizzle); pages past the context are asked for at an out-of-range coordinate, which TMA fills with
+// zeros.
 //
-// Roles: warp 0 lane 0 issues the TMA loads; warp 1 allocates tensor memory and its lane 0 issues the MMAs;
-// warps 2..5 are the softmax and, at the end, write O / sum.  S has two buffers, so that Q K^T of the next
-// tile runs while the softmax works on this one.  O is rescaled in tensor memory only when a row's maximum
-// grew by more than 2^8 since the last rescale (the sums and P carry the stale maximum until then; the
-// result is exact, P merely ranges up to 256).
+// Roles: warp 0 issues the TMA loads (a lane per page); warp 1 allocates tensor memory and its lane 0 issues the
+// MMAs; warps 2..5 and 6..9 are the softmax of group A and B and, at the end, write O / sum.  While one group's
+// softmax runs, the tensor cores work for the other, and the two groups' exponentials share the SM's special
+// function units.  O is rescaled in tensor memory only when a row's maximum grew by more than 2^8 since the
+// last rescale (the sums and P carry the stale maximum until then; the result is exact, P merely ranges up to
+// 256).
 //
 // Formula (reference, src/iian/paged_attn.cpp:112-145): scores q.k * scale; key j visible to the token at
 // position p iff j <= p and (window == 0 or p - j < window); softmax in float32; o = sum p_j v_j; a row that
@@ -28,7 +30,8 @@
 namespace iian {
 
 constexpr int AT_BM = 128, AT_BN = 128, AT_HD = 128;
-constexpr int AT_THREADS = 192;
+constexpr int AT_ROWS = 2 * AT_BM;              // rows of a CTA: two groups of 128
+constexpr int AT_THREADS = 320;
 constexpr unsigned kAtSpinLimit = 4u * 1000u * 1000u;
 constexpr int AT_HALF_BYTES = 128 * 128;          // 128 rows x 64 bf16: one 128-byte-swizzled half tile
 constexpr int AT_TILE_BYTES = 2 * AT_HALF_BYTES;  // a 128 x 128 bf16 tile
@@ -128,11 +131,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
     extern __shared__ __align__(1024) unsigned char at_smem_raw[];
     unsigned char * smem = (unsigned char *) (((uintptr_t) at_smem_raw + 1023) & ~(uintptr_t) 1023);
-    unsigned char * sQ = smem;                               // [2 halves][128 rows][128 B]
-    unsigned char * sK = sQ + AT_TILE_BYTES;                 // [2 stages][2 halves][128 keys][128 B]
-    unsigned char * sV = sK + 2 * AT_TILE_BYTES;             // [2 stages][2 halves][128 keys][128 B]
-    unsigned char * sP = sV + 2 * AT_TILE_BYTES;             // [2 buffers][2 halves of the keys][128 rows][128 B]
-    __shared__ __align__(8) unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
+    unsigned char * sQ = smem;                               // [2 groups][2 halves][128 rows][128 B]
+    unsigned char * sK = sQ + 2 * AT_TILE_BYTES;             // [2 halves][128 keys][128 B]
+    unsigned char * sV = sK + AT_TILE_BYTES;                 // [2 stages][2 halves][128 keys][128 B]
+    unsigned char * sP = sV + 2 * AT_TILE_BYTES;                 // [2 groups][2 halves of the keys][128 rows][128 B]
+    __shared__ __align__(8) unsigned long long k_full, k_empty, v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
     __shared__ unsigned tmem_base_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,56 +146,61 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     const int ctx = p.ctx_len[s];
     const int pos0 = ctx - q_len;
     const int rows_total = q_len * G;
-    const int row0 = ((int) gridDim.x - 1 - (int) blockIdx.x) * AT_BM;      // late rows see the most keys: they start first
+    const int row0 = ((int) gridDim.x - 1 - (int) blockIdx.x) * AT_ROWS;    // late rows see the most keys: they start first
     if (row0 >= rows_total) return;
 
+    // two groups of 128 rows (A, B) share every K/V tile; B may be empty, and A may need a tile less than B
+    const bool has_b = row0 + AT_BM < rows_total;
     const int tok_min = row0 / G;
-    const int tok_max = min(rows_total - 1, row0 + AT_BM - 1) / G;
-    const int k_hi = pos0 + tok_max;
+    const int k_hi_a = pos0 + min(rows_total - 1, row0 + AT_BM - 1) / G;
+    const int k_hi = pos0 + min(rows_total - 1, row0 + AT_ROWS - 1) / G;
     const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : 0;
     const int tile_lo = k_lo / AT_BN, tile_hi = k_hi / AT_BN;
     const int n_tiles = tile_hi - tile_lo + 1;
+    const int n_grp[2] = {k_hi_a / AT_BN - tile_lo + 1, has_b ? n_tiles : 0};
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
     int * status = p.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; i++) {
-            at_mbar_init(at_smem(&k_full[i]), 1); at_mbar_init(at_smem(&k_empty[i]), 1);
-            at_mbar_init(at_smem(&v_full[i]), 1); at_mbar_init(at_smem(&v_empty[i]), 1);
-            at_mbar_init(at_smem(&s_full[i]), 1); at_mbar_init(at_smem(&s_empty[i]), 4);
-            at_mbar_init(at_smem(&p_full[i]), 4); at_mbar_init(at_smem(&pv_done[i]), 1);
+        at_mbar_init(at_smem(&k_full), 1); at_mbar_init(at_smem(&k_empty), 1);
+        for (int g = 0; g < 2; g++) {
+            at_mbar_init(at_smem(&s_full[g]), 1); at_mbar_init(at_smem(&s_empty[g]), 4);
+            at_mbar_init(at_smem(&v_full[g]), 1); at_mbar_init(at_smem(&v_empty[g]), 1);
+            at_mbar_init(at_smem(&p_full[g]), 4); at_mbar_init(at_smem(&pv_done[g]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {          // tensor memory: S (two buffers of 128 columns) and O (128 columns)
+    if (warp == 1) {          // tensor memory: S of both groups (2 x 128 columns), O of both groups (2 x 128 columns)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_base_s)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // Q rows into the swizzled K-major layout: row r, 16-byte chunk c of half h at h * 16 KB + r * 128 + ((c ^ (r & 7)) << 4)
-    for (int idx = threadIdx.x; idx < AT_BM * 16; idx += AT_THREADS) {
-        const int r = idx >> 4, c = idx & 15;
-        const int R = row0 + r;
+    for (int idx = threadIdx.x; idx < AT_ROWS * 16; idx += AT_THREADS) {
+        const int rr = idx >> 4, c = idx & 15;
+        const int g = rr >> 7, r = rr & 127;
+        const int R = row0 + rr;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (R < rows_total) {
             const int tok = R / G, head = kvh * G + R % G;
             v = *reinterpret_cast<const uint4 *>(p.q + ((size_t) (q0 + tok) * p.nh + head) * AT_HD + c * 8);
         }
-        *reinterpret_cast<uint4 *>(sQ + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+        *reinterpret_cast<uint4 *>(sQ + g * AT_TILE_BYTES + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
     }
     at_fence_async_smem();
     at_fence_before();
     __syncthreads();
     at_fence_after();
     const unsigned tmem_base = tmem_base_s;
-    const unsigned tS = tmem_base, tO = tmem_base + 256u;
 
     if (warp == 0) {
         // ---- producer: lane g fetches page g of a tile (two boxes: the halves of the head); lane 0 posts the byte
-        // count.  K runs one tile ahead of V: the next Q K^T can start while this tile's P V still waits for P.
+        // count.  One stage is enough for K: K of the next tile is wanted when this tile's softmax is half way, long
+        // after both Q K^T of this tile have released it.  V has two: P V of a tile follows P V of the tile before
+        // closely, and a load that could start only then would be waited for in full.
         const int ps = p.page_size, pages_per_tile = AT_BN / ps;
         auto load_tile = [&](int i, bool is_k) -> bool {
             const int tile = tile_lo + i, st = i & 1;
-            const unsigned ph = (unsigned) (i >> 1) & 1u;
+            const unsigned ph = is_k ? (unsigned) i & 1u : (unsigned) (i >> 1) & 1u;      // K has one stage, V two
             int page = p.num_pages;                          // out of range: the box is filled with zeros
             if (lane < pages_per_tile) {
                 const int j0 = tile * AT_BN + lane * ps;
@@ -201,7 +209,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                     if (pg >= 0 && pg < p.num_pages) page = pg;
                 }
             }
-            const unsigned empty = at_smem(is_k ? &k_empty[st] : &v_empty[st]), full = at_smem(is_k ? &k_full[st] : &v_full[st]);
+            const unsigned empty = at_smem(is_k ? &k_empty : &v_empty[st]), full = at_smem(is_k ? &k_full : &v_full[st]);
             int ok = 1;
             if (lane == 0) {
                 ok = at_wait(empty, ph ^ 1u) ? 1 : 0;
@@ -211,89 +219,94 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) return false;
             if (lane < pages_per_tile) {
-                unsigned char * base = (is_k ? sK : sV) + st * AT_TILE_BYTES + lane * ps * 128;
+                unsigned char * base = (is_k ? sK : sV + st * AT_TILE_BYTES) + lane * ps * 128;
                 const CUtensorMap * map = is_k ? &map_k : &map_v;
                 at_tma_4d(at_smem(base), map, 0, 0, kvh, page, full);
                 at_tma_4d(at_smem(base + AT_HALF_BYTES), map, 64, 0, kvh, page, full);
             }
             return true;
         };
-        bool ok = load_tile(0, true);
-        if (ok && n_tiles > 1) ok = load_tile(1, true);
+        bool ok = true;
         for (int i = 0; ok && i < n_tiles; i++) {
+            ok = load_tile(i, true);
             if (ok) ok = load_tile(i, false);
-            if (ok && i + 2 < n_tiles) ok = load_tile(i + 2, true);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer -----------------------------------------------------------------------------------
         constexpr unsigned idesc_qk = at_idesc(AT_BM, AT_BN, false);
         constexpr unsigned idesc_pv = at_idesc(AT_BM, AT_HD, true);
+        constexpr int kHalf16 = AT_HALF_BYTES >> 4;
         // descriptors are built once; a step along K adds a constant (in units of 16 bytes) to the start address
-        const unsigned long long dq = at_desc(at_smem(sQ), 16, 1024);
-        const unsigned long long dk[2] = {at_desc(at_smem(sK), 16, 1024), at_desc(at_smem(sK + AT_TILE_BYTES), 16, 1024)};
+        const unsigned long long dq[2] = {at_desc(at_smem(sQ), 16, 1024), at_desc(at_smem(sQ + AT_TILE_BYTES), 16, 1024)};
+        const unsigned long long dk = at_desc(at_smem(sK), 16, 1024);
         const unsigned long long dp[2] = {at_desc(at_smem(sP), 16, 1024), at_desc(at_smem(sP + AT_TILE_BYTES), 16, 1024)};
         const unsigned long long dv[2] = {at_desc(at_smem(sV), AT_HALF_BYTES, 1024), at_desc(at_smem(sV + AT_TILE_BYTES), AT_HALF_BYTES, 1024)};
+        // S = Q K^T of tile i for every group that still has tiles; K is released when the products have read it
         auto issue_qk = [&](int i) -> bool {
-            const int st = i & 1, b = i & 1;
-            const unsigned ph = (unsigned) (i >> 1) & 1u;
-            if (!at_wait(at_smem(&k_full[st]), ph)) { status[0] = 3; status[1] = i; return false; }
-            if (!at_wait(at_smem(&s_empty[b]), ph ^ 1u)) { status[0] = 4; status[1] = i; return false; }
-            at_fence_after();
+            const unsigned ph = (unsigned) i & 1u;
+            if (!at_wait(at_smem(&k_full), ph)) { status[0] = 3; status[1] = i; return false; }
+            for (int g = 0; g < 2; g++) {
+                if (i >= n_grp[g]) continue;
+                if (!at_wait(at_smem(&s_empty[g]), ph ^ 1u)) { status[0] = 4; status[1] = i; return false; }
+                at_fence_after();
 #pragma unroll
-            for (int k = 0; k < 8; k++) {             // 16 values of the head per step: 32 bytes inside the atom, halves 16 KB apart
-                constexpr int kHalf16 = AT_HALF_BYTES >> 4;
-                const unsigned long long off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
-                at_mma(tS + (unsigned) (b * 128), dq + off, dk[st] + off, idesc_qk, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 8; k++) {         // 16 values of the head per step: 32 bytes inside the atom, halves 16 KB apart
+                    const unsigned long long off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
+                    at_mma(tmem_base + (unsigned) (g * 128), dq[g] + off, dk + off, idesc_qk, k > 0 ? 1u : 0u);
+                }
+                at_commit(at_smem(&s_full[g]));
             }
-            at_commit(at_smem(&s_full[b]));
-            at_commit(at_smem(&k_empty[st]));
+            at_commit(at_smem(&k_empty));
             return true;
         };
-        // Q K^T runs two tiles ahead of P V: S(i + 2) may be written as soon as the softmax warps hold S(i) in
-        // registers, which is long before they deliver P(i)
         if (!issue_qk(0)) goto done;
-        if (n_tiles > 1 && !issue_qk(1)) goto done;
         for (int i = 0; i < n_tiles; i++) {
-            if (i + 2 < n_tiles && !issue_qk(i + 2)) goto done;
+            if (i + 1 < n_tiles && !issue_qk(i + 1)) goto done;      // runs while the softmax warps work on tile i
+            const unsigned ph = (unsigned) i & 1u;
             const int st = i & 1;
-            const unsigned ph = (unsigned) (i >> 1) & 1u;
-            if (!at_wait(at_smem(&p_full[i & 1]), ph)) { status[0] = 5; status[1] = i; goto done; }
-            if (!at_wait(at_smem(&v_full[st]), ph)) { status[0] = 6; status[1] = i; goto done; }
-            at_fence_after();
+            if (!at_wait(at_smem(&v_full[st]), (unsigned) (i >> 1) & 1u)) { status[0] = 6; status[1] = i; goto done; }
+            for (int g = 0; g < 2; g++) {
+                if (i >= n_grp[g]) continue;
+                if (!at_wait(at_smem(&p_full[g]), ph)) { status[0] = 5; status[1] = i; goto done; }
+                at_fence_after();
 #pragma unroll
-            for (int k = 0; k < 8; k++) {             // 16 keys per step: P is K-major along the keys, V advances 16 key rows
-                constexpr int kHalf16 = AT_HALF_BYTES >> 4;
-                const unsigned long long a_off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
-                const unsigned long long b_off = (unsigned long long) (k * 16 * 128 / 16);
-                at_mma(tO, dp[st] + a_off, dv[st] + b_off, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 8; k++) {         // 16 keys per step: P is K-major along the keys, V advances 16 key rows
+                    const unsigned long long a_off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
+                    const unsigned long long b_off = (unsigned long long) (k * 16 * 128 / 16);
+                    at_mma(tmem_base + 256u + (unsigned) (g * 128), dp[g] + a_off, dv[st] + b_off, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                at_commit(at_smem(&pv_done[g]));
             }
             at_commit(at_smem(&v_empty[st]));
-            at_commit(at_smem(&pv_done[st]));
         }
     } else if (warp >= 2) {
-        // ---- softmax: thread = row -----------------------------------------------------------------------
+        // ---- softmax: warps 2..5 are group A, 6..9 group B; thread = row ---------------------------------------
+        const int g = (warp - 2) >> 2;
         const int qd = warp & 3;
         const int r = qd * 32 + lane;
-        const int R = row0 + r;
+        const int R = row0 + g * AT_BM + r;
         const bool row_ok = R < rows_total;
         const int row_pos = pos0 + (row_ok ? R / G : 0);
         const unsigned lane_addr = (unsigned) (qd * 32) << 16;
+        const unsigned tS = tmem_base + (unsigned) (g * 128), tO = tmem_base + 256u + (unsigned) (g * 128);
+        unsigned char * sPg = sP + g * AT_TILE_BYTES;
+        const int n_mine = n_grp[g];
         float m_run = -INFINITY, l_run = 0.0f;
         const float sl = p.scale_log2;
-        for (int i = 0; i < n_tiles; i++) {
-            const int b = i & 1;
-            const unsigned ph = (unsigned) (i >> 1) & 1u;
+        bool failed = false;
+        for (int i = 0; i < n_mine; i++) {
+            const unsigned ph = (unsigned) i & 1u;
             const int key0 = (tile_lo + i) * AT_BN;
-            if (!at_wait(at_smem(&s_full[b]), ph)) { if (lane == 0) { status[0] = 7; status[1] = i; } break; }
+            if (!at_wait(at_smem(&s_full[g]), ph)) { if (lane == 0) { status[0] = 7; status[1] = i; } failed = true; break; }
             at_fence_after();
-            // the whole row of S into registers; the buffer is then free for the tile after the next
+            // the whole row of S into registers; tensor memory is then free for the next tile's Q K^T
             unsigned v[AT_BN];
 #pragma unroll
-            for (int c0 = 0; c0 < AT_BN; c0 += 32) at_ld32(tS + lane_addr + (unsigned) (b * 128 + c0), v + c0);
+            for (int c0 = 0; c0 < AT_BN; c0 += 32) at_ld32(tS + lane_addr + (unsigned) c0, v + c0);
             at_wait_ld();
             at_fence_before();
             __syncwarp();
-            if (lane == 0) at_arrive(at_smem(&s_empty[b]));
+            if (lane == 0) at_arrive(at_smem(&s_empty[g]));
             // visible keys of this row in this tile: columns [lo, hi]; most tiles lie wholly below the diagonal
             const int hi = row_ok ? min(AT_BN - 1, row_pos - key0) : -1;
             const int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : 0;
@@ -329,25 +342,22 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 }
             }
             l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            // O may be rescaled only between products: wait for the one of the tile before (rare: the maximum moved)
-            if (i > 0 && __any_sync(0xffffffffu, moved)) {
-                if (!at_wait(at_smem(&pv_done[(i - 1) & 1]), (unsigned) ((i - 1) >> 1) & 1u)) { if (lane == 0) { status[0] = 8; status[1] = i; } break; }
+            if (i > 0) {        // P (and O, if it has to be rescaled) are free once the product of the tile before is complete
+                if (!at_wait(at_smem(&pv_done[g]), ph ^ 1u)) { if (lane == 0) { status[0] = 8; status[1] = i; } failed = true; break; }
                 at_fence_after();
+                if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < AT_HD; c0 += 32) {
-                    unsigned o[32];
-                    at_ld32(tO + lane_addr + (unsigned) c0, o);
-                    at_wait_ld();
+                    for (int c0 = 0; c0 < AT_HD; c0 += 32) {
+                        unsigned o[32];
+                        at_ld32(tO + lane_addr + (unsigned) c0, o);
+                        at_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
-                    at_st32(tO + lane_addr + (unsigned) c0, o);
+                        for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                        at_st32(tO + lane_addr + (unsigned) c0, o);
+                    }
+                    at_wait_st();
                 }
-                at_wait_st();
-                at_fence_before();
             }
-            // this P buffer was last read by the product of the tile before the last
-            if (i > 1 && !at_wait(at_smem(&pv_done[b]), (unsigned) ((i - 2) >> 1) & 1u)) { if (lane == 0) { status[0] = 10; status[1] = i; } break; }
-            unsigned char * sPb = sP + b * AT_TILE_BYTES;
 #pragma unroll
             for (int c = 0; c < 16; c++) {            // sixteen 16-byte chunks (8 keys each) of this row
                 unsigned pk[4];
@@ -356,44 +366,46 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                     __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * e]), __uint_as_float(v[8 * c + 2 * e + 1]));
                     pk[e] = *reinterpret_cast<unsigned *>(&h);
                 }
-                *reinterpret_cast<uint4 *>(sPb + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+                *reinterpret_cast<uint4 *>(sPg + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
                     make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             at_fence_async_smem();                    // P was written by ordinary stores, the MMA reads it through the async proxy
             at_fence_before();
             __syncwarp();
-            if (lane == 0) at_arrive(at_smem(&p_full[b]));
+            if (lane == 0) at_arrive(at_smem(&p_full[g]));
         }
         // ---- O / sum -> out ---------------------------------------------------------------------------
-        if (at_wait(at_smem(&pv_done[(n_tiles - 1) & 1]), (unsigned) ((n_tiles - 1) >> 1) & 1u)) {
-            at_fence_after();
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            __nv_bfloat16 * dst = nullptr;
-            if (row_ok) {
-                const int tok = R / G, head = kvh * G + R % G;
-                dst = p.out + ((size_t) (q0 + tok) * p.nh + head) * AT_HD;
-            }
-#pragma unroll 1
-            for (int c0 = 0; c0 < AT_HD; c0 += 32) {
-                unsigned v[32];
-                at_ld32(tO + lane_addr + (unsigned) c0, v);
-                at_wait_ld();
+        if (n_mine > 0 && !failed) {
+            if (at_wait(at_smem(&pv_done[g]), (unsigned) (n_mine - 1) & 1u)) {
+                at_fence_after();
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                __nv_bfloat16 * dst = nullptr;
                 if (row_ok) {
+                    const int tok = R / G, head = kvh * G + R % G;
+                    dst = p.out + ((size_t) (q0 + tok) * p.nh + head) * AT_HD;
+                }
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_HD; c0 += 32) {
+                    unsigned o[32];
+                    at_ld32(tO + lane_addr + (unsigned) c0, o);
+                    at_wait_ld();
+                    if (row_ok) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; q4++) {
-                        uint4 pk;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
-                        pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
-                        pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
-                        *reinterpret_cast<uint4 *>(dst + c0 + 8 * q4) = pk;
+                        for (int q4 = 0; q4 < 4; q4++) {
+                            uint4 pk;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 0]) * inv, __uint_as_float(o[8 * q4 + 1]) * inv);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 2]) * inv, __uint_as_float(o[8 * q4 + 3]) * inv);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 4]) * inv, __uint_as_float(o[8 * q4 + 5]) * inv);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 6]) * inv, __uint_as_float(o[8 * q4 + 7]) * inv);
+                            pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+                            pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+                            *reinterpret_cast<uint4 *>(dst + c0 + 8 * q4) = pk;
+                        }
                     }
                 }
+            } else if (lane == 0) {
+                status[0] = 9; status[1] = n_mine;
             }
-        } else if (lane == 0) {
-            status[0] = 9; status[1] = n_tiles;
         }
     }
 done:
@@ -469,7 +481,7 @@ IIAN_API int iian_attention_tc(const void * q, const void * k_cache, const void 
         configured = true;
     }
     const int max_rows = max_q_len * (nh / nkv);
-    dim3 grid((max_rows + AT_BM - 1) / AT_BM, nkv, S);
+    dim3 grid((max_rows + AT_ROWS - 1) / AT_ROWS, nkv, S);
     attention_tc_kernel<<<grid, AT_THREADS, smem, stream>>>(mk, mv, p);
     return iian_launch_status();
 }
