@@ -4,18 +4,21 @@
 // of the query heads that share the KV head, so a K/V tile fetched once serves all of them.  Keys are walked in
 // tiles of 128.  Per tile and group: S = Q K^T by tcgen05.mma into tensor memory (128 lanes x 128 columns of
 // float32); the group's four softmax warps read S with tcgen05.ld -- thread i owns row i, so maxima and sums
-// need no shuffles --, write P = exp2(S * scale - max) as bf16 into shared memory, and O += P V is a second
-// tcgen05.mma into another 128 columns of tensor memory (512 columns in all: S and O of both groups).  K and V
-// tiles come through the block table by TMA, one box per page and half head (page_size rows x 64 values,
-// 128-byte swizzle); pages past the context are asked for at an out-of-range coordinate, which TMA fills with
-// zeros.
+// need no shuffles --, and write P = exp2(S * scale - max) as bf16 pairs back into the first 64 of those
+// columns with tcgen05.st; O += P V is a second tcgen05.mma whose A operand is P in tensor memory (no shared
+// memory traffic for P, which matters: a 128 x 128 x 16 MMA with both operands in shared memory reads 8 KB per
+// 64 cycles, all the shared-memory bandwidth there is) and whose B operand is the V tile as TMA left it
+// (MN-major: a key's row holds 64 values of the head).  Tensor memory: S/P and O of both groups, 512 columns.
+// K and V tiles come through the block table by TMA, one box per page and half head (page_size rows x 64
+// values, 128-byte swizzle), two stages each; pages past the context are asked for at an out-of-range
+// coordinate, which TMA fills with zeros.
 //
 // Roles: warp 0 issues the TMA loads (a lane per page); warp 1 allocates tensor memory and its lane 0 issues the
-// MMAs; warps 2..5 and 6..9 are the softmax of group A and B and, at the end, write O / sum.  While one group's
-// softmax runs, the tensor cores work for the other, and the two groups' exponentials share the SM's special
-// function units.  O is rescaled in tensor memory only when a row's maximum grew by more than 2^8 since the
-// last rescale (the sums and P carry the stale maximum until then; the result is exact, P merely ranges up to
-// 256).
+// MMAs; warps 2..5 and 6..9 are the softmax of group A and B and, at the end, write O / sum.  A group's chain
+// is Q K^T -> softmax -> P V -> next Q K^T (S and P share columns, and the tensor pipe runs one thread's MMAs in
+// order); while one group's softmax runs, the tensor cores work for the other.  O is rescaled in tensor memory
+// only when a row's maximum grew by more than 2^8 since the last rescale (the sums and P carry the stale
+// maximum until then; the result is exact, P merely ranges up to 256).
 //
 // Formula (reference, src/iian/paged_attn.cpp:112-145): scores q.k * scale; key j visible to the token at
 // position p iff j <= p and (window == 0 or p - j < window); softmax in float32; o = sum p_j v_j; a row that
@@ -81,6 +84,12 @@ __device__ __forceinline__ void at_mma(unsigned d_tmem, unsigned long long a_des
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (lane = row, 32-bit column = two consecutive bf16 along K)
+__device__ __forceinline__ void at_mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void at_ld32(unsigned taddr, unsigned * r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -132,10 +141,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     extern __shared__ __align__(1024) unsigned char at_smem_raw[];
     unsigned char * smem = (unsigned char *) (((uintptr_t) at_smem_raw + 1023) & ~(uintptr_t) 1023);
     unsigned char * sQ = smem;                               // [2 groups][2 halves][128 rows][128 B]
-    unsigned char * sK = sQ + 2 * AT_TILE_BYTES;             // [2 halves][128 keys][128 B]
-    unsigned char * sV = sK + AT_TILE_BYTES;                 // [2 stages][2 halves][128 keys][128 B]
-    unsigned char * sP = sV + 2 * AT_TILE_BYTES;                 // [2 groups][2 halves of the keys][128 rows][128 B]
-    __shared__ __align__(8) unsigned long long k_full, k_empty, v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
+    unsigned char * sK = sQ + 2 * AT_TILE_BYTES;             // [2 stages][2 halves][128 keys][128 B]
+    unsigned char * sV = sK + 2 * AT_TILE_BYTES;             // [2 stages][2 halves][128 keys][128 B]
+    __shared__ __align__(8) unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
     __shared__ unsigned tmem_base_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -162,9 +170,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     int * status = p.status;
 
     if (threadIdx.x == 0) {
-        at_mbar_init(at_smem(&k_full), 1); at_mbar_init(at_smem(&k_empty), 1);
         for (int g = 0; g < 2; g++) {
-            at_mbar_init(at_smem(&s_full[g]), 1); at_mbar_init(at_smem(&s_empty[g]), 4);
+            at_mbar_init(at_smem(&s_full[g]), 1);
+            at_mbar_init(at_smem(&k_full[g]), 1); at_mbar_init(at_smem(&k_empty[g]), 1);
             at_mbar_init(at_smem(&v_full[g]), 1); at_mbar_init(at_smem(&v_empty[g]), 1);
             at_mbar_init(at_smem(&p_full[g]), 4); at_mbar_init(at_smem(&pv_done[g]), 1);
         }
@@ -194,13 +202,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
 
     if (warp == 0) {
         // ---- producer: lane g fetches page g of a tile (two boxes: the halves of the head); lane 0 posts the byte
-        // count.  One stage is enough for K: K of the next tile is wanted when this tile's softmax is half way, long
-        // after both Q K^T of this tile have released it.  V has two: P V of a tile follows P V of the tile before
-        // closely, and a load that could start only then would be waited for in full.
+        // count.  Two stages each for K and V.
         const int ps = p.page_size, pages_per_tile = AT_BN / ps;
         auto load_tile = [&](int i, bool is_k) -> bool {
             const int tile = tile_lo + i, st = i & 1;
-            const unsigned ph = is_k ? (unsigned) i & 1u : (unsigned) (i >> 1) & 1u;      // K has one stage, V two
+            const unsigned ph = (unsigned) (i >> 1) & 1u;
             int page = p.num_pages;                          // out of range: the box is filled with zeros
             if (lane < pages_per_tile) {
                 const int j0 = tile * AT_BN + lane * ps;
@@ -209,7 +215,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                     if (pg >= 0 && pg < p.num_pages) page = pg;
                 }
             }
-            const unsigned empty = at_smem(is_k ? &k_empty : &v_empty[st]), full = at_smem(is_k ? &k_full : &v_full[st]);
+            const unsigned empty = at_smem(is_k ? &k_empty[st] : &v_empty[st]), full = at_smem(is_k ? &k_full[st] : &v_full[st]);
             int ok = 1;
             if (lane == 0) {
                 ok = at_wait(empty, ph ^ 1u) ? 1 : 0;
@@ -219,16 +225,16 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) return false;
             if (lane < pages_per_tile) {
-                unsigned char * base = (is_k ? sK : sV + st * AT_TILE_BYTES) + lane * ps * 128;
+                unsigned char * base = (is_k ? sK : sV) + st * AT_TILE_BYTES + lane * ps * 128;
                 const CUtensorMap * map = is_k ? &map_k : &map_v;
                 at_tma_4d(at_smem(base), map, 0, 0, kvh, page, full);
                 at_tma_4d(at_smem(base + AT_HALF_BYTES), map, 64, 0, kvh, page, full);
             }
             return true;
         };
-        bool ok = true;
+        bool ok = load_tile(0, true);
         for (int i = 0; ok && i < n_tiles; i++) {
-            ok = load_tile(i, true);
+            if (i + 1 < n_tiles) ok = load_tile(i + 1, true);      // K runs a tile ahead of V
             if (ok) ok = load_tile(i, false);
         }
     } else if (warp == 1 && lane == 0) {
@@ -238,46 +244,42 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
         constexpr int kHalf16 = AT_HALF_BYTES >> 4;
         // descriptors are built once; a step along K adds a constant (in units of 16 bytes) to the start address
         const unsigned long long dq[2] = {at_desc(at_smem(sQ), 16, 1024), at_desc(at_smem(sQ + AT_TILE_BYTES), 16, 1024)};
-        const unsigned long long dk = at_desc(at_smem(sK), 16, 1024);
-        const unsigned long long dp[2] = {at_desc(at_smem(sP), 16, 1024), at_desc(at_smem(sP + AT_TILE_BYTES), 16, 1024)};
+        const unsigned long long dk[2] = {at_desc(at_smem(sK), 16, 1024), at_desc(at_smem(sK + AT_TILE_BYTES), 16, 1024)};
         const unsigned long long dv[2] = {at_desc(at_smem(sV), AT_HALF_BYTES, 1024), at_desc(at_smem(sV + AT_TILE_BYTES), AT_HALF_BYTES, 1024)};
-        // S = Q K^T of tile i for every group that still has tiles; K is released when the products have read it
-        auto issue_qk = [&](int i) -> bool {
-            const unsigned ph = (unsigned) i & 1u;
-            if (!at_wait(at_smem(&k_full), ph)) { status[0] = 3; status[1] = i; return false; }
-            for (int g = 0; g < 2; g++) {
-                if (i >= n_grp[g]) continue;
-                if (!at_wait(at_smem(&s_empty[g]), ph ^ 1u)) { status[0] = 4; status[1] = i; return false; }
-                at_fence_after();
-#pragma unroll
-                for (int k = 0; k < 8; k++) {         // 16 values of the head per step: 32 bytes inside the atom, halves 16 KB apart
-                    const unsigned long long off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
-                    at_mma(tmem_base + (unsigned) (g * 128), dq[g] + off, dk + off, idesc_qk, k > 0 ? 1u : 0u);
-                }
-                at_commit(at_smem(&s_full[g]));
-            }
-            at_commit(at_smem(&k_empty));
-            return true;
-        };
-        if (!issue_qk(0)) goto done;
-        for (int i = 0; i < n_tiles; i++) {
-            if (i + 1 < n_tiles && !issue_qk(i + 1)) goto done;      // runs while the softmax warps work on tile i
-            const unsigned ph = (unsigned) i & 1u;
+        // S = Q K^T of tile i for group g.  S and P of a group share tensor memory, so this must follow the group's
+        // P V of the tile before in program order (the tensor pipe runs a thread's MMAs in order).
+        auto issue_qk = [&](int g, int i) {
             const int st = i & 1;
-            if (!at_wait(at_smem(&v_full[st]), (unsigned) (i >> 1) & 1u)) { status[0] = 6; status[1] = i; goto done; }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {             // 16 values of the head per step: 32 bytes inside the atom, halves 16 KB apart
+                const unsigned long long off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
+                at_mma(tmem_base + (unsigned) (g * 128), dq[g] + off, dk[st] + off, idesc_qk, k > 0 ? 1u : 0u);
+            }
+            at_commit(at_smem(&s_full[g]));
+        };
+        if (!at_wait(at_smem(&k_full[0]), 0u)) { status[0] = 3; status[1] = 0; goto done; }
+        at_fence_after();
+        for (int g = 0; g < 2; g++)
+            if (n_grp[g] > 0) issue_qk(g, 0);
+        at_commit(at_smem(&k_empty[0]));
+        for (int i = 0; i < n_tiles; i++) {
+            const int st = i & 1;
+            const unsigned ph = (unsigned) (i >> 1) & 1u;
+            if (!at_wait(at_smem(&v_full[st]), ph)) { status[0] = 6; status[1] = i; goto done; }
+            if (i + 1 < n_tiles && !at_wait(at_smem(&k_full[(i + 1) & 1]), (unsigned) ((i + 1) >> 1) & 1u)) { status[0] = 3; status[1] = i + 1; goto done; }
             for (int g = 0; g < 2; g++) {
                 if (i >= n_grp[g]) continue;
-                if (!at_wait(at_smem(&p_full[g]), ph)) { status[0] = 5; status[1] = i; goto done; }
+                if (!at_wait(at_smem(&p_full[g]), (unsigned) i & 1u)) { status[0] = 5; status[1] = i; goto done; }
                 at_fence_after();
 #pragma unroll
-                for (int k = 0; k < 8; k++) {         // 16 keys per step: P is K-major along the keys, V advances 16 key rows
-                    const unsigned long long a_off = (unsigned long long) ((k >> 2) * kHalf16 + (k & 3) * 2);
-                    const unsigned long long b_off = (unsigned long long) (k * 16 * 128 / 16);
-                    at_mma(tmem_base + 256u + (unsigned) (g * 128), dp[g] + a_off, dv[st] + b_off, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < 8; k++)           // 16 keys per step: 8 columns of packed P, 16 key rows of V
+                    at_mma_ts(tmem_base + 256u + (unsigned) (g * 128), tmem_base + (unsigned) (g * 128 + k * 8),
+                              dv[st] + (unsigned long long) (k * 16 * 128 / 16), idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
                 at_commit(at_smem(&pv_done[g]));
+                if (i + 1 < n_grp[g]) issue_qk(g, i + 1);
             }
             at_commit(at_smem(&v_empty[st]));
+            if (i + 1 < n_tiles) at_commit(at_smem(&k_empty[(i + 1) & 1]));
         }
     } else if (warp >= 2) {
         // ---- softmax: warps 2..5 are group A, 6..9 group B; thread = row ---------------------------------------
@@ -289,7 +291,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
         const int row_pos = pos0 + (row_ok ? R / G : 0);
         const unsigned lane_addr = (unsigned) (qd * 32) << 16;
         const unsigned tS = tmem_base + (unsigned) (g * 128), tO = tmem_base + 256u + (unsigned) (g * 128);
-        unsigned char * sPg = sP + g * AT_TILE_BYTES;
         const int n_mine = n_grp[g];
         float m_run = -INFINITY, l_run = 0.0f;
         const float sl = p.scale_log2;
@@ -304,9 +305,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
 #pragma unroll
             for (int c0 = 0; c0 < AT_BN; c0 += 32) at_ld32(tS + lane_addr + (unsigned) c0, v + c0);
             at_wait_ld();
-            at_fence_before();
-            __syncwarp();
-            if (lane == 0) at_arrive(at_smem(&s_empty[g]));
             // visible keys of this row in this tile: columns [lo, hi]; most tiles lie wholly below the diagonal
             const int hi = row_ok ? min(AT_BN - 1, row_pos - key0) : -1;
             const int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : 0;
@@ -358,18 +356,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                     at_wait_st();
                 }
             }
+            // P as bf16 pairs into the tensor-memory columns S came from (64 of its 128)
 #pragma unroll
-            for (int c = 0; c < 16; c++) {            // sixteen 16-byte chunks (8 keys each) of this row
-                unsigned pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * e]), __uint_as_float(v[8 * c + 2 * e + 1]));
-                    pk[e] = *reinterpret_cast<unsigned *>(&h);
-                }
-                *reinterpret_cast<uint4 *>(sPg + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
-                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            for (int j = 0; j < AT_BN; j += 2) {      // packed in place: pair j / 2 overwrites a value already used
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                v[j >> 1] = *reinterpret_cast<unsigned *>(&h);
             }
-            at_fence_async_smem();                    // P was written by ordinary stores, the MMA reads it through the async proxy
+            at_st32(tS + lane_addr, v);
+            at_st32(tS + lane_addr + 32u, v + 32);
+            at_wait_st();
             at_fence_before();
             __syncwarp();
             if (lane == 0) at_arrive(at_smem(&p_full[g]));
@@ -473,7 +468,7 @@ IIAN_API int iian_attention_tc(const void * q, const void * k_cache, const void 
     p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
-    const size_t smem = (size_t) 7 * AT_TILE_BYTES + 1024;
+    const size_t smem = (size_t) 6 * AT_TILE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
