@@ -231,7 +231,7 @@ def main() -> int:
         # ---- prefill of one 2,048-token prompt --------------------------------------------------
         toks = rand_tokens(PREFILL_TOKENS)
         times = []
-        for i in range(W + 3):
+        for i in range(W + 5):
             rc = mgr.new_request()
             mgr.allot_state(rc)
             assert mgr.allocate(rc, 0, PREFILL_TOKENS)
@@ -244,7 +244,7 @@ def main() -> int:
             if i >= W:
                 times.append(s_ev.elapsed_time(e_ev))
             mgr.free(rc)
-        p_ms = statistics.mean(times)
+        p_ms = statistics.median(times)
         T = PREFILL_TOKENS
         flops = 2.0 * T * cfg.num_hidden_layers * layer_w + 2.0 * head_w \
             + cfg.num_hidden_layers * 4.0 * cfg.q_size * T * (T + 1) / 2

@@ -48,6 +48,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--graph", action="store_true", help="time the launches as one replayed CUDA graph")
     ap.add_argument("--cfg", type=int, default=0, help="gemm_skinny: tile configuration (0: the kernel's choice)")
+    ap.add_argument("--bn", type=int, default=0, help="gemm_tcgen05: columns of a tile, 128 or 256 (0: the engine's choice)")
+    ap.add_argument("--ksplit", type=int, default=0, help="gemm_skinny: CTAs that share K for one row block (0: the engine's choice)")
     args = ap.parse_args(argv)
 
     import torch
@@ -106,9 +108,9 @@ def main(argv=None) -> int:
         swiglu = args.epilogue == "swiglu"
         out = torch.empty(n, m // 2 if swiglu else m, device=dev, dtype=bf)
         if args.kernel == "gemm_skinny":
-            us = timeit(lambda i: k.gemm_skinny(x, ws[i % copies], out, cfg=args.cfg, epilogue=1 if swiglu else 0))
+            us = timeit(lambda i: k.gemm_skinny(x, ws[i % copies], out, cfg=args.cfg, ksplit=args.ksplit, epilogue=1 if swiglu else 0))
         elif args.kernel == "gemm_tcgen05":
-            us = timeit(lambda i: k.gemm_tcgen05(x, ws[i % copies], out, epilogue=1 if swiglu else 0))
+            us = timeit(lambda i: k.gemm_tcgen05(x, ws[i % copies], out, epilogue=1 if swiglu else 0, bn=args.bn))
             k.tcgen05_check(dev)
         else:
             us = timeit(lambda i: torch.mm(x, ws[i % copies].t(), out=out))
