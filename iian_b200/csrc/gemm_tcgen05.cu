@@ -30,9 +30,25 @@ constexpr int TC_BK = 64;                 // 64 bf16 = 128 bytes = one swizzle a
 constexpr int TC_THREADS = 192;           // warp 0: TMA, warp 1: MMA + TMEM, warps 2..5: epilogue
 constexpr unsigned kSpinLimit = 2u * 1000u * 1000u;
 
-enum { EPI_STORE = 0, EPI_SWIGLU8 = 1 };
+enum { EPI_STORE = 0, EPI_SWIGLU8 = 1, EPI_RESNORM = 2 };
 
 struct TcStatus { int code; int where; };
+
+// The fused forms of the epilogue (all null / zero: plain product), as in the weight-streaming kernel.
+//  * in_partial [T, in_tiles]: the activations are a residual stream times a norm weight, not yet normalised; row t
+//    of the result is multiplied by rsqrt(sum_i in_partial[t, i] / width + eps) (RMSNorm's factor per row commutes
+//    with the product, src/iian/graph.cpp:105-114).
+//  * res / norm_w / out_partial (EPI_RESNORM): the product is the output of a sub-layer: it is rounded to bfloat16 as
+//    the unfused route would store it, added to the float32 residual stream res [T, N] in place, res * norm_w is
+//    stored as bfloat16, and the sum of squares of the tile's columns of every row goes to out_partial [T, n_tiles].
+struct TcExtra {
+    const float * in_partial;
+    int in_tiles;
+    float inv_width, eps;
+    float * res;
+    const float * norm_w;
+    float * out_partial;
+};
 
 __device__ __forceinline__ unsigned smem_addr(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
 
@@ -105,7 +121,11 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 // One accumulator tile (128 x BN, float32, in tensor memory) -> global memory.  `r` holds 32 consecutive
 // columns of this thread's row.
 template <int EPI, typename OutT>
-__device__ __forceinline__ void epilogue_store32(const unsigned * r, OutT * __restrict__ out, int row, int col0, int N, int ldo) {
+__device__ __forceinline__ void epilogue_store32(unsigned * r, OutT * __restrict__ out, int row, int col0, int N, int ldo, float rs) {
+    if (rs != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * rs);
+    }
     if (EPI == EPI_STORE) {
         OutT * dst = out + (size_t) row * ldo + col0;
         if (col0 + 32 <= N && (((uintptr_t) dst) & 15) == 0) {
@@ -158,6 +178,48 @@ __device__ __forceinline__ void epilogue_store32(const unsigned * r, OutT * __re
     }
 }
 
+// EPI_RESNORM for 32 columns of one row: returns the sum of squares of the new residual values.
+__device__ __forceinline__ float epilogue_resnorm32(const unsigned * r, __nv_bfloat16 * __restrict__ out, float * __restrict__ res,
+                                                   const float * __restrict__ norm_w, int row, int col0, int N, float rs) {
+    float sq = 0.0f;
+    float * rp = res + (size_t) row * N + col0;
+    __nv_bfloat16 * op = out + (size_t) row * N + col0;
+    if (col0 + 32 <= N && (((uintptr_t) rp) & 15) == 0 && (((uintptr_t) op) & 15) == 0) {
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            float x[8];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const float4 old = *reinterpret_cast<const float4 *>(rp + 8 * v + 4 * h);
+                float4 nw;
+                nw.x = old.x + __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[8 * v + 4 * h + 0]) * rs));
+                nw.y = old.y + __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[8 * v + 4 * h + 1]) * rs));
+                nw.z = old.z + __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[8 * v + 4 * h + 2]) * rs));
+                nw.w = old.w + __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[8 * v + 4 * h + 3]) * rs));
+                *reinterpret_cast<float4 *>(rp + 8 * v + 4 * h) = nw;
+                sq += nw.x * nw.x + nw.y * nw.y + nw.z * nw.z + nw.w * nw.w;
+                const float4 w4 = __ldg(reinterpret_cast<const float4 *>(norm_w + col0 + 8 * v + 4 * h));
+                x[4 * h + 0] = nw.x * w4.x; x[4 * h + 1] = nw.y * w4.y; x[4 * h + 2] = nw.z * w4.z; x[4 * h + 3] = nw.w * w4.w;
+            }
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(x[0], x[1]), h1 = __floats2bfloat162_rn(x[2], x[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(x[4], x[5]), h3 = __floats2bfloat162_rn(x[6], x[7]);
+            pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+            pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+            *reinterpret_cast<uint4 *>(op + 8 * v) = pk;
+        }
+    } else {
+        for (int i = 0; i < 32; i++)
+            if (col0 + i < N) {
+                const float nw = rp[i] + __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i]) * rs));
+                rp[i] = nw;
+                sq += nw * nw;
+                op[i] = __float2bfloat16_rn(nw * norm_w[col0 + i]);
+            }
+    }
+    return sq;
+}
+
 // Persistent: gridDim.x CTAs (one per SM) walk the output tiles round-robin, row tiles fastest, so the
 // CTAs that run together share a few weight tiles (read from HBM once, then from L2) and sweep the
 // activations, which stay in L2 as a whole.  Tensor memory holds two accumulators: while the epilogue
@@ -165,7 +227,7 @@ __device__ __forceinline__ void epilogue_store32(const unsigned * r, OutT * __re
 template <int BN, int STAGES, int EPI, typename OutT>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-    OutT * __restrict__ out, int T, int N, int K, int ldo, TcStatus * status) {
+    OutT * __restrict__ out, int T, int N, int K, int ldo, TcStatus * status, const TcExtra ex) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle pattern is a function of the address: tiles start on 1024-byte boundaries
     unsigned char * smem = (unsigned char *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
@@ -249,12 +311,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
             }
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
+            float rs = 1.0f;
+            if (ex.in_partial != nullptr && row < T) {          // this row's factor: its partial sums in a fixed order
+                float a = 0.0f;
+                for (int i = 0; i < ex.in_tiles; i++) a += ex.in_partial[(size_t) row * ex.in_tiles + i];
+                rs = rsqrtf(a * ex.inv_width + ex.eps);
+            }
+            float sq = 0.0f;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned r[32];
                 tc_ld32(tmem_base + ((unsigned) (q * 32) << 16) + (unsigned) (buf * BN + c0), r);
                 tc_wait_ld();
-                if (row < T) epilogue_store32<EPI, OutT>(r, out, row, n0 + c0, N, ldo);
+                if (row < T) {
+                    if constexpr (EPI == EPI_RESNORM)
+                        sq += epilogue_resnorm32(r, reinterpret_cast<__nv_bfloat16 *>(out), ex.res, ex.norm_w, row, n0 + c0, N, rs);
+                    else
+                        epilogue_store32<EPI, OutT>(r, out, row, n0 + c0, N, ldo, rs);
+                }
+            }
+            if constexpr (EPI == EPI_RESNORM) {
+                if (row < T) ex.out_partial[(size_t) row * n_tiles + tile / m_tiles] = sq;
             }
             tc_fence_before();
             __syncwarp();
@@ -302,7 +379,7 @@ static int make_map(CUtensorMap * map, const void * base, int rows, int K, int b
 
 template <int BN, int STAGES, int EPI, typename OutT>
 static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out, int T, int N, int K, int ldo, TcStatus * status,
-                     cudaStream_t stream) {
+                     const TcExtra & ex, cudaStream_t stream) {
     constexpr size_t smem = (size_t) STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -317,7 +394,7 @@ static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out,
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     dim3 grid(tiles < sms ? tiles : sms);
-    gemm_tcgen05_kernel<BN, STAGES, EPI, OutT><<<grid, TC_THREADS, smem, stream>>>(ma, mb, (OutT *) out, T, N, K, ldo, status);
+    gemm_tcgen05_kernel<BN, STAGES, EPI, OutT><<<grid, TC_THREADS, smem, stream>>>(ma, mb, (OutT *) out, T, N, K, ldo, status, ex);
     return iian_launch_status();
 }
 
@@ -325,18 +402,15 @@ static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out,
 
 using namespace iian;
 
-// x: [T, K] bf16, w: [N, K] bf16; out: [T, N] (epilogue 0) or [T, N / 2] (epilogue 1: SiLU(gate) * up over
-// rows interleaved in groups of 8), bf16 or f32.  K must be a multiple of 8 (16-byte rows for TMA), x and w
-// 16-byte aligned.  status: two ints on the device, zero before the launch; non-zero afterwards means a
-// wait gave up (code 1 producer, 2 MMA, 3 epilogue) and the output is not valid.
-IIAN_API int iian_gemm_tcgen05(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
-                               int bn, int * status, cudaStream_t stream) {
+static int tc_entry(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
+                    int bn, int * status, const TcExtra & ex, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return IIAN_OK;
     if (K <= 0 || K % 8 != 0) return IIAN_ERR_SHAPE;
     if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU8 && N % 16 != 0) return IIAN_ERR_SHAPE;
     if (status == nullptr) return IIAN_ERR_SHAPE;
     if (bn != 128 && bn != 256) return IIAN_ERR_SHAPE;
+    if (ex.in_partial != nullptr && ex.in_tiles <= 0) return IIAN_ERR_SHAPE;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, x, T, K, TC_BM);
     if (rc != IIAN_OK) return rc;
@@ -344,16 +418,44 @@ IIAN_API int iian_gemm_tcgen05(const void * x, const void * w, void * out, int o
     if (rc != IIAN_OK) return rc;
     TcStatus * st = (TcStatus *) status;
     const int ldo = epilogue == EPI_SWIGLU8 ? N / 2 : N;
+    if (epilogue == EPI_RESNORM) {
+        if (out_dtype != IIAN_BF16 || ex.res == nullptr || ex.norm_w == nullptr || ex.out_partial == nullptr) return IIAN_ERR_SHAPE;
+        if (bn == 256) return launch_tc<256, 4, EPI_RESNORM, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+        return launch_tc<128, 6, EPI_RESNORM, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+    }
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU8) return IIAN_ERR_SHAPE;
     if (out_dtype == IIAN_BF16) {
-        if (bn == 256) return epilogue == EPI_STORE ? launch_tc<256, 4, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream)
-                                                    : launch_tc<256, 4, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream);
-        return epilogue == EPI_STORE ? launch_tc<128, 6, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream)
-                                     : launch_tc<128, 6, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, stream);
+        if (bn == 256) return epilogue == EPI_STORE ? launch_tc<256, 4, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream)
+                                                    : launch_tc<256, 4, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+        return epilogue == EPI_STORE ? launch_tc<128, 6, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream)
+                                     : launch_tc<128, 6, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
     }
     if (out_dtype == IIAN_F32) {
         if (epilogue != EPI_STORE) return IIAN_ERR_DTYPE;
-        if (bn == 256) return launch_tc<256, 4, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, stream);
-        return launch_tc<128, 6, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, stream);
+        if (bn == 256) return launch_tc<256, 4, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+        return launch_tc<128, 6, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, ex, stream);
     }
     return IIAN_ERR_DTYPE;
+}
+
+// x: [T, K] bf16, w: [N, K] bf16; out: [T, N] (epilogue 0) or [T, N / 2] (epilogue 1: SiLU(gate) * up over
+// rows interleaved in groups of 8), bf16 or f32.  K must be a multiple of 8 (16-byte rows for TMA), x and w
+// 16-byte aligned.  status: two ints on the device, zero before the launch; non-zero afterwards means a
+// wait gave up (code 1 producer, 2 MMA, 3 epilogue) and the output is not valid.
+IIAN_API int iian_gemm_tcgen05(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
+                               int bn, int * status, cudaStream_t stream) {
+    if (epilogue == EPI_RESNORM) return IIAN_ERR_SHAPE;
+    const TcExtra none = {nullptr, 0, 0.0f, 0.0f, nullptr, nullptr, nullptr};
+    return tc_entry(x, w, out, out_dtype, T, N, K, epilogue, bn, status, none, stream);
+}
+
+// The product with its fused forms.  in_partial [T, in_tiles] (or null): the rows' sums of squares in parts; the
+// result's row t is multiplied by rsqrt(sum / width + eps) with inv_width = 1 / width.  epilogue 2: out = bf16(res *
+// norm_w) after res [T, N] float32 += bf16(product), and out_partial [T, ceil(N / bn)] receives the sums of squares
+// of res per tile of bn columns.
+IIAN_API int iian_gemm_tcgen05_fused(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
+                                     int bn, int * status, const float * in_partial, int in_tiles, float inv_width, float eps,
+                                     float * res, const float * norm_w, float * out_partial, cudaStream_t stream) {
+    const TcExtra ex = {in_partial, in_tiles, inv_width, eps, res, norm_w, out_partial};
+    return tc_entry(x, w, out, out_dtype, T, N, K, epilogue, bn, status, ex, stream);
 }

@@ -173,7 +173,10 @@ class CudaKernels:
         if n == 0:
             return
         if row_scale is not None or residual_norm is not None:
-            self.gemm_skinny_fused(x, w, out, 2 if residual_norm is not None else 0, row_scale, residual_norm)
+            if self._tcgen05_ok(x, w, n, k):
+                self.gemm_tcgen05(x, w, out, row_scale=row_scale, residual_norm=residual_norm)
+            else:
+                self.gemm_skinny_fused(x, w, out, 2 if residual_norm is not None else 0, row_scale, residual_norm)
             return
         self._linear_dispatch(x, w, out, n, m, k)
 
@@ -183,10 +186,22 @@ class CudaKernels:
         """Whether the product of ``x`` with ``w`` can carry a RowScale or a ResidualNorm (the weight-streaming
         kernel's range: up to 8 rows of bfloat16)."""
         n, k = x.shape
-        return self.FUSE_NORM and self._skinny_ok(x, w, n, k)
+        return self.FUSE_NORM and (self._skinny_ok(x, w, n, k) or self._tcgen05_ok(x, w, n, k))
 
-    def norm_parts(self, w: torch.Tensor) -> int:
-        """Parts in which a ResidualNorm product with weight ``w`` leaves the sums of squares."""
+    def can_take_prenormed(self, n_rows: int, w: torch.Tensor, dtype: torch.dtype) -> bool:
+        """Whether a product of ``n_rows`` rows with ``w`` can carry a RowScale: the row counts of the weight-streaming
+        kernel and of the tcgen05 kernel (the library product between them cannot)."""
+        if not self.FUSE_NORM or dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.data_ptr() % 16:
+            return False
+        k = w.shape[1]
+        if n_rows <= self.SKINNY_MAX_ROWS:
+            return k % 32 == 0
+        return n_rows >= self.TCGEN05_MIN_ROWS and k % 8 == 0 and not self.LIBRARY_GEMM_ONLY
+
+    def norm_parts(self, w: torch.Tensor, n_rows: int = 1) -> int:
+        """Parts in which a ResidualNorm product of ``n_rows`` rows with weight ``w`` leaves the sums of squares."""
+        if n_rows >= self.TCGEN05_MIN_ROWS:
+            return -(-w.shape[0] // self.tcgen05_tile_columns(w.shape[0]))
         return -(-w.shape[0] // 16)
 
     def gemm_skinny_fused(self, x, w, out, epilogue: int, row_scale=None, residual_norm=None) -> None:
@@ -250,7 +265,10 @@ class CudaKernels:
         """out[t, f] = silu(x . w_gate_f) * (x . w_up_f) for w with gate and up rows interleaved in groups of 8."""
         n, k = x.shape
         if row_scale is not None:
-            self.gemm_skinny_fused(x, w, out, 1, row_scale, None)
+            if self._tcgen05_ok(x, w, n, k):
+                self.gemm_tcgen05(x, w, out, epilogue=1, row_scale=row_scale)
+            else:
+                self.gemm_skinny_fused(x, w, out, 1, row_scale, None)
             return
         if self._tcgen05_ok(x, w, n, k):
             self.gemm_tcgen05(x, w, out, epilogue=1)
@@ -366,9 +384,16 @@ class CudaKernels:
             t.zero_()
             raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (wait {code}, iteration {where}); its result is not valid")
 
-    def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, bn: int = 0) -> None:
+    @staticmethod
+    def tcgen05_tile_columns(n: int) -> int:
+        """Columns of an output tile of the tcgen05 product for a weight with ``n`` rows."""
+        return 256 if n % 256 == 0 or n > 4096 else 128
+
+    def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, bn: int = 0,
+                     row_scale=None, residual_norm=None) -> None:
         """``epilogue`` 0: out[t, n] = x . w; 1: w holds gate and up rows interleaved in groups of 8 and
-        out[t, f] = silu(gate_f) * up_f with half as many columns."""
+        out[t, f] = silu(gate_f) * up_f with half as many columns; 2 (with ``residual_norm``): the residual add and
+        the next norm's weight ride in the epilogue.  ``row_scale``: rows are multiplied by a folded norm's factor."""
         t_rows, k = x.shape
         n = w.shape[0]
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -377,11 +402,35 @@ class CudaKernels:
         if w.shape[1] != k or out.shape != (t_rows, want_cols):
             raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
         if bn == 0:
-            bn = 256 if n % 256 == 0 or n > 4096 else 128
-        fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05",
-                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+            bn = self.tcgen05_tile_columns(n)
+        status = self.tcgen05_status_buffer(x.device).data_ptr()
+        if row_scale is None and residual_norm is None:
+            fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05",
+                     [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+            _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
+                      t_rows, n, k, epilogue, bn, status, _stream()), "gemm_tcgen05")
+            return
+        in_p = in_tiles = 0
+        inv_w = eps = 0.0
+        if row_scale is not None:
+            if row_scale.partials.dtype != torch.float32 or row_scale.partials.shape[0] != t_rows:
+                raise KernelError("linear: RowScale partials must be float32 [rows, parts]")
+            in_p, in_tiles = _cuda(row_scale.partials, "row-scale partials"), row_scale.partials.shape[1]
+            inv_w, eps = 1.0 / row_scale.width, row_scale.eps
+        res = nw = out_p = 0
+        if residual_norm is not None:
+            rn = residual_norm
+            if (rn.residual.shape != (t_rows, n) or rn.residual.dtype != torch.float32 or rn.weight.numel() != n
+                    or rn.partials.shape != (t_rows, -(-n // bn)) or out.dtype != torch.bfloat16):
+                raise KernelError("linear: ResidualNorm operands do not fit the product")
+            res, nw = _cuda(rn.residual, "residual", torch.float32), _cuda(rn.weight, "norm weight", torch.float32)
+            out_p = _cuda(rn.partials, "norm partials", torch.float32)
+            epilogue = 2
+        fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05_fused",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                  c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p])
         _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
-                  t_rows, n, k, epilogue, bn, self.tcgen05_status_buffer(x.device).data_ptr(), _stream()), "gemm_tcgen05")
+                  t_rows, n, k, epilogue, bn, status, in_p, in_tiles, inv_w, eps, res, nw, out_p, _stream()), "gemm_tcgen05")
 
     def prefetch_l2(self, ptr: int, nbytes: int) -> None:
         fn = _fn("prefetch", "iian_prefetch_l2", [c_void_p, c_longlong, c_void_p])

@@ -92,8 +92,7 @@ class Attention(Mixer):
 
     def takes_prenormed(self, n_rows: int) -> bool:
         k = ops.kernels()
-        return (getattr(k, "FUSE_NORM", False) and n_rows <= getattr(k, "SKINNY_MAX_ROWS", 0) and self.hidden % 32 == 0
-                and self.dtype == torch.bfloat16 and self.w_qkv.dtype == torch.bfloat16)
+        return hasattr(k, "can_take_prenormed") and k.can_take_prenormed(n_rows, self.w_qkv, self.dtype)
 
     def _project_out(self, k, attn: torch.Tensor, ctx, norm_out):
         if (norm_out is not None and self.b_o is None and hasattr(k, "can_fuse_norm")

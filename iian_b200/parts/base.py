@@ -112,7 +112,7 @@ class NormOut:
         from ..ops.fused import ResidualNorm, RowScale
         n, width = x.shape[0], w.shape[0]
         out = ctx.buf(f"prenormed_{self.name}", (n, width), x.dtype)
-        partials = ctx.buf(f"norm_partials_{self.name}", (n, k.norm_parts(w)), torch.float32)
+        partials = ctx.buf(f"norm_partials_{self.name}", (n, k.norm_parts(w, n)), torch.float32)
         k.linear(x, w, out, residual_norm=ResidualNorm(self.residual, self.weight, partials))
         return Prenormed(out, RowScale(partials, width, self.eps), self.norm)
 

@@ -60,9 +60,8 @@ class GatedMLP(FeedForward):
 
     def takes_prenormed(self, n_rows: int) -> bool:
         k = ops.kernels()
-        if not getattr(k, "FUSE_NORM", False) or self.interleave != 8 or self.w_gate_up.dtype != self.dtype:
-            return False
-        return n_rows <= getattr(k, "SKINNY_MAX_ROWS", 0) and self.hidden % 32 == 0 and self.dtype == torch.bfloat16
+        return (hasattr(k, "can_take_prenormed") and self.interleave == 8
+                and k.can_take_prenormed(n_rows, self.w_gate_up, self.dtype))
 
     def forward(self, x, ctx, norm_out=None):
         k = ops.kernels()

@@ -360,7 +360,8 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch():
         assert torch.equal(one[0], full[r])
 
 
-@pytest.mark.parametrize("B,H,M2,K_", [(1, 64, 48, 96), (8, 4096, 6144, 4096), (5, 288, 100, 160), (3, 1024, 32, 2048)])
+@pytest.mark.parametrize("B,H,M2,K_", [(1, 64, 48, 96), (8, 4096, 6144, 4096), (5, 288, 100, 160), (3, 1024, 32, 2048),
+                                       (200, 288, 100, 160), (300, 1024, 520, 1096), (129, 4360, 264, 64)])
 def test_gemm_skinny_folded_norm(B, H, M2, K_):
     """A product that ends a sub-layer adds to the residual, prepares residual * norm weight and leaves the sums
     of squares in parts; the next product multiplies its rows by rsqrt(mean + eps).  Together they equal the
@@ -376,7 +377,7 @@ def test_gemm_skinny_folded_norm(B, H, M2, K_):
     # folded route
     res = res0.clone()
     xt = torch.full((B, H), float("nan"), dtype=torch.bfloat16).cuda()
-    partials = torch.full((B, k.norm_parts(w1)), float("nan")).cuda()
+    partials = torch.full((B, k.norm_parts(w1, B)), float("nan")).cuda()
     k.linear(a, w1, xt, residual_norm=ResidualNorm(res, nw, partials))
     out = torch.full((B, M2), float("nan"), dtype=torch.bfloat16).cuda()
     k.linear(xt, w2, out, row_scale=RowScale(partials, H, eps))
@@ -402,10 +403,10 @@ def test_gemm_skinny_folded_norm(B, H, M2, K_):
     assert (out.float() - out_b.float()).abs().max() < 2 * tol(torch.bfloat16, max(1.0, want.abs().max().item()))
 
 
-def test_gemm_skinny_row_scale_with_swiglu():
+@pytest.mark.parametrize("B,H,F", [(6, 512, 160), (150, 520, 168), (260, 1024, 2304)])
+def test_gemm_skinny_row_scale_with_swiglu(B, H, F):
     from iian_b200.ops.fused import RowScale
     k = K()
-    B, H, F = 6, 512, 160
     x = rnd(B, H, dtype=torch.bfloat16, seed=60)
     wg, wu = rnd(F, H, dtype=torch.bfloat16, seed=61, std=0.05), rnd(F, H, dtype=torch.bfloat16, seed=62, std=0.05)
     inter = torch.stack([wg.view(F // 8, 8, H), wu.view(F // 8, 8, H)], dim=1).reshape(2 * F, H).contiguous()
