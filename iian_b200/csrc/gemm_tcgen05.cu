@@ -348,6 +348,178 @@ done:
     }
 }
 
+// ---- the same product on pairs of SMs ---------------------------------------------------------------
+// A cluster of two CTAs owns a tile of 256 rows x BN columns: CTA r of the pair holds rows 128 r .. 128 r + 127 of
+// the activations and columns BN / 2 * r .. of the weights in its shared memory, and its 128 rows of the
+// accumulator in its tensor memory.  One thread of CTA 0 issues tcgen05.mma.cta_group::2 (M = 256), which reads
+// both CTAs' shared memory and writes both tensor memories; each SM therefore fills 32 KB of shared memory per K
+// block instead of 48 KB, which leaves room for six stages and lowers the traffic (and the power) per flop.
+// Both CTAs' TMA loads complete on CTA 0's `full` barrier; tcgen05.commit with a CTA mask arrives on the `empty`
+// and `accumulator full` barriers of both; the epilogue warps of both arrive on CTA 0's `accumulator empty`.
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned map_to_cta(unsigned addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// no multicast: the tile lands in this CTA's shared memory; only the completion goes to the barrier of CTA 0
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap * map, int x, int y, unsigned bar_cluster) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(unsigned bar) {      // arrives on the barrier at this offset in both CTAs
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short) 3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc,
+                                            unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_pair_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+    OutT * __restrict__ out, int T, int N, int K, int ldo, TcStatus * status, const TcExtra ex) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char * smem = (unsigned char *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    constexpr int HALF = BN / 2;
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = HALF * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr unsigned TMEM_COLS = 2 * BN;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    __shared__ unsigned tmem_base_s;
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_cta_rank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (T + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (N + BN - 1) / BN;
+    const int num_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_addr(&full_bar[s]), 1); mbar_init(smem_addr(&empty_bar[s]), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(smem_addr(&acc_full[b]), 1); mbar_init(smem_addr(&acc_empty[b]), 8); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {          // the same warp of both CTAs allocates: the two tensor memories get the same columns
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();       // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const unsigned tmem_base = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer (both CTAs): its half of the pair's operands, completion on CTA 0's barrier ----------
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+            const int m0 = (tile % m_tiles) * (2 * TC_BM) + (int) rank * TC_BM, n0 = (tile / m_tiles) * BN + (int) rank * HALF;
+            for (int kb = 0; kb < num_kb; kb++, it++) {
+                const int s = it % STAGES;
+                const unsigned phase = (it / STAGES) & 1;
+                if (!mbar_wait(smem_addr(&empty_bar[s]), phase ^ 1)) { status->code = 1; status->where = it; failed = 1; goto done; }
+                const unsigned bar = map_to_cta(smem_addr(&full_bar[s]), 0);
+                if (rank == 0) mbar_expect_tx(smem_addr(&full_bar[s]), 2 * STAGE_BYTES);
+                tma_load_2d_pair(smem_addr(smem + s * STAGE_BYTES), &map_a, kb * TC_BK, m0, bar);
+                tma_load_2d_pair(smem_addr(smem + s * STAGE_BYTES + A_BYTES), &map_b, kb * TC_BK, n0, bar);
+            }
+        }
+        // the last commits still arrive on this CTA's barriers: take them before the CTA may leave
+        for (int i = 0; i < STAGES; i++, it++)
+            if (!mbar_wait(smem_addr(&empty_bar[it % STAGES]), ((it / STAGES) & 1) ^ 1)) { status->code = 5; status->where = it; failed = 1; break; }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- MMA issuer (CTA 0 only) -------------------------------------------------------------------
+        constexpr unsigned idesc = instr_desc_bf16(2 * TC_BM, BN);
+        int it = 0, use = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, use++) {
+            const int buf = use & 1;
+            const unsigned acc_phase = (use >> 1) & 1;
+            if (!mbar_wait(smem_addr(&acc_empty[buf]), acc_phase ^ 1)) { status->code = 4; status->where = use; failed = 1; goto done; }
+            tc_fence_after();
+            const unsigned d_tmem = tmem_base + (unsigned) (buf * BN);
+            for (int kb = 0; kb < num_kb; kb++, it++) {
+                const int s = it % STAGES;
+                const unsigned phase = (it / STAGES) & 1;
+                if (!mbar_wait(smem_addr(&full_bar[s]), phase)) { status->code = 2; status->where = it; failed = 1; goto done; }
+                tc_fence_after();
+                const unsigned long long da = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES));
+                const unsigned long long db = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + A_BYTES));
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++)
+                    tc_mma_pair(d_tmem, da + (unsigned long long) (k * 2), db + (unsigned long long) (k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tc_commit_pair(smem_addr(&empty_bar[s]));
+            }
+            tc_commit_pair(smem_addr(&acc_full[buf]));
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue (both CTAs): this CTA's 128 rows of the pair's tile ----------------------------------
+        const int q = warp & 3;
+        int use = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, use++) {
+            const int buf = use & 1;
+            const unsigned acc_phase = (use >> 1) & 1;
+            const int m0 = (tile % m_tiles) * (2 * TC_BM) + (int) rank * TC_BM, n0 = (tile / m_tiles) * BN;
+            if (!mbar_wait(smem_addr(&acc_full[buf]), acc_phase)) {
+                if (lane == 0) { status->code = 3; status->where = use; }
+                failed = 1;
+                break;
+            }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            float rs = 1.0f;
+            if (ex.in_partial != nullptr && row < T) {
+                float a = 0.0f;
+                for (int i = 0; i < ex.in_tiles; i++) a += ex.in_partial[(size_t) row * ex.in_tiles + i];
+                rs = rsqrtf(a * ex.inv_width + ex.eps);
+            }
+            float sq = 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                unsigned r[32];
+                tc_ld32(tmem_base + ((unsigned) (q * 32) << 16) + (unsigned) (buf * BN + c0), r);
+                tc_wait_ld();
+                if (row < T) {
+                    if constexpr (EPI == EPI_RESNORM)
+                        sq += epilogue_resnorm32(r, reinterpret_cast<__nv_bfloat16 *>(out), ex.res, ex.norm_w, row, n0 + c0, N, rs);
+                    else
+                        epilogue_store32<EPI, OutT>(r, out, row, n0 + c0, N, ldo, rs);
+                }
+            }
+            if constexpr (EPI == EPI_RESNORM) {
+                if (row < T) ex.out_partial[(size_t) row * n_tiles + tile / m_tiles] = sq;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_addr(&acc_empty[buf]), 0));     // eight arrivals free the accumulator
+        }
+    }
+done:
+    // ---- common exit: both CTAs arrive here, also after a wait that gave up; neither frees tensor memory or
+    // leaves while the other may still read its shared memory or write its tensor memory
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -398,10 +570,43 @@ static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out,
     return iian_launch_status();
 }
 
+template <int BN, int STAGES, int EPI, typename OutT>
+static int launch_tc_pair(const CUtensorMap & ma, const CUtensorMap & mb, void * out, int T, int N, int K, int ldo, TcStatus * status,
+                          const TcExtra & ex, cudaStream_t stream) {
+    constexpr size_t smem = (size_t) STAGES * (TC_BM * TC_BK * 2 + (BN / 2) * TC_BK * 2) + 1024;
+    auto kernel = gemm_tcgen05_pair_kernel<BN, STAGES, EPI, OutT>;
+    static int pairs = 0;
+    if (pairs == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        if (e != cudaSuccess) return 1000 + (int) e;
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) (sms & ~1));
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }
+        pairs = n < sms / 2 ? n : sms / 2;
+    }
+    const int tiles = ((T + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + BN - 1) / BN);
+    dim3 grid((unsigned) (2 * (tiles < pairs ? tiles : pairs)));
+    kernel<<<grid, TC_THREADS, smem, stream>>>(ma, mb, (OutT *) out, T, N, K, ldo, status, ex);
+    return iian_launch_status();
+}
+
 }  // namespace iian
 
 using namespace iian;
 
+// bn: 128 or 256 columns per tile on one SM; 512: tiles of 256 x 256 on pairs of SMs
 static int tc_entry(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
                     int bn, int * status, const TcExtra & ex, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return IIAN_OK;
@@ -409,15 +614,29 @@ static int tc_entry(const void * x, const void * w, void * out, int out_dtype, i
     if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
     if (epilogue == EPI_SWIGLU8 && N % 16 != 0) return IIAN_ERR_SHAPE;
     if (status == nullptr) return IIAN_ERR_SHAPE;
-    if (bn != 128 && bn != 256) return IIAN_ERR_SHAPE;
+    if (bn != 128 && bn != 256 && bn != 512) return IIAN_ERR_SHAPE;
     if (ex.in_partial != nullptr && ex.in_tiles <= 0) return IIAN_ERR_SHAPE;
+    const bool pair = bn == 512;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, x, T, K, TC_BM);
     if (rc != IIAN_OK) return rc;
-    rc = make_map(&mb, w, N, K, bn);
+    rc = make_map(&mb, w, N, K, pair ? 128 : bn);
     if (rc != IIAN_OK) return rc;
     TcStatus * st = (TcStatus *) status;
     const int ldo = epilogue == EPI_SWIGLU8 ? N / 2 : N;
+    if (pair) {
+        if (epilogue == EPI_RESNORM) {
+            if (out_dtype != IIAN_BF16 || ex.res == nullptr || ex.norm_w == nullptr || ex.out_partial == nullptr) return IIAN_ERR_SHAPE;
+            return launch_tc_pair<256, 6, EPI_RESNORM, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+        }
+        if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU8) return IIAN_ERR_SHAPE;
+        if (out_dtype == IIAN_BF16)
+            return epilogue == EPI_STORE ? launch_tc_pair<256, 6, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream)
+                                         : launch_tc_pair<256, 6, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+        if (out_dtype == IIAN_F32 && epilogue == EPI_STORE)
+            return launch_tc_pair<256, 6, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+        return IIAN_ERR_DTYPE;
+    }
     if (epilogue == EPI_RESNORM) {
         if (out_dtype != IIAN_BF16 || ex.res == nullptr || ex.norm_w == nullptr || ex.out_partial == nullptr) return IIAN_ERR_SHAPE;
         if (bn == 256) return launch_tc<256, 4, EPI_RESNORM, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
@@ -441,7 +660,8 @@ static int tc_entry(const void * x, const void * w, void * out, int out_dtype, i
 // x: [T, K] bf16, w: [N, K] bf16; out: [T, N] (epilogue 0) or [T, N / 2] (epilogue 1: SiLU(gate) * up over
 // rows interleaved in groups of 8), bf16 or f32.  K must be a multiple of 8 (16-byte rows for TMA), x and w
 // 16-byte aligned.  status: two ints on the device, zero before the launch; non-zero afterwards means a
-// wait gave up (code 1 producer, 2 MMA, 3 epilogue) and the output is not valid.
+// wait gave up (code 1 producer, 2 and 4 MMA, 3 epilogue, 5 producer's tail) and the output is not valid.  bn: columns
+// of a tile, 128 or 256; 512 runs tiles of 256 x 256 on pairs of SMs (tcgen05 cta_group::2).
 IIAN_API int iian_gemm_tcgen05(const void * x, const void * w, void * out, int out_dtype, int T, int N, int K, int epilogue,
                                int bn, int * status, cudaStream_t stream) {
     if (epilogue == EPI_RESNORM) return IIAN_ERR_SHAPE;

@@ -201,7 +201,7 @@ class CudaKernels:
     def norm_parts(self, w: torch.Tensor, n_rows: int = 1) -> int:
         """Parts in which a ResidualNorm product of ``n_rows`` rows with weight ``w`` leaves the sums of squares."""
         if n_rows >= self.TCGEN05_MIN_ROWS:
-            return -(-w.shape[0] // self.tcgen05_tile_columns(w.shape[0]))
+            return -(-w.shape[0] // self.tcgen05_tile_columns(n_rows, w.shape[0]))
         return -(-w.shape[0] // 16)
 
     def gemm_skinny_fused(self, x, w, out, epilogue: int, row_scale=None, residual_norm=None) -> None:
@@ -384,10 +384,20 @@ class CudaKernels:
             t.zero_()
             raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (wait {code}, iteration {where}); its result is not valid")
 
-    @staticmethod
-    def tcgen05_tile_columns(n: int) -> int:
-        """Columns of an output tile of the tcgen05 product for a weight with ``n`` rows."""
-        return 256 if n % 256 == 0 or n > 4096 else 128
+    TCGEN05_PAIR = os.environ.get("IIAN_TCGEN05_PAIR", "1") not in ("0", "false", "off")
+
+    @classmethod
+    def tcgen05_tile(cls, n_rows: int, n: int) -> int:
+        """The tile of the tcgen05 product for ``n_rows`` rows and a weight with ``n`` rows: 128 or 256 columns on one
+        SM, or 512: tiles of 256 x 256 on pairs of SMs (from two row tiles on)."""
+        wide = n % 256 == 0 or n > 4096
+        if wide and cls.TCGEN05_PAIR and n_rows > 128:
+            return 512
+        return 256 if wide else 128
+
+    @classmethod
+    def tcgen05_tile_columns(cls, n_rows: int, n: int) -> int:
+        return min(256, cls.tcgen05_tile(n_rows, n))
 
     def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, bn: int = 0,
                      row_scale=None, residual_norm=None) -> None:
@@ -402,7 +412,7 @@ class CudaKernels:
         if w.shape[1] != k or out.shape != (t_rows, want_cols):
             raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
         if bn == 0:
-            bn = self.tcgen05_tile_columns(n)
+            bn = self.tcgen05_tile(t_rows, n)
         status = self.tcgen05_status_buffer(x.device).data_ptr()
         if row_scale is None and residual_norm is None:
             fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05",
@@ -421,7 +431,7 @@ class CudaKernels:
         if residual_norm is not None:
             rn = residual_norm
             if (rn.residual.shape != (t_rows, n) or rn.residual.dtype != torch.float32 or rn.weight.numel() != n
-                    or rn.partials.shape != (t_rows, -(-n // bn)) or out.dtype != torch.bfloat16):
+                    or rn.partials.shape != (t_rows, -(-n // min(bn, 256))) or out.dtype != torch.bfloat16):
                 raise KernelError("linear: ResidualNorm operands do not fit the product")
             res, nw = _cuda(rn.residual, "residual", torch.float32), _cuda(rn.weight, "norm weight", torch.float32)
             out_p = _cuda(rn.partials, "norm partials", torch.float32)

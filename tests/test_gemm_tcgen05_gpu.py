@@ -1,5 +1,5 @@
 """The tcgen05 + TMA matrix product against a float64 reference: tails in every dimension, both tile
-widths, float32 output, and the fused SiLU(gate) * up epilogue over rows interleaved in groups of 8."""
+widths and the tiles on pairs of SMs, float32 output, and the fused SiLU(gate) * up epilogue over rows interleaved in groups of 8."""
 import pytest
 import torch
 
@@ -23,7 +23,7 @@ SHAPES = [(128, 256, 64), (128, 256, 256), (1, 128, 64), (200, 384, 512), (130, 
 
 
 @pytest.mark.parametrize("T,N,Kd", SHAPES)
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 def test_gemm_tcgen05_store(T, N, Kd, bn):
     k = K()
     x, w = rnd(T, Kd, seed=1), rnd(N, Kd, seed=2, std=0.05)
@@ -35,24 +35,26 @@ def test_gemm_tcgen05_store(T, N, Kd, bn):
     assert err < 1.6e-2 * max(1.0, want.abs().max().item()), err
 
 
-def test_gemm_tcgen05_float32_out():
+@pytest.mark.parametrize("bn", [128, 512])
+def test_gemm_tcgen05_float32_out(bn):
     k = K()
     x, w = rnd(77, 512, seed=3), rnd(503, 512, seed=4, std=0.05)
     out = torch.full((77, 503), float("nan"), dtype=torch.float32, device="cuda")
-    k.gemm_tcgen05(x, w, out, bn=128)
+    k.gemm_tcgen05(x, w, out, bn=bn)
     k.tcgen05_check(x.device)
     want = x.double().cpu() @ w.double().cpu().T
     assert (out.double().cpu() - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("bn", [0, 512])
 @pytest.mark.parametrize("T,F,Kd", [(128, 128, 64), (300, 160, 256), (2048, 12288, 4096)])
-def test_gemm_tcgen05_swiglu_epilogue(T, F, Kd):
+def test_gemm_tcgen05_swiglu_epilogue(T, F, Kd, bn):
     k = K()
     x = rnd(T, Kd, seed=5)
     wg, wu = rnd(F, Kd, seed=6, std=0.05), rnd(F, Kd, seed=7, std=0.05)
     inter = torch.stack([wg.view(F // 8, 8, Kd), wu.view(F // 8, 8, Kd)], dim=1).reshape(2 * F, Kd).contiguous()
     out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device="cuda")
-    k.gemm_tcgen05(x, inter, out, epilogue=1)
+    k.gemm_tcgen05(x, inter, out, epilogue=1, bn=bn)
     k.tcgen05_check(x.device)
     xd = x.double().cpu()
     want = plain.silu(xd @ wg.double().cpu().T) * (xd @ wu.double().cpu().T)
