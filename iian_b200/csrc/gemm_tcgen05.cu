@@ -387,14 +387,14 @@ __device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long 
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-template <int BN, int STAGES, int EPI, typename OutT>
+template <int BN, int STAGES, int KPS, int EPI, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_pair_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
     OutT * __restrict__ out, int T, int N, int K, int ldo, TcStatus * status, const TcExtra ex) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char * smem = (unsigned char *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
     constexpr int HALF = BN / 2;
-    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = HALF * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = HALF * TC_BK * 2, KB_BYTES = A_BYTES + B_BYTES, STAGE_BYTES = KPS * KB_BYTES;
     constexpr unsigned TMEM_COLS = 2 * BN;
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_base_s;
@@ -403,7 +403,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) gemm_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_cta_rank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    // a stage holds KPS blocks of 64 along K and is handed over with one barrier phase and one commit: the tensor
+    // pipe idles for a fixed time at every hand-over, so longer stages keep it busier.  Blocks past the end of K
+    // are filled with zeros by TMA.
+    const int num_kb = ((K + TC_BK - 1) / TC_BK + KPS - 1) / KPS;
     const int m_tiles = (T + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (N + BN - 1) / BN;
     const int num_tiles = m_tiles * n_tiles;
 
@@ -434,8 +437,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) gemm_
                 if (!mbar_wait(smem_addr(&empty_bar[s]), phase ^ 1)) { status->code = 1; status->where = it; failed = 1; goto done; }
                 const unsigned bar = map_to_cta(smem_addr(&full_bar[s]), 0);
                 if (rank == 0) mbar_expect_tx(smem_addr(&full_bar[s]), 2 * STAGE_BYTES);
-                tma_load_2d_pair(smem_addr(smem + s * STAGE_BYTES), &map_a, kb * TC_BK, m0, bar);
-                tma_load_2d_pair(smem_addr(smem + s * STAGE_BYTES + A_BYTES), &map_b, kb * TC_BK, n0, bar);
+#pragma unroll
+                for (int j = 0; j < KPS; j++) {
+                    tma_load_2d_pair(smem_addr(smem + s * STAGE_BYTES + j * KB_BYTES), &map_a, (kb * KPS + j) * TC_BK, m0, bar);
+                    tma_load_2d_pair(smem_addr(smem + s * STAGE_BYTES + j * KB_BYTES + A_BYTES), &map_b, (kb * KPS + j) * TC_BK, n0, bar);
+                }
             }
         }
         // the last commits still arrive on this CTA's barriers: take them before the CTA may leave
@@ -456,11 +462,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) gemm_
                 const unsigned phase = (it / STAGES) & 1;
                 if (!mbar_wait(smem_addr(&full_bar[s]), phase)) { status->code = 2; status->where = it; failed = 1; goto done; }
                 tc_fence_after();
-                const unsigned long long da = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES));
-                const unsigned long long db = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + A_BYTES));
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++)
-                    tc_mma_pair(d_tmem, da + (unsigned long long) (k * 2), db + (unsigned long long) (k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                for (int j = 0; j < KPS; j++) {
+                    const unsigned long long da = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + j * KB_BYTES));
+                    const unsigned long long db = smem_desc_sw128(smem_addr(smem + s * STAGE_BYTES + j * KB_BYTES + A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; k++)
+                        tc_mma_pair(d_tmem, da + (unsigned long long) (k * 2), db + (unsigned long long) (k * 2), idesc, (kb > 0 || j > 0 || k > 0) ? 1u : 0u);
+                }
                 tc_commit_pair(smem_addr(&empty_bar[s]));
             }
             tc_commit_pair(smem_addr(&acc_full[buf]));
@@ -570,11 +579,11 @@ static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out,
     return iian_launch_status();
 }
 
-template <int BN, int STAGES, int EPI, typename OutT>
+template <int BN, int STAGES, int KPS, int EPI, typename OutT>
 static int launch_tc_pair(const CUtensorMap & ma, const CUtensorMap & mb, void * out, int T, int N, int K, int ldo, TcStatus * status,
                           const TcExtra & ex, cudaStream_t stream) {
-    constexpr size_t smem = (size_t) STAGES * (TC_BM * TC_BK * 2 + (BN / 2) * TC_BK * 2) + 1024;
-    auto kernel = gemm_tcgen05_pair_kernel<BN, STAGES, EPI, OutT>;
+    constexpr size_t smem = (size_t) STAGES * KPS * (TC_BM * TC_BK * 2 + (BN / 2) * TC_BK * 2) + 1024;
+    auto kernel = gemm_tcgen05_pair_kernel<BN, STAGES, KPS, EPI, OutT>;
     static int pairs = 0;
     if (pairs == 0) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
@@ -627,14 +636,14 @@ static int tc_entry(const void * x, const void * w, void * out, int out_dtype, i
     if (pair) {
         if (epilogue == EPI_RESNORM) {
             if (out_dtype != IIAN_BF16 || ex.res == nullptr || ex.norm_w == nullptr || ex.out_partial == nullptr) return IIAN_ERR_SHAPE;
-            return launch_tc_pair<256, 6, EPI_RESNORM, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+            return launch_tc_pair<256, 3, 2, EPI_RESNORM, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
         }
         if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU8) return IIAN_ERR_SHAPE;
         if (out_dtype == IIAN_BF16)
-            return epilogue == EPI_STORE ? launch_tc_pair<256, 6, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream)
-                                         : launch_tc_pair<256, 6, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+            return epilogue == EPI_STORE ? launch_tc_pair<256, 3, 2, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream)
+                                         : launch_tc_pair<256, 3, 2, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream);
         if (out_dtype == IIAN_F32 && epilogue == EPI_STORE)
-            return launch_tc_pair<256, 6, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, ex, stream);
+            return launch_tc_pair<256, 3, 2, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, ex, stream);
         return IIAN_ERR_DTYPE;
     }
     if (epilogue == EPI_RESNORM) {
