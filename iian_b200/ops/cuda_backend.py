@@ -224,6 +224,8 @@ class CudaKernels:
                 raise KernelError("linear: ResidualNorm operands do not fit the product")
             res, nw = _cuda(rn.residual, "residual", torch.float32), _cuda(rn.weight, "norm weight", torch.float32)
             out_p = _cuda(rn.partials, "norm partials", torch.float32)
+        if self.prefetcher is not None:
+            self.prefetcher.before_product(self)
         fn = _fn("gemm_skinny", "iian_gemm_skinny_fused",
                  [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_float,
                   c_void_p, c_void_p, c_void_p, c_void_p])
@@ -273,6 +275,8 @@ class CudaKernels:
         if self._tcgen05_ok(x, w, n, k):
             self.gemm_tcgen05(x, w, out, epilogue=1)
             return
+        if self.prefetcher is not None:
+            self.prefetcher.before_product(self)
         self.gemm_skinny(x, w, out, epilogue=1)
         if self.weight_log is not None:
             self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
@@ -285,6 +289,8 @@ class CudaKernels:
                 self.gemm_tcgen05(x, w, out)
                 return
             if n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+                if self.prefetcher is not None:
+                    self.prefetcher.before_product(self)
                 self.gemm_skinny(x, w, out)
                 if self.weight_log is not None:
                     self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
@@ -731,9 +737,12 @@ class WeightPrefetcher:
     """Keeps HBM busy between the weight-streaming products of a captured decode step.
 
     ``weights`` is the order in which the step's products read their weights (recorded on an eager
-    run).  After product ``i`` has been launched on the capturing stream, a side stream (forked with an
-    event, so it starts when product ``i`` completes) prefetches what comes next into L2: from the end of
-    what was prefetched so far up to ``window`` bytes beyond the start of product ``i + 1``'s weights.
+    run).  Before product ``i`` is launched on the capturing stream, a side stream is forked with an event
+    (so it runs beside product ``i``) and prefetches the head of product ``i + 1``'s weights into L2: from the
+    end of what was prefetched so far up to ``window`` bytes beyond their start.  Product ``i + 1`` then finds
+    its first rounds of loads in L2 and HBM does not idle while it starts up.  ``IIAN_PREFETCH_EARLY=0`` forks
+    after product ``i`` instead (the prefetch then runs beside whatever follows it, which only pays where an
+    attention kernel follows: 3.55 against 3.48 ms a step at batch 1, 3.72 against 3.67 ms at batch 8).
     The side stream is joined into the main stream before the capture ends.
 
     Measured on B200 at the Qwen3-8B sizes, batch 8: a window of 8 MB (the head of the next matrix, which
@@ -750,18 +759,27 @@ class WeightPrefetcher:
             pos += nbytes
         self.total = pos
         self.window = window
+        self.early = os.environ.get("IIAN_PREFETCH_EARLY", "1") not in ("0", "false", "off")
         self.side = torch.cuda.Stream()
         self.index = 0             # products launched so far
         self.cursor = 0            # bytes of the concatenated weight sequence already asked for
         self.launches = 0
 
+    def before_product(self, kernels) -> None:
+        if self.early:
+            self._prefetch_head(kernels, self.index + 1)
+
     def after_product(self, kernels) -> None:
-        i = self.index
         self.index += 1
-        if self.index >= len(self.weights):
+        if not self.early:
+            self._prefetch_head(kernels, self.index)
+
+    def _prefetch_head(self, kernels, j: int) -> None:
+        """Fork the side stream at this point of the main stream and ask for the head of product ``j``'s weights."""
+        if j >= len(self.weights):
             return
-        begin = max(self.cursor, self.starts[self.index])
-        end = min(self.total, self.starts[self.index] + self.window)
+        begin = max(self.cursor, self.starts[j])
+        end = min(self.total, self.starts[j] + self.window)
         if end <= begin:
             return
         main = torch.cuda.current_stream()
@@ -769,7 +787,6 @@ class WeightPrefetcher:
         ev.record(main)
         self.side.wait_event(ev)
         with torch.cuda.stream(self.side):
-            j = self.index
             while j < len(self.weights) and self.starts[j] < end:
                 ptr, nbytes = self.weights[j]
                 lo = max(begin, self.starts[j]) - self.starts[j]
