@@ -112,6 +112,30 @@ __device__ __forceinline__ void at_st32(unsigned taddr, const unsigned * r) {
 }
 __device__ __forceinline__ void at_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void at_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// packed pairs of float32 (one instruction for two values) and the maximum of three
+__device__ __forceinline__ unsigned long long at_pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void at_unpack2(unsigned long long v, float & a, float & b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long at_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long at_add2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 __device__ __forceinline__ float at_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -315,9 +339,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < AT_BN; j += 4) {
-                mx4[0] = fmaxf(mx4[0], __uint_as_float(v[j]));     mx4[1] = fmaxf(mx4[1], __uint_as_float(v[j + 1]));
-                mx4[2] = fmaxf(mx4[2], __uint_as_float(v[j + 2])); mx4[3] = fmaxf(mx4[3], __uint_as_float(v[j + 3]));
+            for (int j = 0; j < AT_BN; j += 8) {      // maxima of three: half the instructions
+                mx4[0] = at_max3(mx4[0], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                mx4[1] = at_max3(mx4[1], __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                mx4[2] = at_max3(mx4[2], __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                mx4[3] = at_max3(mx4[3], __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the maximum the sums are taken against moves only when it grew by more than 2^8 (or was unset)
@@ -329,17 +355,28 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 moved = true;
             }
             const float neg = m_run == -INFINITY ? 0.0f : m_run * sl;
-            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // s * scale - max for two keys per instruction (packed float32 pairs), the exponentials one by one, the
+            // sums in pairs again; the pair of probabilities is rounded to bfloat16 at once, into a register whose
+            // values have been used already
+            const unsigned long long sl2 = at_pack2(sl, sl), neg2 = at_pack2(-neg, -neg);
+            unsigned long long sum2[2] = {0ull, 0ull};
 #pragma unroll
             for (int j = 0; j < AT_BN; j += 4) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float pv = at_exp2(fmaf(__uint_as_float(v[j + e]), sl, -neg));     // 2^-inf = 0 for masked keys
-                    sum4[e] += pv;
-                    v[j + e] = __float_as_uint(pv);
+                for (int e = 0; e < 2; e++) {
+                    const unsigned long long t = at_fma2(at_pack2(__uint_as_float(v[j + 2 * e]), __uint_as_float(v[j + 2 * e + 1])), sl2, neg2);
+                    float t0, t1;
+                    at_unpack2(t, t0, t1);
+                    const float p0 = at_exp2(t0), p1 = at_exp2(t1);                // 2^-inf = 0 for masked keys
+                    sum2[e] = at_add2(sum2[e], at_pack2(p0, p1));
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    v[(j >> 1) + e] = *reinterpret_cast<unsigned *>(&h);
                 }
             }
-            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            float s0, s1, s2, s3;
+            at_unpack2(sum2[0], s0, s1);
+            at_unpack2(sum2[1], s2, s3);
+            l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
             if (i > 0) {        // P (and O, if it has to be rescaled) are free once the product of the tile before is complete
                 if (!at_wait(at_smem(&pv_done[g]), ph ^ 1u)) { if (lane == 0) { status[0] = 8; status[1] = i; } failed = true; break; }
                 at_fence_after();
@@ -357,11 +394,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 }
             }
             // P as bf16 pairs into the tensor-memory columns S came from (64 of its 128)
-#pragma unroll
-            for (int j = 0; j < AT_BN; j += 2) {      // packed in place: pair j / 2 overwrites a value already used
-                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                v[j >> 1] = *reinterpret_cast<unsigned *>(&h);
-            }
             at_st32(tS + lane_addr, v);
             at_st32(tS + lane_addr + 32u, v + 32);
             at_wait_st();
