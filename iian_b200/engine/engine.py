@@ -20,6 +20,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Union
 
 import torch
 
+from .. import ops
 from ..config.engine import EngineConfig
 from ..parts.base import KVNeed
 from ..sampling.params import SamplingParams
@@ -199,6 +200,9 @@ class Engine:
                       for r in reqs]
         tokens = self.sampler.sample(logits, [r.params for r in reqs], [r.seed for r in reqs],
                                      [r.n_output for r in reqs], banned)
+        kernels = ops.kernels()
+        if hasattr(kernels, "check_device_status"):
+            kernels.check_device_status()      # the tokens are on the host: a kernel that gave up has said so by now
         now = time.monotonic()
         for r, tok in zip(reqs, tokens):
             r.tokens.append(tok)

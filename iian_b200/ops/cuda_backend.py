@@ -380,8 +380,19 @@ class CudaKernels:
             self._tc_status[device] = t
         return t
 
+    _tc_used = False           # a tcgen05 kernel was launched since the status was last read
+
+    def check_device_status(self) -> None:
+        """Called where the host has just waited for the device anyway (tokens or logits were read): if a tcgen05
+        kernel ran since the last call, read its status words and raise if one gave up on a barrier."""
+        if not CudaKernels._tc_used:
+            return
+        for device in list(self._tc_status):
+            self.tcgen05_check(device)
+
     def tcgen05_check(self, device) -> None:
         """Synchronise and raise if a tcgen05 kernel gave up waiting (its output would be garbage)."""
+        CudaKernels._tc_used = False
         t = self._tc_status.get(device)
         if t is None:
             return
@@ -420,6 +431,7 @@ class CudaKernels:
         if bn == 0:
             bn = self.tcgen05_tile(t_rows, n)
         status = self.tcgen05_status_buffer(x.device).data_ptr()
+        CudaKernels._tc_used = True
         if row_scale is None and residual_norm is None:
             fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05",
                      [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
@@ -522,6 +534,7 @@ class CudaKernels:
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or q.numel() != n * num_heads * head_dim:
             raise KernelError("paged_attention_tc: cache / q shapes do not match the head counts")
         status = self.tcgen05_status_buffer(q.device)
+        CudaKernels._tc_used = True
         bt = meta.block_table
         fn = _fn("attention_tc", "iian_attention_tc",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

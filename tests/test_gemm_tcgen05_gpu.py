@@ -69,3 +69,22 @@ def test_gemm_tcgen05_refuses_what_it_cannot_do():
         k.gemm_tcgen05(rnd(8, 60), rnd(16, 60), torch.empty(8, 16, dtype=torch.bfloat16, device="cuda"))   # K not a multiple of 8
     with pytest.raises(KernelError):
         k.gemm_tcgen05(rnd(8, 64).float(), rnd(16, 64), torch.empty(8, 16, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_a_kernel_that_gave_up_is_reported_at_the_next_host_wait():
+    """The status words a tcgen05 kernel writes when a bounded wait runs out are read where the host waits for the
+    device anyway; here they are set by hand (no kernel is made to give up)."""
+    from iian_b200.ops.cuda_backend import CudaKernels, KernelError
+    k = K()
+    x, w = rnd(128, 64, seed=1), rnd(128, 64, seed=2)
+    out = torch.empty(128, 128, dtype=torch.bfloat16, device="cuda")
+    k.gemm_tcgen05(x, w, out)
+    k.check_device_status()                      # a clean run: nothing to report, and the flag is taken down
+    assert not CudaKernels._tc_used
+    k.check_device_status()
+    k.gemm_tcgen05(x, w, out)
+    torch.cuda.synchronize()
+    k.tcgen05_status_buffer(x.device).copy_(torch.tensor([2, 5], dtype=torch.int32))
+    with pytest.raises(KernelError, match="gave up"):
+        k.check_device_status()
+    assert k.tcgen05_status_buffer(x.device).tolist() == [0, 0]
