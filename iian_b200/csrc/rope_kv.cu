@@ -119,6 +119,79 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_fast_k
     }
 }
 
+// The fast form for head sizes up to 128 with several heads per warp: a warp takes HPW consecutive heads of a token
+// and has all their loads in flight before it touches the first (a head of 128 bfloat16 is only 256 bytes; one head
+// per warp leaves the memory system mostly idle: 27.6 us for 2048 tokens of 32 + 2 x 8 heads, against 50 MB to move).
+template <typename A, int HPW>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_wide_kernel(
+    const A * __restrict__ qkv, A * __restrict__ q_out, A * __restrict__ k_cache, A * __restrict__ v_cache,
+    const float * __restrict__ q_weight, const float * __restrict__ k_weight, const float2 * __restrict__ table,
+    const int * __restrict__ slots, int N, int nh, int nkv, int hd, float eps, int page_size, int num_pages, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nh + 2 * nkv;
+    const int groups = (heads_total + HPW - 1) / HPW;
+    const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= (long long) N * groups) return;
+    const int t = (int) (item / groups);
+    const int h0 = (int) (item % groups) * HPW;
+    const int slot = slots != nullptr ? slots[t] : -1;
+    const bool slot_ok = slot >= 0 && slot < num_pages * page_size;
+    const int half = hd >> 1;
+    const int p0 = 2 * lane;
+    const bool mine = p0 < half;
+    const A * row = qkv + (size_t) t * heads_total * hd;
+    float2 lo[HPW], hi[HPW];
+    bool live[HPW];
+#pragma unroll
+    for (int j = 0; j < HPW; j++) {
+        const int h = h0 + j;
+        live[j] = h < heads_total && (h < nh || (write_kv && slot_ok));     // a padding token stores no K/V
+        lo[j] = hi[j] = make_float2(0.0f, 0.0f);
+        if (live[j] && mine) {
+            lo[j] = Pair<A>::load(row + (size_t) h * hd + p0);
+            hi[j] = Pair<A>::load(row + (size_t) h * hd + half + p0);
+        }
+    }
+    float4 cssn = make_float4(1.0f, 0.0f, 1.0f, 0.0f);                        // cos0 sin0 cos1 sin1
+    if (table != nullptr && mine) cssn = *reinterpret_cast<const float4 *>(table + (size_t) t * half + p0);
+#pragma unroll
+    for (int j = 0; j < HPW; j++) {
+        if (!live[j]) continue;                                              // uniform over the warp
+        const int h = h0 + j;
+        const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+        A * dst;
+        if (is_q) {
+            dst = q_out + ((size_t) t * nh + h) * hd;
+        } else {
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            const int page = slot / page_size, off = slot % page_size;
+            dst = (is_k ? k_cache : v_cache) + (((size_t) page * nkv + kvh) * page_size + off) * hd;
+        }
+        const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+        float2 a = lo[j], c = hi[j];
+        if (w != nullptr) {
+            const float ss = warp_sum(a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y);
+            const float inv = rsqrtf(ss / (float) hd + eps);
+            if (mine) {
+                const float2 wl = *reinterpret_cast<const float2 *>(w + p0), wh = *reinterpret_cast<const float2 *>(w + half + p0);
+                a.x = a.x * inv * wl.x; a.y = a.y * inv * wl.y;
+                c.x = c.x * inv * wh.x; c.y = c.y * inv * wh.y;
+            }
+        }
+        if ((is_q || is_k) && table != nullptr) {
+            const float2 r0 = make_float2(a.x * cssn.x - c.x * cssn.y, a.y * cssn.z - c.y * cssn.w);
+            const float2 r1 = make_float2(a.x * cssn.y + c.x * cssn.x, a.y * cssn.w + c.y * cssn.z);
+            a = r0; c = r1;
+        }
+        if (mine) {
+            Pair<A>::store(dst + p0, a);
+            Pair<A>::store(dst + half + p0, c);
+        }
+    }
+}
+
 // General form: one warp per (token, head); any head size, partial rotation, either pairing style, bias.
 // A lane owns rotation pairs p = lane, lane + 32, ...: elements (p, p + half) in NEOX style, (2p, 2p + 1)
 // interleaved; beyond the rotated part it owns single elements.  Both members of a pair sit in the same
@@ -260,6 +333,18 @@ IIAN_API int iian_qk_norm_rope_store(
                       ((uintptr_t) v_cache & 7) == 0 && ((uintptr_t) q_weight & 7) == 0 && ((uintptr_t) k_weight & 7) == 0 &&
                       ((uintptr_t) table & 15) == 0;
     const float2 * tab = no_rope ? nullptr : (const float2 *) table;
+    if (fast && hd <= 128) {
+        constexpr int HPW = 4;          // measured at 2048 tokens of 32 + 2 x 8 heads: 2 and 4 heads per warp 21 us, 8: 25 us, 16: 34 us
+        const long long witems = (long long) N * ((nh + 2 * nkv + HPW - 1) / HPW);
+        const unsigned wblocks = (unsigned) ((witems + kWarpsPerBlock - 1) / kWarpsPerBlock);
+        if (act_dtype == IIAN_F32)
+            return iian_launch(qk_norm_rope_store_wide_kernel<float, HPW>, dim3(wblocks), dim3(threads), 0, stream,
+                (const float *) qkv, (float *) q_out, (float *) k_cache, (float *) v_cache, q_weight, k_weight, tab, slots,
+                N, nh, nkv, hd, eps, page_size, num_pages, write_kv);
+        return iian_launch(qk_norm_rope_store_wide_kernel<__nv_bfloat16, HPW>, dim3(wblocks), dim3(threads), 0, stream,
+            (const __nv_bfloat16 *) qkv, (__nv_bfloat16 *) q_out, (__nv_bfloat16 *) k_cache, (__nv_bfloat16 *) v_cache,
+            q_weight, k_weight, tab, slots, N, nh, nkv, hd, eps, page_size, num_pages, write_kv);
+    }
     if (fast) {
         if (act_dtype == IIAN_F32)
             return iian_launch(qk_norm_rope_store_fast_kernel<float>, dim3(blocks), dim3(threads), 0, stream,
