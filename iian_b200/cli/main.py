@@ -49,6 +49,10 @@ def _add_sampling_flags(o: Options) -> None:
     o.add("--top-p", "Nucleus sampling", "P", 1.0, float)
     o.add("--top-k", "Top-k sampling (0 = off)", "K", 0, int)
     o.add("--min-p", "Min-p sampling", "P", 0.0, float)
+    o.add("--repeat-penalty", "Repetition penalty (1 = off)", "R", 1.0, float)
+    o.add("--presence-penalty", "Presence penalty [-2, 2]", "X", 0.0, float)
+    o.add("--frequency-penalty", "Frequency penalty [-2, 2]", "X", 0.0, float)
+    o.add("--stop", "Stop token ids, e.g. '7,9' (the reference stops on strings; this engine has no tokenizer)", "IDS", "", str)
 
 
 def engine_config_from_args(ns):
@@ -67,6 +71,9 @@ def sampling_from_args(ns):
     # one --seed serves as the engine's base seed and, when given, as the request's own seed
     # (src/iian/cli/cmd_run.cpp:37, src/iian/cli/engine_options.cpp:111)
     return SamplingParams(temperature=ns.temp, top_p=ns.top_p, top_k=ns.top_k, min_p=ns.min_p,
+                          repetition_penalty=ns.repeat_penalty, presence_penalty=ns.presence_penalty,
+                          frequency_penalty=ns.frequency_penalty,
+                          stop_token_ids=[int(t) for t in ns.stop.replace(",", " ").split()],
                           seed=ns.seed if "seed" in ns.given else None, max_tokens=ns.max_tokens)
 
 

@@ -333,6 +333,40 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     if (pick_thread < 0 && threadIdx.x == 0) out[blockIdx.x] = imax;
 }
 
+// Logits processors in the reference's order (src/iian/sampler.cpp:72-109), as lists the host prepares per row:
+//  * allowed ids (sorted; an empty list allows everything): every other logit becomes -inf (:72-76);
+//  * one edit per touched token: l += pre (logit bias; -inf for a banned token or the end of a bad word, :77-88),
+//    then l = l > 0 ? l * mul_pos : l * mul_neg (repetition penalty: 1 / r and r, :106), then l += post
+//    (-(frequency * count + presence) for tokens that were produced, :107).
+// One block per row; a row's lists are the ranges [off[r], off[r + 1]).
+__global__ void logit_edits_kernel(float * __restrict__ logits, int V, size_t stride,
+                                   const int * __restrict__ allow_off, const int * __restrict__ allow_ids,
+                                   const int * __restrict__ edit_off, const int * __restrict__ edit_tok,
+                                   const float * __restrict__ pre, const float * __restrict__ mul_pos,
+                                   const float * __restrict__ mul_neg, const float * __restrict__ post) {
+    const int r = blockIdx.x;
+    float * row = logits + (size_t) r * stride;
+    const int a0 = allow_off[r], a1 = allow_off[r + 1];
+    if (a1 > a0) {
+        for (int v = threadIdx.x; v < V; v += blockDim.x) {
+            int lo = a0, hi = a1;                 // is v among the sorted ids [a0, a1)?
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (allow_ids[mid] < v) lo = mid + 1; else hi = mid;
+            }
+            if (lo == a1 || allow_ids[lo] != v) row[v] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    for (int e = edit_off[r] + threadIdx.x; e < edit_off[r + 1]; e += blockDim.x) {
+        const int t = edit_tok[e];
+        if (t < 0 || t >= V) continue;
+        float l = row[t] + pre[e];
+        l = l > 0.0f ? l * mul_pos[e] : l * mul_neg[e];
+        row[t] = l + post[e];
+    }
+}
+
 }  // namespace iian
 
 using namespace iian;
@@ -366,5 +400,17 @@ IIAN_API int iian_sample(const float * logits, int R, int V, long long stride, c
     if (V <= 0) return IIAN_ERR_SHAPE;
     sample_kernel<<<R, kSampleThreads, 0, stream>>>(logits, V, (size_t) stride, temperature, top_k, top_p, min_p,
                                                     uniform, out);
+    return iian_launch_status();
+}
+
+// logits [R, V] float32, changed in place.  allow_off / edit_off: [R + 1] int32 prefix sums; a token may appear in
+// at most one edit of its row.
+IIAN_API int iian_logit_edits(float * logits, int R, int V, long long stride, const int * allow_off, const int * allow_ids,
+                              const int * edit_off, const int * edit_tok, const float * pre, const float * mul_pos,
+                              const float * mul_neg, const float * post, cudaStream_t stream) {
+    if (R <= 0) return IIAN_OK;
+    if (V <= 0 || allow_off == nullptr || edit_off == nullptr) return IIAN_ERR_SHAPE;
+    logit_edits_kernel<<<R, 256, 0, stream>>>(logits, V, (size_t) stride, allow_off, allow_ids, edit_off, edit_tok, pre,
+                                              mul_pos, mul_neg, post);
     return iian_launch_status();
 }

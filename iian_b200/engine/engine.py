@@ -198,8 +198,12 @@ class Engine:
         if any(r.n_output < r.params.min_tokens for r in reqs):
             banned = [list(self.eos_token_ids) + list(r.params.stop_token_ids) if r.n_output < r.params.min_tokens else []
                       for r in reqs]
+        histories = None
+        if any(r.params.has_processors for r in reqs):      # (prompt, output) of the rows whose processors read them
+            histories = [(r.tokens[:r.n_prompt], r.tokens[r.n_prompt:]) if r.params.has_processors else ((), ())
+                         for r in reqs]
         tokens = self.sampler.sample(logits, [r.params for r in reqs], [r.seed for r in reqs],
-                                     [r.n_output for r in reqs], banned)
+                                     [r.n_output for r in reqs], banned, histories)
         kernels = ops.kernels()
         if hasattr(kernels, "check_device_status"):
             kernels.check_device_status()      # the tokens are on the host: a kernel that gave up has said so by now

@@ -733,6 +733,23 @@ class CudaKernels:
         fn = _fn("sampling", "iian_argmax", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p])
         _check(fn(logits.data_ptr(), r, v, logits.stride(0), _cuda(out, "argmax out", torch.int32), _stream()), "argmax")
 
+    def logit_edits(self, logits: torch.Tensor, ints: torch.Tensor, floats: torch.Tensor, n_allow: int, n_edit: int) -> None:
+        """Logits processors on ``logits`` [R, V] float32, in place.  ``ints`` (int32, on the device) holds, one after
+        the other, allow_off [R + 1], edit_off [R + 1], allow_ids [n_allow], edit_tok [n_edit]; ``floats`` holds pre,
+        mul_pos, mul_neg, post, [n_edit] each."""
+        r, v = logits.shape
+        if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
+            raise KernelError("logit_edits: logits must be float32 on CUDA with contiguous rows")
+        if ints.numel() != 2 * (r + 1) + n_allow + n_edit or floats.numel() != 4 * n_edit:
+            raise KernelError("logit_edits: the lists do not have the announced lengths")
+        ip, fp = _cuda(ints, "edit lists", torch.int32), _cuda(floats, "edit values", torch.float32) if n_edit else 0
+        allow_off, edit_off = ip, ip + 4 * (r + 1)
+        allow_ids, edit_tok = ip + 8 * (r + 1), ip + 8 * (r + 1) + 4 * n_allow
+        fn = _fn("sampling", "iian_logit_edits", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+        _check(fn(logits.data_ptr(), r, v, logits.stride(0), allow_off, allow_ids, edit_off, edit_tok,
+                  fp, fp + 4 * n_edit, fp + 8 * n_edit, fp + 12 * n_edit, _stream()), "logit_edits")
+
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
                min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
         r, v = logits.shape

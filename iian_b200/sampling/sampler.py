@@ -44,22 +44,88 @@ def request_seed(params: SamplingParams, engine_seed: int, request_id: int) -> i
     return (engine_seed + request_id * GOLDEN) & _MASK
 
 
+def row_edits(p: SamplingParams, prompt: Sequence[int], output: Sequence[int], banned: Sequence[int] = ()):
+    """What the logits processors do to one row, as ``(allowed ids sorted, {token: [pre, mul_pos, mul_neg, post]})``:
+    ``l += pre; l = l * mul_pos if l > 0 else l * mul_neg; l += post``, in the reference's order
+    (src/iian/sampler.cpp:72-109): allowed ids, logit bias, bad words, (banned ids while min_tokens holds), penalties.
+    """
+    edits = {}
+
+    def entry(t):
+        return edits.setdefault(int(t), [0.0, 1.0, 1.0, 0.0])
+
+    for t, b in p.logit_bias.items():
+        entry(t)[0] += float(b)
+    n_out = len(output)
+    for bw in p.bad_words:                  # the last token of a sequence whose beginning has just been produced
+        if not bw:
+            continue
+        pre = len(bw) - 1
+        if n_out < pre:
+            continue
+        if all(int(output[n_out - pre + i]) == int(bw[i]) for i in range(pre)):
+            entry(bw[-1])[0] = float("-inf")
+    for t in banned:
+        entry(t)[0] = float("-inf")
+    if p.repetition_penalty != 1.0 or p.presence_penalty != 0.0 or p.frequency_penalty != 0.0:
+        start = 0 if p.repetition_last_n < 0 else max(0, n_out - p.repetition_last_n)
+        counts = {}
+        for t in output[start:]:
+            counts[int(t)] = counts.get(int(t), 0) + 1
+        if p.repetition_penalty != 1.0:     # the repetition penalty applies to prompt tokens as well
+            for t in prompt:
+                counts.setdefault(int(t), 0)
+        for t, c in counts.items():
+            e = entry(t)
+            if p.repetition_penalty != 1.0:
+                e[1], e[2] = 1.0 / p.repetition_penalty, p.repetition_penalty
+            if c > 0:
+                e[3] -= p.frequency_penalty * c + p.presence_penalty
+    return sorted(set(int(t) for t in p.allowed_token_ids)), edits
+
+
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
 
+    def apply_processors(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                         histories: Optional[Sequence] = None, banned: Optional[Sequence[Sequence[int]]] = None) -> None:
+        """Run the rows' logits processors on the device: the host only makes the short lists of touched tokens."""
+        r, vocab = logits.shape
+        allow_off, edit_off, allow_ids, edit_tok = [0], [0], [], []
+        vals = [[], [], [], []]
+        for row in range(r):
+            p = params[row]
+            ban = banned[row] if banned is not None else ()
+            if p.has_processors or ban:
+                prompt, output = histories[row] if histories is not None and p.has_processors else ((), ())
+                allowed, edits = row_edits(p, prompt, output, ban)
+                allow_ids += [t for t in allowed if 0 <= t < vocab]
+                for t, e in edits.items():
+                    if 0 <= t < vocab:
+                        edit_tok.append(t)
+                        for j in range(4):
+                            vals[j].append(e[j])
+            allow_off.append(len(allow_ids))
+            edit_off.append(len(edit_tok))
+        if not allow_ids and not edit_tok:
+            return
+        ints = torch.tensor(allow_off + edit_off + allow_ids + edit_tok, dtype=torch.int32).to(logits.device)
+        floats = torch.tensor(vals[0] + vals[1] + vals[2] + vals[3], dtype=torch.float32).to(logits.device)
+        ops.kernels().logit_edits(logits, ints, floats, len(allow_ids), len(edit_tok))
+
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               indices: Sequence[int], banned: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+               indices: Sequence[int], banned: Optional[Sequence[Sequence[int]]] = None,
+               histories: Optional[Sequence] = None) -> List[int]:
         """One token per logits row.  ``indices[r]`` is the number of tokens request ``r`` has produced
-        so far; ``banned[r]`` lists ids that may not be produced now (min_tokens)."""
+        so far; ``banned[r]`` lists ids that may not be produced now (min_tokens); ``histories[r]`` is the
+        request's ``(prompt tokens, output tokens)``, read only for rows whose parameters have processors."""
         r = logits.shape[0]
         if r == 0:
             return []
         k = ops.kernels()
-        if banned is not None:
-            for row, ids in enumerate(banned):
-                if ids:
-                    logits[row, torch.as_tensor(list(ids), dtype=torch.long, device=logits.device)] = float("-inf")
+        if banned is not None or any(p.has_processors for p in params):
+            self.apply_processors(logits, params, histories, banned)
         out = torch.empty(r, dtype=torch.int32, device=logits.device)
         if all(p.is_greedy for p in params):
             k.argmax(logits, out)

@@ -232,3 +232,48 @@ def sample_from(probs: torch.Tensor, u: float) -> int:
             if run > r:
                 return i
     return last
+
+
+def process_logits(logits: torch.Tensor, prompt: Sequence[int], output: Sequence[int], *, allowed=(), bias=None,
+                   bad_words=(), banned=(), presence=0.0, frequency=0.0, repetition=1.0, last_n=-1) -> torch.Tensor:
+    """The logits processors on one row, dense and in the reference's order (src/iian/sampler.cpp:72-109): allowed
+    ids (:72-76), logit bias (:77), bad words (:78-88), ids that may not be produced yet (the caller's EOS mask while
+    min_tokens holds, :89-91), then the penalties over the counts of the last ``last_n`` output tokens, the
+    repetition penalty reaching prompt tokens too (:93-109)."""
+    l = logits.clone().double()
+    n_vocab = l.numel()
+    if len(allowed):
+        keep = torch.full_like(l, float("-inf"))
+        for t in allowed:
+            if 0 <= t < n_vocab:
+                keep[t] = l[t]
+        l = keep
+    for t, b in (bias or {}).items():
+        l[t] += b
+    n_out = len(output)
+    for bw in bad_words:
+        if not len(bw):
+            continue
+        pre = len(bw) - 1
+        if n_out < pre:
+            continue
+        if all(output[n_out - pre + i] == bw[i] for i in range(pre)) and 0 <= bw[-1] < n_vocab:
+            l[bw[-1]] = float("-inf")
+    for t in banned:
+        l[t] = float("-inf")
+    if repetition != 1.0 or presence != 0.0 or frequency != 0.0:
+        counts: Dict[int, int] = {}
+        start = 0 if last_n < 0 else max(0, n_out - last_n)
+        for t in output[start:]:
+            counts[t] = counts.get(t, 0) + 1
+        if repetition != 1.0:
+            for t in prompt:
+                counts.setdefault(t, 0)
+        for t, c in counts.items():
+            if t < 0 or t >= n_vocab:
+                continue
+            if repetition != 1.0:
+                l[t] = l[t] / repetition if l[t] > 0 else l[t] * repetition
+            if c > 0:
+                l[t] -= frequency * c + presence
+    return l
