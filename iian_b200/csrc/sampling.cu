@@ -367,6 +367,69 @@ __global__ void logit_edits_kernel(float * __restrict__ logits, int V, size_t st
     }
 }
 
+// Log-probabilities of the raw distribution (src/iian/sampler.cpp:63-70, 174-182): log softmax of the row at the
+// chosen token and at the k largest logits (value descending, lowest id first among equals).  One block per row;
+// the k-th pick is the largest entry that comes after the pick before it in that order, so no entry is marked.
+__global__ void __launch_bounds__(kSampleThreads) logprobs_kernel(
+    const float * __restrict__ logits, int V, size_t stride, const int * __restrict__ tokens, const int * __restrict__ want_k,
+    int kmax, float * __restrict__ out_lp, int * __restrict__ top_ids, float * __restrict__ top_lp) {
+    __shared__ float fs[32];
+    __shared__ int is[32];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int k = want_k[r];
+    if (k < 0) return;
+    const float * row = logits + (size_t) r * stride;
+    float mx; int mi;
+    block_argmax(row, V, 1.0f, mx, mi, fs, is);
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) acc += expf(row[i] - mx);
+    __syncthreads();
+    const float lse = mx + logf(block_sum(acc, red));
+    if (threadIdx.x == 0) {
+        const int t = tokens[r];
+        out_lp[r] = (t >= 0 && t < V) ? row[t] - lse : -INFINITY;
+    }
+    float pv = INFINITY;
+    int pi = -1;
+    for (int j = 0; j < kmax; j++) {
+        if (j >= k || j >= V) {
+            if (threadIdx.x == 0) { top_ids[(size_t) r * kmax + j] = -1; top_lp[(size_t) r * kmax + j] = -INFINITY; }
+            continue;
+        }
+        float b = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            const bool after = v < pv || (v == pv && i > pi);          // after the pick before, in (value desc, id asc) order
+            if (after && (v > b || (v == b && i < bi))) { b = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, b, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > b || (ob == b && oi < bi)) { b = ob; bi = oi; }
+        }
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        __syncthreads();
+        if (lane == 0) { fs[warp] = b; is[warp] = bi; }
+        __syncthreads();
+        b = lane < (blockDim.x >> 5) ? fs[lane] : -INFINITY;
+        bi = lane < (blockDim.x >> 5) ? is[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, b, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > b || (ob == b && oi < bi)) { b = ob; bi = oi; }
+        }
+        pv = b; pi = bi;
+        if (threadIdx.x == 0) {
+            top_ids[(size_t) r * kmax + j] = bi == 0x7fffffff ? -1 : bi;
+            top_lp[(size_t) r * kmax + j] = bi == 0x7fffffff ? -INFINITY : b - lse;
+        }
+    }
+}
+
 }  // namespace iian
 
 using namespace iian;
@@ -412,5 +475,15 @@ IIAN_API int iian_logit_edits(float * logits, int R, int V, long long stride, co
     if (V <= 0 || allow_off == nullptr || edit_off == nullptr) return IIAN_ERR_SHAPE;
     logit_edits_kernel<<<R, 256, 0, stream>>>(logits, V, (size_t) stride, allow_off, allow_ids, edit_off, edit_tok, pre,
                                               mul_pos, mul_neg, post);
+    return iian_launch_status();
+}
+
+// Raw log-probabilities: out_lp [R] at tokens [R]; the want_k[r] (at most kmax; negative: skip the row) largest
+// entries of row r into top_ids / top_lp [R, kmax], the rest of a row filled with -1 / -inf.
+IIAN_API int iian_logprobs(const float * logits, int R, int V, long long stride, const int * tokens, const int * want_k,
+                           int kmax, float * out_lp, int * top_ids, float * top_lp, cudaStream_t stream) {
+    if (R <= 0) return IIAN_OK;
+    if (V <= 0 || kmax < 0 || kmax > 64) return IIAN_ERR_SHAPE;
+    logprobs_kernel<<<R, kSampleThreads, 0, stream>>>(logits, V, (size_t) stride, tokens, want_k, kmax, out_lp, top_ids, top_lp);
     return iian_launch_status();
 }

@@ -202,8 +202,15 @@ class Engine:
         if any(r.params.has_processors for r in reqs):      # (prompt, output) of the rows whose processors read them
             histories = [(r.tokens[:r.n_prompt], r.tokens[r.n_prompt:]) if r.params.has_processors else ((), ())
                          for r in reqs]
+        want_lp = any(r.params.logprobs >= 0 for r in reqs)
+        raw = logits.clone() if want_lp and (banned is not None or histories is not None) else logits
         tokens = self.sampler.sample(logits, [r.params for r in reqs], [r.seed for r in reqs],
                                      [r.n_output for r in reqs], banned, histories)
+        if want_lp:                                       # of the raw distribution, as the reference reports them
+            for r, lp in zip(reqs, self.sampler.logprobs(raw, tokens, [r.params for r in reqs])):
+                if lp is not None:
+                    r.pending_logprobs.append(lp)
+                    r.logprobs.append(lp)
         kernels = ops.kernels()
         if hasattr(kernels, "check_device_status"):
             kernels.check_device_status()      # the tokens are on the host: a kernel that gave up has said so by now
@@ -238,10 +245,11 @@ class Engine:
                 self._deliver(r, False)
 
     def _deliver(self, r: Request, final: bool) -> None:
-        chunk = OutputChunk(tokens=r.pending_tokens, finished=final, finish_reason=r.finish_reason,
-                            stop_reason=r.stop_reason, error=r.error, n_prompt_tokens=r.n_prompt,
-                            n_output_tokens=r.n_output, n_cached_tokens=r.num_cached_tokens)
+        chunk = OutputChunk(tokens=r.pending_tokens, logprobs=r.pending_logprobs, finished=final,
+                            finish_reason=r.finish_reason, stop_reason=r.stop_reason, error=r.error,
+                            n_prompt_tokens=r.n_prompt, n_output_tokens=r.n_output, n_cached_tokens=r.num_cached_tokens)
         r.pending_tokens = []
+        r.pending_logprobs = []
         r.outputs.append(chunk)
 
     def _finish(self, r: Request, status: RequestStatus, why: FinishReason, error: str = "") -> None:

@@ -40,6 +40,7 @@ class FinishReason(enum.Enum):
 @dataclass
 class OutputChunk:
     tokens: List[int] = field(default_factory=list)
+    logprobs: List = field(default_factory=list)      # parallel to tokens, if asked for: (logprob, [(id, logprob)])
     finished: bool = False
     finish_reason: FinishReason = FinishReason.NONE
     stop_reason: str = ""
@@ -89,6 +90,8 @@ class Request:
         self.seed = seed
         self.outputs: List[OutputChunk] = []
         self.pending_tokens: List[int] = []
+        self.pending_logprobs: List = []
+        self.logprobs: List = []                     # of all output tokens so far, if asked for
         self.t_first_token = self.t_last_token = self.t_finished = 0.0
         self.tokens = _Tokens(int(t) for t in tokens)       # prompt + generated
         self.tokens._req = None

@@ -750,6 +750,21 @@ class CudaKernels:
         _check(fn(logits.data_ptr(), r, v, logits.stride(0), allow_off, allow_ids, edit_off, edit_tok,
                   fp, fp + 4 * n_edit, fp + 8 * n_edit, fp + 12 * n_edit, _stream()), "logit_edits")
 
+    def logprobs(self, logits: torch.Tensor, tokens: torch.Tensor, want_k: torch.Tensor, kmax: int):
+        """Raw log-probabilities of ``tokens`` [R] and of the ``want_k[r]`` most likely tokens of each row (negative:
+        the row is skipped): ``(lp [R], top_ids [R, kmax], top_lp [R, kmax])`` on the device."""
+        r, v = logits.shape
+        if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
+            raise KernelError("logprobs: logits must be float32 on CUDA with contiguous rows")
+        lp = torch.full((r,), float("-inf"), dtype=torch.float32, device=logits.device)
+        ids = torch.full((r, max(kmax, 1)), -1, dtype=torch.int32, device=logits.device)
+        lps = torch.full((r, max(kmax, 1)), float("-inf"), dtype=torch.float32, device=logits.device)
+        fn = _fn("sampling", "iian_logprobs", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p])
+        _check(fn(logits.data_ptr(), r, v, logits.stride(0), _cuda(tokens, "tokens", torch.int32),
+                  _cuda(want_k, "want_k", torch.int32), kmax, lp.data_ptr(), ids.data_ptr(), lps.data_ptr(), _stream()), "logprobs")
+        return lp, ids, lps
+
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
                min_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
         r, v = logits.shape

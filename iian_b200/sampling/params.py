@@ -2,8 +2,8 @@
 
 Names, defaults and validation follow ``SamplingParams`` of the reference
 (include/iian/sampling.h:15-46, src/iian/sampler.cpp:13-28), the logits processors included: allowed ids, logit
-bias, bad words and the presence / frequency / repetition penalties (sampler.cpp:72-109).  Log-probabilities, stop
-strings and grammars need a tokenizer or text on the sampling path and are not part of this engine.
+bias, bad words and the presence / frequency / repetition penalties (sampler.cpp:72-109).  Log-probabilities are those of the raw
+distribution (sampler.cpp:63-70, 174-182).  Stop strings and grammars need text and are not part of this engine.
 """
 from __future__ import annotations
 
@@ -26,6 +26,7 @@ class SamplingParams:
     min_tokens: int = 0
     ignore_eos: bool = False
     stop_token_ids: List[int] = field(default_factory=list)
+    logprobs: int = -1                # -1 none, 0 the produced token only, k: the k most likely tokens as well (<= 20)
     logit_bias: Dict[int, float] = field(default_factory=dict)
     allowed_token_ids: List[int] = field(default_factory=list)
     bad_words: List[List[int]] = field(default_factory=list)      # token sequences that may not be produced
@@ -54,6 +55,8 @@ class SamplingParams:
             raise ValueError("frequency_penalty must be in [-2, 2]")
         if self.repetition_penalty <= 0.0:
             raise ValueError("repetition_penalty must be > 0")
+        if self.logprobs > 20:
+            raise ValueError("logprobs must be <= 20")
         for t in self.logit_bias:
             if t < 0 or t >= n_vocab:
                 raise ValueError(f"logit_bias token id out of range: {t}")

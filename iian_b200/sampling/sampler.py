@@ -141,3 +141,17 @@ class Sampler:
         top_k = dev[4].to(torch.int32)
         k.sample(logits, dev[0].contiguous(), top_k, dev[1].contiguous(), dev[2].contiguous(), dev[3].contiguous(), out)
         return out.tolist()
+
+    def logprobs(self, raw_logits: torch.Tensor, tokens: Sequence[int], params: Sequence[SamplingParams]):
+        """For every row whose parameters ask for it: ``(log-probability of its token, [(id, log-probability)] of the
+        ``logprobs`` most likely tokens)`` under the raw distribution (before any processor); ``None`` for the others."""
+        want = [p.logprobs for p in params]
+        if all(w < 0 for w in want):
+            return [None] * len(want)
+        kmax = max(max(want), 0)
+        dev = raw_logits.device
+        lp, ids, lps = ops.kernels().logprobs(raw_logits, torch.tensor(list(tokens), dtype=torch.int32).to(dev),
+                                              torch.tensor(want, dtype=torch.int32).to(dev), kmax)
+        lp, ids, lps = lp.tolist(), ids.tolist(), lps.tolist()
+        return [None if w < 0 else (lp[r], [(ids[r][j], lps[r][j]) for j in range(min(w, len(ids[r]))) if ids[r][j] >= 0])
+                for r, w in enumerate(want)]

@@ -125,3 +125,53 @@ def test_generation_with_penalties_follows_the_plain_walk(tmp_path):
             assert margins[k] < 1e-4, (k, got, want)
             break
     assert len(got) == 10 and 8 not in got and all(t in allowed for t in got)
+
+
+@pytest.mark.gpu
+def test_logprobs_kernel():
+    from iian_b200.sampling.sampler import Sampler
+    vocab, rows = 1500, 5
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn(rows, vocab, generator=g) * 4).float()
+    logits[1, 7] = logits[1, 900] = logits[1].max() + 1.0          # equal values: the lower id comes first
+    logits[3, 10:20] = float("-inf")
+    tokens = [3, 900, 55, 12, 1499]
+    params = [SamplingParams(logprobs=k) for k in (0, 5, -1, 20, 1)]
+    got = Sampler(torch.device("cuda")).logprobs(logits.cuda(), tokens, params)
+    ref = torch.log_softmax(logits.double(), dim=-1)
+    for r, p in enumerate(params):
+        if p.logprobs < 0:
+            assert got[r] is None
+            continue
+        lp, top = got[r]
+        want_lp = ref[r, tokens[r]].item()
+        assert lp == want_lp if want_lp == float("-inf") else abs(lp - want_lp) < 1e-4
+        order = sorted(range(vocab), key=lambda i: (-logits[r, i].item(), i))[:p.logprobs]
+        assert [t for t, _ in top] == order
+        for t, v in top:
+            assert abs(v - ref[r, t].item()) < 1e-4
+
+
+@pytest.mark.gpu
+def test_logprobs_through_the_engine_are_those_of_the_raw_distribution(tmp_path):
+    from helpers import TINY, random_tokens, write_tiny
+    from iian_b200 import EngineConfig, SamplingParams as SP
+    from iian_b200.engine.engine import Engine
+    d = write_tiny(str(tmp_path), "A")
+    cfg, w = plain.load_folder(d)
+    vocab = TINY["A"]["vocab_size"]
+    prompt = random_tokens(vocab, 6, 9)
+    eng = Engine(d, EngineConfig(dtype="float32", block_size=8, max_model_len=64, kv_cache_tokens=256))
+    r = eng.submit(prompt, SP(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=3, repetition_penalty=1.5,
+                              logit_bias={2: 3.0}))
+    while not r.is_finished:
+        eng.step()
+    out = r.output_tokens
+    assert len(r.logprobs) == len(out) == 6
+    assert sum(len(c.logprobs) for c in r.outputs) == 6
+    toks = list(prompt)
+    for tok, (lp, top) in zip(out, r.logprobs):
+        ref = torch.log_softmax(plain.forward(cfg, w, toks)[-1].double(), dim=-1)      # before bias and penalty
+        assert abs(lp - ref[tok].item()) < 1e-3
+        assert len(top) == 3 and top[0][0] == int(torch.argmax(ref)) and abs(top[0][1] - ref.max().item()) < 1e-3
+        toks.append(tok)
