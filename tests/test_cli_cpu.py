@@ -49,6 +49,10 @@ def test_flags_map_to_the_configs():
     s = sampling_from_args(ns)
     assert s.max_tokens == 9 and s.is_greedy and s.top_k == 4 and s.top_p == 0.5 and s.min_p == 0.1 and s.seed == 11
     assert sampling_from_args(opts().parse([])).seed is None and sampling_from_args(opts().parse([])).temperature == 0.7
+    p = sampling_from_args(opts().parse(["--repeat-penalty", "1.2", "--presence-penalty", "0.5", "--frequency-penalty", "-1",
+                                         "--stop", "7,9"]))
+    assert (p.repetition_penalty, p.presence_penalty, p.frequency_penalty, p.stop_token_ids) == (1.2, 0.5, -1.0, [7, 9])
+    assert p.has_processors and not sampling_from_args(opts().parse([])).has_processors
 
 
 def test_commands(capsys):
