@@ -192,6 +192,97 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_wide_k
     }
 }
 
+// Head size 128 in bfloat16, the serving case: the kernel above is bound by instruction issue (64 % of the issue
+// slots at 2048 tokens), not by memory, so this form moves 8 bytes per access.  Sixteen lanes own a head: lane s of
+// them has elements 4 s .. 4 s + 3 of each half, i.e. four rotation pairs; a warp works on two heads at a time and
+// on HPW heads of a token in all.
+template <int HPW>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_vec128_kernel(
+    const __nv_bfloat16 * __restrict__ qkv, __nv_bfloat16 * __restrict__ q_out, __nv_bfloat16 * __restrict__ k_cache,
+    __nv_bfloat16 * __restrict__ v_cache, const float * __restrict__ q_weight, const float * __restrict__ k_weight,
+    const float2 * __restrict__ table, const int * __restrict__ slots, int N, int nh, int nkv, float eps, int page_size,
+    int num_pages, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int hd = 128, half = 64;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane & 15, hsel = lane >> 4;
+    const int heads_total = nh + 2 * nkv;
+    const int groups = (heads_total + HPW - 1) / HPW;
+    const long long item = (long long) blockIdx.x * kWarpsPerBlock + warp;
+    if (item >= (long long) N * groups) return;
+    const int t = (int) (item / groups);
+    const int h0 = (int) (item % groups) * HPW;
+    const int slot = slots != nullptr ? slots[t] : -1;
+    const bool slot_ok = slot >= 0 && slot < num_pages * page_size;
+    const int page = slot_ok ? slot / page_size : 0, off = slot_ok ? slot % page_size : 0;
+    const __nv_bfloat16 * row = qkv + (size_t) t * heads_total * hd;
+    uint2 lo[HPW / 2], hi[HPW / 2];
+#pragma unroll
+    for (int j = 0; j < HPW / 2; j++) {
+        const int h = h0 + 2 * j + hsel;
+        lo[j] = hi[j] = make_uint2(0u, 0u);
+        if (h < heads_total && (h < nh || (write_kv && slot_ok))) {
+            lo[j] = *reinterpret_cast<const uint2 *>(row + (size_t) h * hd + 4 * sub);
+            hi[j] = *reinterpret_cast<const uint2 *>(row + (size_t) h * hd + half + 4 * sub);
+        }
+    }
+    float cs[4] = {1.0f, 1.0f, 1.0f, 1.0f}, sn[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (table != nullptr) {
+        const float4 t0 = *reinterpret_cast<const float4 *>(table + (size_t) t * half + 4 * sub);
+        const float4 t1 = *reinterpret_cast<const float4 *>(table + (size_t) t * half + 4 * sub + 2);
+        cs[0] = t0.x; sn[0] = t0.y; cs[1] = t0.z; sn[1] = t0.w; cs[2] = t1.x; sn[2] = t1.y; cs[3] = t1.z; sn[3] = t1.w;
+    }
+#pragma unroll
+    for (int j = 0; j < HPW / 2; j++) {
+        const int h = h0 + 2 * j + hsel;
+        const bool live = h < heads_total && (h < nh || (write_kv && slot_ok));     // a padding token stores no K/V
+        const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+        const float * w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+        float a[4], c[4];
+        {
+            const float2 a01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&lo[j].x));
+            const float2 a23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&lo[j].y));
+            const float2 c01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&hi[j].x));
+            const float2 c23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&hi[j].y));
+            a[0] = a01.x; a[1] = a01.y; a[2] = a23.x; a[3] = a23.y;
+            c[0] = c01.x; c[1] = c01.y; c[2] = c23.x; c[3] = c23.y;
+        }
+        // sum of squares over the sixteen lanes of this head (all lanes take part in the shuffles)
+        float ss = (a[0] * a[0] + a[1] * a[1]) + (a[2] * a[2] + a[3] * a[3]) + (c[0] * c[0] + c[1] * c[1]) + (c[2] * c[2] + c[3] * c[3]);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (!live) continue;
+        if (w != nullptr) {
+            const float inv = rsqrtf(ss / (float) hd + eps);
+            const float4 wl = *reinterpret_cast<const float4 *>(w + 4 * sub), wh = *reinterpret_cast<const float4 *>(w + half + 4 * sub);
+            a[0] *= inv * wl.x; a[1] *= inv * wl.y; a[2] *= inv * wl.z; a[3] *= inv * wl.w;
+            c[0] *= inv * wh.x; c[1] *= inv * wh.y; c[2] *= inv * wh.z; c[3] *= inv * wh.w;
+        }
+        if ((is_q || is_k) && table != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float r0 = a[i] * cs[i] - c[i] * sn[i], r1 = a[i] * sn[i] + c[i] * cs[i];
+                a[i] = r0; c[i] = r1;
+            }
+        }
+        __nv_bfloat16 * dst;
+        if (is_q) {
+            dst = q_out + ((size_t) t * nh + h) * hd;
+        } else {
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            dst = (is_k ? k_cache : v_cache) + (((size_t) page * nkv + kvh) * page_size + off) * hd;
+        }
+        uint2 o0, o1;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(a[0], a[1]), p1 = __floats2bfloat162_rn(a[2], a[3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(c[0], c[1]), p3 = __floats2bfloat162_rn(c[2], c[3]);
+        o0.x = *reinterpret_cast<unsigned *>(&p0); o0.y = *reinterpret_cast<unsigned *>(&p1);
+        o1.x = *reinterpret_cast<unsigned *>(&p2); o1.y = *reinterpret_cast<unsigned *>(&p3);
+        *reinterpret_cast<uint2 *>(dst + 4 * sub) = o0;
+        *reinterpret_cast<uint2 *>(dst + half + 4 * sub) = o1;
+    }
+}
+
 // General form: one warp per (token, head); any head size, partial rotation, either pairing style, bias.
 // A lane owns rotation pairs p = lane, lane + 32, ...: elements (p, p + half) in NEOX style, (2p, 2p + 1)
 // interleaved; beyond the rotated part it owns single elements.  Both members of a pair sit in the same
@@ -333,6 +424,14 @@ IIAN_API int iian_qk_norm_rope_store(
                       ((uintptr_t) v_cache & 7) == 0 && ((uintptr_t) q_weight & 7) == 0 && ((uintptr_t) k_weight & 7) == 0 &&
                       ((uintptr_t) table & 15) == 0;
     const float2 * tab = no_rope ? nullptr : (const float2 *) table;
+    if (fast && hd == 128 && act_dtype == IIAN_BF16 && ((uintptr_t) q_weight & 15) == 0 && ((uintptr_t) k_weight & 15) == 0) {
+        constexpr int HPW = 4;
+        const long long witems = (long long) N * ((nh + 2 * nkv + HPW - 1) / HPW);
+        const unsigned wblocks = (unsigned) ((witems + kWarpsPerBlock - 1) / kWarpsPerBlock);
+        return iian_launch(qk_norm_rope_store_vec128_kernel<HPW>, dim3(wblocks), dim3(threads), 0, stream,
+            (const __nv_bfloat16 *) qkv, (__nv_bfloat16 *) q_out, (__nv_bfloat16 *) k_cache, (__nv_bfloat16 *) v_cache,
+            q_weight, k_weight, tab, slots, N, nh, nkv, eps, page_size, num_pages, write_kv);
+    }
     if (fast && hd <= 128) {
         constexpr int HPW = 4;          // measured at 2048 tokens of 32 + 2 x 8 heads: 2 and 4 heads per warp 21 us, 8: 25 us, 16: 34 us
         const long long witems = (long long) N * ((nh + 2 * nkv + HPW - 1) / HPW);
