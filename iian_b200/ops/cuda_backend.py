@@ -196,11 +196,11 @@ class CudaKernels:
         k = w.shape[1]
         if n_rows <= self.SKINNY_MAX_ROWS:
             return k % 32 == 0
-        return n_rows >= self.TCGEN05_MIN_ROWS and k % 8 == 0 and not self.LIBRARY_GEMM_ONLY
+        return self._tcgen05_rows_ok(n_rows, w.shape[0]) and k % 8 == 0 and not self.LIBRARY_GEMM_ONLY
 
     def norm_parts(self, w: torch.Tensor, n_rows: int = 1) -> int:
         """Parts in which a ResidualNorm product of ``n_rows`` rows with weight ``w`` leaves the sums of squares."""
-        if n_rows >= self.TCGEN05_MIN_ROWS:
+        if n_rows > self.SKINNY_MAX_ROWS:
             return -(-w.shape[0] // self.tcgen05_tile_columns(n_rows, w.shape[0]))
         return -(-w.shape[0] // 16)
 
@@ -249,8 +249,20 @@ class CudaKernels:
     TCGEN05_MIN_ROWS = 128
     LIBRARY_GEMM_ONLY = os.environ.get("IIAN_LIBRARY_GEMM", "0") not in ("0", "false", "off")
 
+    # ... and only when the product has many tiles of 256 x 256 (several waves of the 74 pairs of SMs): with few tiles
+    # the SMs that work cannot stream the weights fast enough, and with one or two waves the idle tail of the last
+    # wave costs more than the fused epilogue saves; the library product (which splits K, and uses TMA multicast in
+    # clusters of four) is faster there.  Measured on B200 at the Qwen3-8B sizes, whole prefill steps in ms with the
+    # threshold at 0 / 64 / 130 / 400 / all library: 256 tokens 9.4 / 6.5 / - / - / -; 1024 tokens 15.2 / 15.2 / 13.9 /
+    # 14.4 / 14.3; 2048 tokens 27.1 / 27.1 / 26.2 / 25.9 / 27.6; 4096 tokens - / - / 54.4 / 52.5 / 52.9.  At 300 the own
+    # kernel takes the gate/up product with its SwiGLU epilogue from 1024 rows on (384 tiles) and nothing else of a layer.
+    TCGEN05_MIN_TILES = int(os.environ.get("IIAN_TCGEN05_MIN_TILES", "300"))
+
+    def _tcgen05_rows_ok(self, n: int, m: int) -> bool:
+        return n >= self.TCGEN05_MIN_ROWS and (-(-n // 256)) * (-(-m // 256)) >= self.TCGEN05_MIN_TILES
+
     def _tcgen05_ok(self, x, w, n, k) -> bool:
-        return (not self.LIBRARY_GEMM_ONLY and n >= self.TCGEN05_MIN_ROWS and k % 8 == 0
+        return (not self.LIBRARY_GEMM_ONLY and self._tcgen05_rows_ok(n, w.shape[0]) and k % 8 == 0
                 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 

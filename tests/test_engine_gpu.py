@@ -207,3 +207,22 @@ def test_decode_steps_from_graphs_match_eager_steps(setup, name, dtype):
         scale = max(1.0, outs[0].float().abs().max().item())
         assert err <= tol_ * scale, f"step {rec['step']}: graph and eager logits differ by {err} (scale {scale})"
     assert reps[1].runner._graphs, "no decode graph was captured"
+
+
+def test_product_dispatch_by_tiles(monkeypatch):
+    """bfloat16 products: up to 8 rows the weight-streaming kernel, from 128 rows the tcgen05 kernel if the product
+    has several waves of tiles of 256 x 256, the library product in between and for fewer tiles."""
+    from iian_b200.ops.cuda_backend import CudaKernels
+    k = CudaKernels()
+    monkeypatch.setattr(CudaKernels, "TCGEN05_MIN_TILES", 300)
+    def ok(rows, out_features, in_features=4096):
+        x = torch.empty(rows, in_features, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(out_features, in_features, dtype=torch.bfloat16, device="cuda")
+        return k._tcgen05_ok(x, w, rows, in_features), k.can_fuse_norm(x, w), k.can_take_prenormed(rows, w, torch.bfloat16)
+    assert ok(8, 4096) == (False, True, True)               # the streaming kernel folds norms too
+    assert ok(64, 4096) == (False, False, False)
+    assert ok(2048, 4096) == (False, False, False)          # 8 x 16 tiles: the library
+    assert ok(2048, 6144) == (False, False, False)          # 8 x 24
+    assert ok(1024, 24576) == (True, True, True)            # 4 x 96
+    assert ok(512, 24576) == (False, False, False)          # 2 x 96
+    assert ok(2048, 151936)[0]
