@@ -949,8 +949,10 @@ IIAN_API int iian_attention_decode_fused(
 //  * The array has kNoAllocScratchFloats floats (8 MiB) for partial results, after a fixed region of
 //    kNoAllocCounters ints for the per-row-tile arrival counters.  Every GPU on which this library is
 //    loaded holds both until the process exits.
-//  * A call needs N * nh * n_split * (hd + 1) floats and S * nkv * ceil(max_q_len * nh / nkv / 16)
-//    counters; a larger request is refused with IIAN_ERR_LIMIT and nothing is launched.
+//  * A call with n_split > 1 needs N * nh * n_split * (hd + 1) floats and, in the decode form, S * nkv *
+//    ceil(max_q_len * nh / nkv / 16) counters; a larger request is refused with IIAN_ERR_LIMIT and nothing
+//    is launched.  The form that merges inside a thread-block cluster (small_tiles == 2) and unsplit calls
+//    use nothing of the array and are not limited by it.
 //    iian_attention_mma_noalloc_capacity() returns the limit in floats.
 //  * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
 //    device current) and remembers it per device.  Make that first call before any stream capture.
@@ -980,24 +982,31 @@ IIAN_API int iian_attention_mma_noalloc(
     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
     float scale, int window, int n_split, int small_tiles, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
-    if (n_split < 1 || nh <= 0 || hd <= 0) return IIAN_ERR_SHAPE;
+    if (n_split < 1 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || (hd != 64 && hd != 128)) return IIAN_ERR_SHAPE;
+    // which form runs decides what it needs of the array: the cluster form (small_tiles == 2, n_split 2..8)
+    // merges in shared memory and needs nothing; the prefill form (small_tiles == 0) needs the partial results
+    // but no counters; an unsplit call needs neither
+    const bool uses_scratch = n_split > 1 && small_tiles != 2;
+    const bool uses_counters = uses_scratch && small_tiles != 0;
     const unsigned long long need = (unsigned long long) N * nh * n_split * (unsigned long long) (hd + 1);
-    if (n_split > 1 && need > kNoAllocScratchFloats) return IIAN_ERR_LIMIT;
-    if (nkv <= 0 || nh % nkv != 0) return IIAN_ERR_SHAPE;
+    if (uses_scratch && need > kNoAllocScratchFloats) return IIAN_ERR_LIMIT;
     const unsigned long long n_counters = (unsigned long long) S * nkv * (((unsigned long long) max_q_len * (nh / nkv) + 15) / 16);
-    if (n_split > 1 && n_counters > kNoAllocCounters) return IIAN_ERR_LIMIT;
+    if (uses_counters && n_counters > kNoAllocCounters) return IIAN_ERR_LIMIT;
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return 1000 + (int) e;
     if (dev < 0 || dev >= kMaxDevices) return IIAN_ERR_LIMIT;
-    if (g_noalloc_ptr[dev] == nullptr) {          // set-up, once per device, with that device current
-        float * ptr = nullptr;
+    float * base = __atomic_load_n(&g_noalloc_ptr[dev], __ATOMIC_ACQUIRE);
+    if (base == nullptr) {          // set-up, once per device, with that device current (two threads that race
+        float * ptr = nullptr;      // here both look the same address up and store the same value)
         e = cudaGetSymbolAddress((void **) &ptr, g_noalloc_scratch);
-        if (e != cudaSuccess || ptr == nullptr) return 1000 + (int) e;
-        g_noalloc_ptr[dev] = ptr;
+        if (e != cudaSuccess) return 1000 + (int) e;
+        if (ptr == nullptr) return IIAN_ERR_NOSYMBOL;
+        __atomic_store_n(&g_noalloc_ptr[dev], ptr, __ATOMIC_RELEASE);
+        base = ptr;
     }
-    int * counters = reinterpret_cast<int *>(g_noalloc_ptr[dev]);       // an int region of its own, zero at rest
-    float * part_o = g_noalloc_ptr[dev] + kNoAllocCounters;
+    int * counters = reinterpret_cast<int *>(base);                     // an int region of its own, zero at rest
+    float * part_o = base + kNoAllocCounters;
     float * part_lse = part_o + (size_t) N * nh * n_split * hd;
     return iian_attention_mma(q, k_cache, v_cache, out, part_o, part_lse, counters, cu_q, ctx_len, block_table, max_blocks,
                               N, S, max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, n_split, small_tiles,

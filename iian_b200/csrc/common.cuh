@@ -16,6 +16,7 @@ enum {
     IIAN_ERR_SHAPE = 2,      // a size the kernel refuses
     IIAN_ERR_ALIGN = 3,      // a pointer or stride is not aligned as required
     IIAN_ERR_LIMIT = 4,      // beyond a stated maximum
+    IIAN_ERR_NOSYMBOL = 5,   // the address of a device array inside the library could not be resolved
 };
 
 static inline int iian_launch_status() {

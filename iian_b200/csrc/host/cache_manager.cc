@@ -75,7 +75,7 @@ int CacheManager::find_cached_prefix(const int32_t * tokens, int n_tokens, const
                                      std::vector<std::vector<int>> & tables) {
     const int G = num_groups();
     tables.assign(G, {});
-    if (!prefix_caching_ || n_tokens < 2) return 0;
+    if (!prefix_caching_ || n_tokens < 2 || G == 0) return 0;      // without page groups there is nothing to share
     const int bs = block_size_;
     const int max_blocks = std::min((n_tokens - 1) / bs, n_hashes);
     std::vector<std::vector<int>> found(G);

@@ -25,7 +25,13 @@ IIAN_API int iian_prefetch_l2(const void * ptr, long long bytes, cudaStream_t st
     const long long lines = (bytes + 127) / 128;
     const int threads = 256;
     long long blocks = (lines + threads - 1) / threads;
-    if (blocks > 148 * 4) blocks = 148 * 4;
+    static int sms = 0;           // four blocks per SM are enough to keep the requests flowing
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms = n;
+    }
+    if (blocks > (long long) sms * 4) blocks = (long long) sms * 4;
     prefetch_l2_kernel<<<(unsigned) blocks, threads, 0, stream>>>((const char *) ptr, (size_t) bytes);
     return iian_launch_status();
 }

@@ -69,6 +69,9 @@ class Engine:
             model = Model.from_folder(model, self.cfg.dtype, device)
         self.model = model
         c = self.cfg
+        if c.max_model_len > model.max_position:
+            raise ValueError(f"max_model_len {c.max_model_len} is beyond the model's {model.max_position} positions "
+                             f"(max_position_embeddings)")
         self.max_model_len = c.max_model_len or min(model.max_position, 8192)
         c.sched.max_model_len = self.max_model_len
         bs = c.block_size

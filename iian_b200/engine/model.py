@@ -143,13 +143,20 @@ class Model:
                     raise ValueError(f"layer {call.layer} reads cache {call.cache}, whose owner stores something else")
         return needs
 
+    def all_parts(self) -> List[object]:
+        out = [self.embedding, self.final_norm, self.head]
+        for blk in self.blocks:
+            out.extend(part for _, part in blk.parts())
+        return out
+
+    def graph_safe(self) -> bool:
+        """Whether every part allows its forward pass to be replayed from a CUDA graph."""
+        return all(getattr(part, "graph_safe", True) for part in self.all_parts())
+
     def kernel_libraries(self) -> List[str]:
         libs = set()
-        for part in [self.embedding, self.final_norm, self.head]:
+        for part in self.all_parts():
             libs.update(part.kernel_libraries())
-        for blk in self.blocks:
-            for _, part in blk.parts():
-                libs.update(part.kernel_libraries())
         if self.dtype == torch.bfloat16:
             from ..csrc import build
             libs.update(build.BF16_SOURCES)

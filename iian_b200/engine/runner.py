@@ -25,7 +25,7 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager, RequestCache
 from ..cache.storage import CacheStorage, plan_groups
-from ..parts.base import KVNeed, StateNeed
+from ..parts.base import KVNeed, StateNeed, prefix_reusable
 from .model import Model
 
 
@@ -113,7 +113,8 @@ class ModelRunner:
                  enable_prefix_caching: bool = False, window_capacity_tokens: Optional[int] = None,
                  cuda_graphs: bool = False, max_model_len: Optional[int] = None):
         self.model = model
-        self.cuda_graphs = cuda_graphs and model.device.type == "cuda"
+        # decode steps are replayed from graphs only if every part of the model can be recorded
+        self.cuda_graphs = cuda_graphs and model.device.type == "cuda" and model.graph_safe()
         self.weight_prefetch = os.environ.get("IIAN_WEIGHT_PREFETCH", "1") not in ("0", "false", "off")
         self.max_model_len = max_model_len or capacity_tokens
         self._graphs: Dict[Tuple[int, int], "_GraphSlot"] = {}
@@ -124,7 +125,10 @@ class ModelRunner:
         needs = model.cache_needs()
         groups, kinds = plan_groups(needs, capacity_tokens, block_size, window_capacity_tokens)
         has_state = any(isinstance(n, StateNeed) for n in needs.values())
-        self.manager = CacheManager(groups, block_size, enable_prefix_caching, num_state_slots=max_num_seqs)
+        # a request may start behind another request's prefix only if every cache of the model can be shared
+        # page by page (and there is at least one page group to share)
+        self.prefix_caching = bool(enable_prefix_caching and groups and all(prefix_reusable(n) for n in needs.values()))
+        self.manager = CacheManager(groups, block_size, self.prefix_caching, num_state_slots=max_num_seqs)
         self.storage = CacheStorage(needs, groups, kinds, block_size, max_num_seqs if has_state else 0,
                                     model.dtype, self.device)
         self.workspace = Workspace(self.device)
@@ -398,7 +402,7 @@ class ModelRunner:
         key = (bucket, ctx_bucket)
         slot = self._graphs.get(key)
         if slot is None:
-            slot = self._capture(bucket, ctx_bucket, entries)
+            slot = self._capture(bucket, ctx_bucket)
             self._graphs[key] = slot
         ctx = self.build_decode_context(entries, slot)
         slot.graph.replay()
@@ -406,7 +410,7 @@ class ModelRunner:
         self.last_upload_bytes = ctx.upload_bytes
         return slot.logits[:n]
 
-    def _capture(self, num_seqs: int, ctx_bucket: int, entries: Sequence[StepEntry]) -> "_GraphSlot":
+    def _capture(self, num_seqs: int, ctx_bucket: int) -> "_GraphSlot":
         mgr = self.manager
         n_groups = len(mgr.groups)
         max_blocks = max(1, mgr.blocks_for(max(self.max_model_len, ctx_bucket)))
@@ -420,9 +424,12 @@ class ModelRunner:
         kv_heads = [n.num_kv_heads for n in self.model.cache_needs().values() if isinstance(n, KVNeed)]
         k = ops.kernels()
         slot.n_split = k.attention_splits(num_seqs, min(kv_heads), ctx_bucket) if kv_heads and hasattr(k, "attention_splits") else 1
-        # run once eagerly (loads kernels, sizes every buffer, records the order in which weights are
-        # streamed), then capture the same launches -- with a side stream that prefetches the next weights
-        ctx = self.build_context(entries, slot)
+        # Warm up eagerly on a batch of padding sequences only (it loads the kernels, sizes every buffer and
+        # records the order in which weights are streamed, but stores nothing: padding tokens have cache cell
+        # -1 and state slot -1), then capture the same launches -- with a side stream that prefetches the next
+        # weights.  The step that asked for this graph then runs exactly once, as the first replay: a mixer
+        # with state of its own must not see a step twice.
+        ctx = self.build_context([], slot)
         prefetch = self.weight_prefetch and hasattr(k, "weight_log")
         if prefetch:
             k.weight_log = []

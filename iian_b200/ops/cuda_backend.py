@@ -27,7 +27,8 @@ class KernelError(RuntimeError):
 
 
 _ERRS = {1: "element types not supported by this kernel", 2: "a size this kernel refuses",
-         3: "a pointer or stride is not aligned as the kernel requires", 4: "beyond the kernel's stated maximum"}
+         3: "a pointer or stride is not aligned as the kernel requires", 4: "beyond the kernel's stated maximum",
+         5: "the address of a device array inside the library could not be resolved"}
 
 
 LAUNCHES = [0]        # kernel launches issued by this module (a split attention counts its merge kernel too)
@@ -570,7 +571,23 @@ class CudaKernels:
                                          scale=scale, window=window)
 
     DECODE_STAGES = int(os.environ.get("IIAN_DECODE_STAGES", "2"))     # shared-memory tiles per CTA of the decode kernel
-    DECODE_SLOTS = 148 * 2                                             # CTAs of the decode kernel one launch should not exceed
+    _sm_count = {}
+
+    @classmethod
+    def sm_count(cls, device=None) -> int:
+        """Streaming multiprocessors of ``device`` (the current one by default), asked from the driver once."""
+        idx = torch.cuda.current_device() if device is None else torch.device(device).index
+        if idx is None:
+            idx = torch.cuda.current_device()
+        n = cls._sm_count.get(idx)
+        if n is None:
+            n = cls._sm_count[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+        return n
+
+    @property
+    def DECODE_SLOTS(self) -> int:
+        """CTAs of the decode kernel one launch should not exceed: two per SM."""
+        return 2 * self.sm_count()
     _stages_set = None
 
     def set_decode_stages(self, stages: int) -> None:

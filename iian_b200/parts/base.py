@@ -64,10 +64,20 @@ class KVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A fixed-size state per request: one tensor of ``shape`` and ``dtype`` per slot."""
+    """A fixed-size state per request: one tensor of ``shape`` and ``dtype`` per slot.
+
+    The state after token t depends on every token before it and only its latest value is kept, so a
+    request cannot start behind a prefix that another request computed: a model with such a need runs
+    with prefix reuse switched off (``prefix_reusable``)."""
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+def prefix_reusable(need) -> bool:
+    """Whether a request may skip tokens whose cache entries another request left behind.  Keys and values
+    per token can be shared page by page; a fixed-size state cannot (it would need a snapshot per page)."""
+    return isinstance(need, KVNeed)
 
 
 class Part:
@@ -85,6 +95,13 @@ class Part:
     def kernel_libraries(self) -> Tuple[str, ...]:
         """Names of the CUDA libraries this part launches (compiled together before the first step)."""
         return ()
+
+    # Whether ``forward`` may be recorded into a CUDA graph and replayed for later steps: it must read the
+    # step's integers from the context's device tensors only (never from the host lists ``h_*``, whose values
+    # a recording would freeze), launch the same work whatever those integers are, and leave padding rows
+    # (sequence -1, cache cell -1, state slot -1) without effect.  A model with a part that says False runs
+    # its decode steps eagerly.
+    graph_safe = True
 
 
 @dataclass

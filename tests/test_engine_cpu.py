@@ -125,3 +125,42 @@ def test_a_request_that_cannot_fit_is_failed_not_hung(setup):
         assert a.is_finished and b.is_finished
         assert {a.finish_reason, b.finish_reason} <= {FinishReason.LENGTH, FinishReason.ERROR}
         assert FinishReason.LENGTH in {a.finish_reason, b.finish_reason}     # one after the other they both fit
+
+
+def test_max_model_len_beyond_the_models_positions_is_refused(setup):
+    model, _, _ = setup
+    with ops.use_kernels(FakeKernels()):
+        with pytest.raises(ValueError, match="positions"):
+            engine(model, kv_cache_tokens=1024, max_model_len=TINY["B"]["max_position_embeddings"] + 1)
+
+
+@pytest.mark.parametrize("layout", ["mixed", "ema_only"])
+def test_a_model_with_state_runs_without_prefix_reuse(tmp_path, layout):
+    """A mixer with a fixed-size state of its own (tests/toy_model.py): the engine is asked for prefix reuse
+    and switches it off, because a request that started behind a cached prefix would lack the state those
+    tokens build; with so few pages that requests are preempted, the tokens still equal the plain model's.
+    The layout without attention has no page group at all."""
+    from toy_model import CFG, CFG_EMA_ONLY, plain_toy_greedy, register_toy, unregister_toy, write_toy
+    cfg = CFG if layout == "mixed" else CFG_EMA_ONLY
+    register_toy()
+    try:
+        d = write_toy(str(tmp_path), cfg)
+        v = cfg["vocab_size"]
+        shared = random_tokens(v, 24, 5)
+        prompts = [shared + random_tokens(v, n, 20 + i) for i, n in enumerate([3, 9, 17])]
+        want = [plain_toy_greedy(d, p, 6, cfg)[0] for p in prompts]
+        with ops.use_kernels(FakeKernels()):
+            model = Model.from_folder(d, "float32", "cpu")
+            eng = engine(model, kv_cache_tokens=64, max_model_len=64, budget=16, seqs=3, enable_prefix_caching=True)
+            assert not eng.runner.prefix_caching
+            assert len(eng.cache.groups) == (1 if layout == "mixed" else 0)
+            for _ in range(2):
+                assert eng.generate(prompts, max_tokens=6, temperature=0.0) == want
+            st = eng.stats()
+        assert st.prefix_cache_hits == 0
+        if layout == "mixed":
+            assert st.preemptions >= 1
+        eng.cache.check_invariants()
+        assert eng.cache.slots.num_free == eng.cache.slots.num_slots
+    finally:
+        unregister_toy()

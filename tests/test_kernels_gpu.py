@@ -147,8 +147,14 @@ def attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=0, sta
     if standout:        # one far key among hundreds decides the output of the last query
         for s in range(S):
             far = min(3, ctx_lens[s] - 1) if not window else max(0, ctx_lens[s] - window)      # window: the oldest key still visible
+            if standout == "outside":       # ... or would decide it, if a window one key too long let it in
+                if not window or ctx_lens[s] - window - 1 < 0:
+                    continue
+                far = ctx_lens[s] - window - 1
             qs[s][-1] *= 4.0
             ks[s][far] = qs[s][-1][::nh // nkv][:nkv] * 1.0
+            if standout == "outside":
+                vs[s][far] = 25.0           # seen by mistake, it would move the output far beyond any tolerance
     ks = [k.to(dtype).float() for k in ks]
     vs = [v.to(dtype).float() for v in vs]
     qs = [q.to(dtype).float() for q in qs]
@@ -196,9 +202,11 @@ ATT_CASES = [
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("case", ATT_CASES)
-@pytest.mark.parametrize("standout", [False, True])
+@pytest.mark.parametrize("standout", [False, True, "outside"])
 def test_paged_attention_generic(dtype, case, standout):
     nh, nkv, hd, ps, ctx_lens, q_lens, window = case
+    if standout == "outside" and not window:
+        pytest.skip("no window")
     q, kc, vc, m, want, scale = attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=3, standout=standout)
     out = torch.empty(q.shape[0], nh * hd, dtype=dtype).cuda()
     K().paged_attention_generic(q, kc, vc, out, m, num_heads=nh, num_kv_heads=nkv, head_dim=hd, scale=scale, window=window)
@@ -518,11 +526,13 @@ MMA_CASES = [
 
 
 @pytest.mark.parametrize("case", MMA_CASES)
-@pytest.mark.parametrize("standout", [False, True])
+@pytest.mark.parametrize("standout", [False, True, "outside"])
 @pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles", "cluster2", "cluster4", "cluster8", "split4_scratch", "tc"])
 def test_paged_attention_mma(case, standout, mode):
     nh, nkv, hd, ps, ctx_lens, q_lens, window = case
     dtype = torch.bfloat16
+    if standout == "outside" and not window:
+        pytest.skip("no window")
     q, kc, vc, m, want, scale = attention_case(dtype, nh, nkv, hd, ps, ctx_lens, q_lens, window, seed=5, standout=standout)
     out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=dtype).cuda()
     kw = {}

@@ -155,6 +155,63 @@ def test_random_weights_mode(tmp_path):
         f.close()
 
 
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The generator is counter-based: an element depends on (seed, tensor name, index) only -- not on the slab
+    it was drawn in, not on other tensors -- and is written out here a second time with Python integers."""
+    from iian_b200.weights import random_init as ri
+    cpu = torch.device("cpu")
+    key = ri.tensor_key(7, "model.layers.0.mlp.up_proj.weight")
+    whole = ri.standard_normal(key, 0, 5000, cpu)
+    assert torch.equal(whole[1234:1300], ri.standard_normal(key, 1234, 66, cpu))
+    assert not torch.equal(whole[:64], ri.standard_normal(ri.tensor_key(7, "model.layers.1.mlp.up_proj.weight"), 0, 64, cpu))
+    assert not torch.equal(whole[:64], ri.standard_normal(ri.tensor_key(8, "model.layers.0.mlp.up_proj.weight"), 0, 64, cpu))
+    # the same numbers from Python integers (SplitMix64 finaliser, FNV-1a of the name)
+    m = (1 << 64) - 1
+    def mix(x):
+        x = (x + 0x9E3779B97F4A7C15) & m
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & m
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & m
+        return x ^ (x >> 31)
+    h = 0xCBF29CE484222325
+    for b in b"model.layers.0.mlp.up_proj.weight":
+        h = ((h ^ b) * 0x100000001B3) & m
+    assert key == mix(7) ^ h
+    knots = torch.special.ndtri((torch.arange(65537, dtype=torch.float64) + 0.5) / 65537.0).float()
+    for i in (0, 1, 77, 4999):
+        bits = mix(((i * 0xD1B54A32D192ED03) & m) ^ key)
+        u = bits >> 32
+        lo, hi = knots[u >> 16], knots[(u >> 16) + 1]
+        want = lo + (hi - lo) * torch.tensor((u & 0xFFFF) / 65536.0, dtype=torch.float32)
+        assert whole[i].item() == want.item()
+        assert ri.uniform(key, i, 1, cpu).item() == (bits >> 40) / float(1 << 24)
+    # and they look normal: mean, variance, fourth moment, tails
+    x = ri.standard_normal(key, 0, 1 << 20, cpu).double()
+    assert abs(x.mean().item()) < 4e-3 and abs(x.var().item() - 1) < 6e-3 and abs((x ** 4).mean().item() - 3) < 0.05
+    assert 0.0024 < (x.abs() > 3).double().mean().item() < 0.0030 and x.abs().max().item() < 4.4
+    u = ri.uniform(key, 0, 1 << 20, cpu).double()
+    assert abs(u.mean().item() - 0.5) < 2e-3 and abs(u.var().item() - 1 / 12) < 1e-3 and u.min() >= 0 and u.max() < 1
+
+
+@pytest.mark.gpu
+def test_random_values_are_the_same_bits_on_cpu_and_gpu(tmp_path):
+    """What lets a plain implementation on the CPU rebuild the model a GPU run drew on the device."""
+    from iian_b200.weights import random_init as ri
+    from iian_b200.weights.loader import TensorSpec
+    for name, spec in (("a.weight", TensorSpec((513, 1031))), ("b.norm", TensorSpec((4099,), init="ones_jitter"))):
+        c = ri.draw(name, spec, 11, torch.device("cpu"), 0.02, 0.1)
+        g = ri.draw(name, spec, 11, torch.device("cuda:0"), 0.02, 0.1)
+        assert torch.equal(c, g.cpu())
+    big = TensorSpec(((1 << 24) + 77,))                     # more than one slab
+    c = ri.draw("big", big, 3, torch.device("cpu"), 0.02, 0.0)
+    g = ri.draw("big", big, 3, torch.device("cuda:0"), 0.02, 0.0)
+    assert torch.equal(c, g.cpu())
+    from iian_b200.weights.random_init import write_model_folder
+    d1 = write_model_folder(str(tmp_path / "c"), ARCH, tiny_config("B"), seed=5)
+    d2 = write_model_folder(str(tmp_path / "g"), ARCH, tiny_config("B"), seed=5, device="cuda:0")
+    with open(os.path.join(d1, "model.safetensors"), "rb") as f1, open(os.path.join(d2, "model.safetensors"), "rb") as f2:
+        assert f1.read() == f2.read()
+
+
 def test_sharded_folder(tmp_path):
     d = write_tiny(tmp_path, "A")
     f = SafetensorsFile(os.path.join(d, "model.safetensors"))
