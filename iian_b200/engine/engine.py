@@ -108,6 +108,7 @@ class Engine:
         self._new: List[Request] = []
         self._aborts: List[int] = []
         self._thread: Optional[threading.Thread] = None
+        self.logits_hook = None       # optional callable(requests, logits [len(requests), vocab]) run before sampling
         self._quit = False
         self._wake = threading.Condition(self._lock)
         if c.warmup and model.device.type == "cuda":
@@ -193,6 +194,8 @@ class Engine:
         self.scheduler.update_after_step(so)
         self._stats.prompt_tokens += n_prompt_done
         if sampled:
+            if self.logits_hook is not None:
+                self.logits_hook(sampled, logits)
             self._process_outputs(sampled, logits)
         return True
 

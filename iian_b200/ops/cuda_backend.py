@@ -32,11 +32,14 @@ _ERRS = {1: "element types not supported by this kernel", 2: "a size this kernel
 
 
 LAUNCHES = [0]        # kernel launches issued by this module (a split attention counts its merge kernel too)
+LAUNCHES_BY_ENTRY = {}     # the same by entry point ("attention_tc", "gemm_skinny_fused", ...; "library_gemm" for cuBLAS):
+                           # tests read it to see which kernel a step was served by (a replayed graph counts once, at capture)
 
 
 def _check(code: int, what: str) -> None:
     if code == 0:
         LAUNCHES[0] += 1
+        LAUNCHES_BY_ENTRY[what] = LAUNCHES_BY_ENTRY.get(what, 0) + 1
         return
     if code >= 1000:
         raise KernelError(f"{what}: CUDA launch failed with error {code - 1000}")
@@ -320,10 +323,12 @@ class CudaKernels:
         """cuBLAS through torch.mm, for large bfloat16 products (as the reference does for large batches)."""
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
+            LAUNCHES_BY_ENTRY["library_gemm"] = LAUNCHES_BY_ENTRY.get("library_gemm", 0) + 1
             return True
         if out.dtype == torch.float32 and self._library_f32_out:
             try:
                 torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+                LAUNCHES_BY_ENTRY["library_gemm"] = LAUNCHES_BY_ENTRY.get("library_gemm", 0) + 1
                 return True
             except (TypeError, RuntimeError):
                 type(self)._library_f32_out = False

@@ -10,9 +10,12 @@ import torch
 
 import plain_qwen3 as plain
 
-# Three tiny Qwen3 configurations that differ in every size and option: layers, width (one is no power
-# of two), heads and groups, head size (explicit, != hidden/heads), feed-forward width, vocabulary
-# (two are odd), rope base, norm eps, tied or not, page size, and a sliding window on some layers.
+# Tiny Qwen3 configurations that differ in every size and option: layers, width (some are no power of two),
+# heads and groups, head size (explicit, != hidden/heads), feed-forward width, vocabulary (most are odd),
+# rope base, norm eps, tied or not, page size, and a sliding window on some layers.  A, B and C have head
+# sizes only the general kernels take; D (head size 128), E and F (head size 64, eight query heads on one
+# KV head / one each) are served in bfloat16 by the kernels that serve the large shapes: tcgen05 prefill
+# attention, mma.sync attention, the fused decode attention with its cluster merge, the 16-lane rotary form.
 TINY = {
     "A": dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=10000.0,
@@ -24,9 +27,20 @@ TINY = {
               num_key_value_heads=3, head_dim=48, rms_norm_eps=3e-6, rope_theta=500000.0,
               max_position_embeddings=512, tie_word_embeddings=False,
               use_sliding_window=True, sliding_window=20, max_window_layers=1),
+    "D": dict(vocab_size=331, hidden_size=256, intermediate_size=384, num_hidden_layers=3, num_attention_heads=8,
+              num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
+              max_position_embeddings=512, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=40, max_window_layers=2),
+    "E": dict(vocab_size=257, hidden_size=192, intermediate_size=320, num_hidden_layers=3, num_attention_heads=8,
+              num_key_value_heads=1, head_dim=64, rms_norm_eps=2e-6, rope_theta=10000.0,
+              max_position_embeddings=384, tie_word_embeddings=True,
+              use_sliding_window=True, sliding_window=48, max_window_layers=1),
+    "F": dict(vocab_size=199, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=4, head_dim=64, rms_norm_eps=1e-5, rope_theta=50000.0,
+              max_position_embeddings=256, tie_word_embeddings=False),
 }
-BLOCK_SIZE = {"A": 16, "B": 8, "C": 16}
-SEED = {"A": 0, "B": 2, "C": 5}
+BLOCK_SIZE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 8, "F": 32}
+SEED = {"A": 0, "B": 2, "C": 5, "D": 6, "E": 7, "F": 8}
 
 
 def tiny_config(name: str):

@@ -22,12 +22,15 @@ import torch
 
 
 # ---- files ---------------------------------------------------------------------------------------
-def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
-    """Every tensor of a safetensors file as float64 (integers as int64)."""
+def read_safetensors(path: str, keep32: bool = False) -> Dict[str, torch.Tensor]:
+    """Every tensor of a safetensors file as float64 (integers as int64).  ``keep32``: tensors stored in 16 or 32
+    bits stay float32 (the same values in half the memory; for models of several GB)."""
     with open(path, "rb") as f:
         (hlen,) = struct.unpack("<Q", f.read(8))
         header = json.loads(f.read(hlen).decode("utf-8"))
-        data = f.read()
+        base = 8 + hlen
+    data = np.memmap(path, dtype=np.uint8, mode="r", offset=base) if os.path.getsize(path) > base else np.zeros(0, np.uint8)
+    wide = (lambda t: t) if keep32 else (lambda t: t.double())
     out = {}
     for name, info in header.items():
         if name == "__metadata__":
@@ -37,12 +40,12 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
         shape = info["shape"]
         tag = info["dtype"]
         if tag == "F32":
-            t = torch.from_numpy(np.frombuffer(raw, dtype="<f4").copy()).double()
+            t = wide(torch.from_numpy(np.frombuffer(raw, dtype="<f4").copy()))
         elif tag == "F16":
-            t = torch.from_numpy(np.frombuffer(raw, dtype="<f2").copy()).double()
+            t = wide(torch.from_numpy(np.frombuffer(raw, dtype="<f2").copy()).float())
         elif tag == "BF16":
             u = np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16
-            t = torch.from_numpy(u.view(np.float32).copy()).double()
+            t = wide(torch.from_numpy(u.view(np.float32).copy()))
         elif tag == "F64":
             t = torch.from_numpy(np.frombuffer(raw, dtype="<f8").copy())
         elif tag in ("I32", "I64"):
@@ -53,10 +56,27 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
     return out
 
 
-def load_folder(model_dir: str):
+def load_folder(model_dir: str, keep32: bool = False):
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
-    return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"))
+    return cfg, read_safetensors(os.path.join(model_dir, "model.safetensors"), keep32)
+
+
+class _CastOnUse:
+    """The weights by name, widened to the computing dtype each time one is used (nothing is kept)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], dtype):
+        self.w, self.dtype = w, dtype
+
+    def __getitem__(self, k):
+        v = self.w[k]
+        return v.to(self.dtype) if v.is_floating_point() else v
+
+    def get(self, k, default=None):
+        return self[k] if k in self.w else default
+
+    def __contains__(self, k):
+        return k in self.w
 
 
 # ---- parts ---------------------------------------------------------------------------------------
@@ -135,7 +155,7 @@ def layer_windows(cfg: dict) -> List[Optional[int]]:
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], dtype=torch.float64,
             return_hidden: bool = False) -> torch.Tensor:
     """Logits [T, vocab] at every position of one sequence (src/iian/arch/qwen3.cpp:61-104)."""
-    W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
+    W = _CastOnUse(w, dtype)
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
@@ -144,7 +164,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], dtype=
     T = len(tokens)
     pos = torch.arange(T)
     windows = layer_windows(cfg)
-    x = embedding(W["model.embed_tokens.weight"], tokens)
+    x = embedding(w["model.embed_tokens.weight"], tokens).to(dtype)
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
         h = rms_norm(x, W[p + "input_layernorm.weight"], eps)                         # qwen3.cpp:77
@@ -173,8 +193,13 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], dtype=
     xn = rms_norm(x, W["model.norm.weight"], eps)                                     # qwen3.cpp:103
     if return_hidden:
         return xn
-    w_out = W["lm_head.weight"] if "lm_head.weight" in W else W["model.embed_tokens.weight"]   # qwen3.cpp:26-27
-    return xn @ w_out.T
+    return head(w, xn, dtype)
+
+
+def head(w: Dict[str, torch.Tensor], xn: torch.Tensor, dtype=torch.float64) -> torch.Tensor:
+    """Logits of normalised rows: the output matrix if the file has one, else the embedding (qwen3.cpp:26-27, 103)."""
+    w_out = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
+    return xn.to(dtype) @ w_out.to(dtype).T
 
 
 # ---- sampling ------------------------------------------------------------------------------------

@@ -70,11 +70,12 @@ def check(folders, plains, name, dtype, reqs, steps, max_tokens):
     return got
 
 
-LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 7, 24, 61, 100, 45], "C": [3, 50, 129, 64, 90]}
+LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 7, 24, 61, 100, 45], "C": [3, 50, 129, 64, 90],
+           "D": [5, 130, 64, 200, 33], "E": [1, 70, 129, 50, 90], "F": [3, 40, 100, 17, 65]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", sorted(TINY))
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cutting_does_not_change_logits(folders, plains, name, dtype, mode):
     reqs = requests_for(name, LENGTHS[name], 11)
@@ -82,6 +83,41 @@ def test_cutting_does_not_change_logits(folders, plains, name, dtype, mode):
     builder = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions}.get(mode)
     steps = builder(reqs) if builder else trace_mixed(reqs, max_tokens, seed=3)
     check(folders, plains, name, dtype, reqs, steps, max_tokens)
+
+
+# which entry points of the kernel layer must have served a bfloat16 model with heads of 128 (D) or 64 (E, F),
+# by the way its work was cut (ops.cuda_backend.LAUNCHES_BY_ENTRY); the general attention kernel must not appear
+SERVED_BY = {
+    ("D", "whole"): {"attention_tc", "gemm_tcgen05"},                    # long portions: tcgen05 attention and products
+    ("D", "tail"): {"attention_tc", "attention_decode_fused", "gemm_skinny_fused"},
+    ("D", "portions"): {"attention_tc", "attention_mma"},               # portions under 16 tokens go to mma.sync
+    ("D", "mixed"): {"attention_decode_fused", "gemm_skinny_fused"},
+    ("E", "whole"): {"attention_mma", "gemm_tcgen05"},
+    ("E", "tail"): {"attention_mma", "attention_decode_fused", "gemm_skinny_fused"},
+    ("F", "mixed"): {"attention_mma", "attention_decode_fused"},
+}
+
+
+@pytest.mark.parametrize("case", sorted(SERVED_BY))
+@pytest.mark.parametrize("min_tiles", [0, 300])
+def test_the_serving_kernels_run_inside_whole_model_checks(folders, plains, monkeypatch, case, min_tiles):
+    """The logits of D, E and F in bfloat16 come from the kernels that serve the large shapes, not from the general
+    ones -- with the own tcgen05 product from the first tile on (as the other tests run) and with the dispatch
+    rule's default threshold, under which these small products go to the library instead."""
+    from iian_b200.ops import cuda_backend
+    name, mode = case
+    monkeypatch.setattr(cuda_backend.CudaKernels, "TCGEN05_MIN_TILES", min_tiles)
+    cuda_backend.LAUNCHES_BY_ENTRY.clear()
+    reqs = requests_for(name, LENGTHS[name], 13)
+    builder = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions}.get(mode)
+    steps = builder(reqs) if builder else trace_mixed(reqs, 256, seed=6)
+    check(folders, plains, name, "bfloat16", reqs, steps, 256)
+    seen = set(cuda_backend.LAUNCHES_BY_ENTRY)
+    want = set(SERVED_BY[case])
+    if min_tiles:
+        want = {("library_gemm" if w == "gemm_tcgen05" else w) for w in want}
+    assert want <= seen, f"{name} {mode}: expected launches of {sorted(want - seen)}; saw {sorted(seen)}"
+    assert "paged_attention_generic" not in seen
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -100,13 +136,14 @@ def test_float32_rows_are_bit_identical_under_recutting(folders, plains, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_pages_are_used_again(folders, plains, dtype):
-    reqs = requests_for("B", [60, 60, 60, 60, 60, 60], 5)
-    check(folders, plains, "B", dtype, reqs, trace_mixed(reqs, 128, seed=1), 128)
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_pages_are_used_again(folders, plains, name, dtype):
+    reqs = requests_for(name, [60, 60, 60, 60, 60, 60], 5)
+    check(folders, plains, name, dtype, reqs, trace_mixed(reqs, 128, seed=1), 128)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D", "E"])
 def test_long_decoding(folders, plains, name, dtype):
     n = TINY[name]["max_position_embeddings"] - 6
     reqs = requests_for(name, [n], 31)
@@ -115,7 +152,7 @@ def test_long_decoding(folders, plains, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", sorted(TINY))
 def test_first_tokens(folders, plains, name, dtype):
     reqs = requests_for(name, [1, 2, 3], 41)
     check(folders, plains, name, dtype, reqs, trace_tail(reqs, tail=8), 256)

@@ -61,11 +61,10 @@ class ToyEma(Mixer):
         place = idx - cu[seq0]                                              # the token's place in its portion
         same = (seq[:, None] == seq[None, :]) & (idx[None, :] <= idx[:, None]) & valid_t[:, None]
         power = (idx[:, None] - idx[None, :]).clamp(min=0).to(torch.float32)
-        mix = torch.where(same, torch.pow(torch.tensor(self.decay, device=dev), power), torch.zeros((), device=dev))
+        mix = torch.pow(self.decay, power) * same.to(torch.float32)
         before = cache.state[slot_t.clamp(min=0)]                           # [N, H]
-        carry = torch.pow(torch.tensor(self.decay, device=dev), (place + 1).to(torch.float32))
-        states = mix @ x.float() + carry[:, None] * before
-        states = torch.where(valid_t[:, None], states, torch.zeros((), device=dev))
+        carry = torch.pow(self.decay, (place + 1).clamp(min=0).to(torch.float32))
+        states = (mix @ x.float() + carry[:, None] * before) * valid_t[:, None].to(torch.float32)
         out = (states @ self.w.T).to(x.dtype)
         # the state after each request's last token of this step goes back to its slot; written as an atomic
         # add of (new - old) so that padding sequences (which add zero to slot 0) need no branch
@@ -73,7 +72,7 @@ class ToyEma(Mixer):
         last = (cu[1:n_seq + 1] - 1).clamp(min=0)
         valid_s = slots >= 0
         old = cache.state[slots.clamp(min=0)]
-        delta = torch.where(valid_s[:, None], states[last] - old, torch.zeros((), device=dev))
+        delta = (states[last] - old) * valid_s[:, None].to(torch.float32)
         cache.state.index_put_((slots.clamp(min=0),), delta, accumulate=True)
         return out
 
