@@ -25,27 +25,20 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen3-8B shape
-SHAPE_8B = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
-                num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
-                max_position_embeddings=40960, tie_word_embeddings=False)
+from iian_b200.cli.workloads import SHAPES  # noqa: E402  (shapes by name; no CUDA is touched by the import)
+
+SHAPE_8B = SHAPES["8b"]     # BASELINE.json configs[2]
 CONTEXT_LEN = 8192          # the engine's max_model_len for the benchmark
 PROMPT_LEN = 1024           # decode starts from prompts of this many random tokens
 PREFILL_TOKENS = 2048
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
-def load_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.isfile(path):
-        try:
-            with open(path) as f:
-                p = json.load(f)
-            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
-                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"]))}, "measured"
-        except (KeyError, ValueError, OSError):
-            pass
-    return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0), "fallback"
+def reference_arm(args) -> int:
+    """``--impl reference``: the unmodified reference through its own command line, if it could be built here."""
+    print(json.dumps({"impl": "reference", "unavailable": "CocoRoF/iian is a C++/CMake program with no setup.py or "
+                      "pyproject.toml (pip: 'not installable'), reads GGUF checkpoints only and has no sm_100 build; "
+                      "there is nothing to install under baseline/_ref"}))
+    return 0
 
 
 class ClockSampler:
@@ -101,112 +94,59 @@ def main() -> int:
                     help="run fewer layers than the configuration has (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cuda-graphs", action="store_true")
-    ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points and the prefill")
+    ap.add_argument("--skip-points", action="store_true", help="the headline and the end-to-end figure only")
+    ap.add_argument("--skip-32b", action="store_true", help="leave out the Qwen3-32B shape")
+    ap.add_argument("--skip-serve", action="store_true", help="leave out the continuous-batching workload (Qwen3-0.6B shape)")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "CocoRoF/iian is a C++/CMake program with no setup.py or "
-                          "pyproject.toml (pip: 'not installable'), reads GGUF checkpoints only and has no sm_100 build; "
-                          "there is nothing to install under baseline/_ref"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     K, W = args.steps, max(3, args.warmup)
 
+    import gc
     import torch
     from iian_b200 import EngineConfig, SamplingParams, SchedulerConfig
     from iian_b200 import ops
-    from iian_b200.config.registry import get_architecture
+    from iian_b200.cli import workloads as wl
     from iian_b200.engine.engine import Engine
-    from iian_b200.engine.model import Model
     from iian_b200.engine.runner import StepEntry
-    from iian_b200.models.qwen3 import qwen3_config_from_dict
 
-    peaks, peak_kind = load_peaks()
+    peaks, peak_kind = wl.load_peaks(ROOT)
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    shape = dict(SHAPE_8B, num_hidden_layers=args.layers)
-    cfg = qwen3_config_from_dict(shape)
-    arch = get_architecture("Qwen3ForCausalLM")
     t_build = time.time()
-    model = Model.from_random(arch, cfg, seed=0, dtype="bfloat16", device=dev, norm_jitter=0.0)
+    model = wl.random_model("8b", "bfloat16", dev, seed=0, layers=args.layers)
+    cfg = model.config
+    acc = wl.Accounting(cfg)
     max_b = max(args.batch, 1 if args.skip_points else 64)
     per_req = PROMPT_LEN + W + K + 48
-    ecfg = EngineConfig(dtype="bfloat16", max_model_len=CONTEXT_LEN, kv_cache_tokens=max(CONTEXT_LEN, max_b * per_req),
+    longest_prefill = PREFILL_TOKENS if args.skip_points else max(PREFILL_TOKENS, 8192)
+    ecfg = EngineConfig(dtype="bfloat16", max_model_len=max(CONTEXT_LEN, longest_prefill + 64),
+                        kv_cache_tokens=max(CONTEXT_LEN, longest_prefill + 64, max_b * per_req),
                         block_size=16, enable_prefix_caching=False, warmup=True, cuda_graphs=not args.no_cuda_graphs,
                         sched=SchedulerConfig(max_num_seqs=max_b, max_num_batched_tokens=2048))
     engine = Engine(model, ecfg)
-    runner, mgr, kern = engine.runner, engine.runner.manager, ops.kernels()
+    runner, kern = engine.runner, ops.kernels()
     print(f"[bench] model and engine ready in {time.time() - t_build:.1f} s "
           f"({model.weight_bytes / 1e9:.2f} GB of weights, cache {runner.storage.bytes / 1e9:.2f} GB)", file=sys.stderr)
-
-    gen = torch.Generator().manual_seed(1234)
-    def rand_tokens(n):
-        return torch.randint(5, cfg.vocab_size - 5, (n,), generator=gen).tolist()
-
-    layer_w = cfg.hidden_size * (cfg.q_size + 2 * cfg.kv_size) + cfg.q_size * cfg.hidden_size \
-        + 3 * cfg.hidden_size * cfg.intermediate_size
-    head_w = cfg.vocab_size * cfg.hidden_size
-    weight_bytes_step = 2 * (cfg.num_hidden_layers * layer_w + head_w)
-    kv_bytes_token = cfg.num_hidden_layers * 2 * cfg.kv_size * 2
-
-    def prefill_requests(B):
-        caches = []
-        for _ in range(B):
-            rc = mgr.new_request()
-            mgr.allot_state(rc)
-            caches.append(rc)
-        prompts = [rand_tokens(PROMPT_LEN) for _ in range(B)]
-        per_step = max(1, 2048 // PROMPT_LEN)
-        for i in range(0, B, per_step):
-            ents = []
-            for rc, pr in zip(caches[i:i + per_step], prompts[i:i + per_step]):
-                assert mgr.allocate(rc, 0, PROMPT_LEN)
-                ents.append(StepEntry(rc, pr, 0, []))
-            runner.step(ents)
-        return caches
-
-    def decode_device_timed(B, warm, steps):
-        caches = prefill_requests(B)
-        out = torch.empty(B, dtype=torch.int32, device=dev)
-        toks = rand_tokens(B)
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        pos = PROMPT_LEN
-        launches0 = 0
-        for i in range(warm + steps):
-            if i == warm:
-                torch.cuda.synchronize()
-                launches0 = runner.launches
-                start.record()
-            ents = []
-            for rc, t in zip(caches, toks):
-                assert mgr.allocate(rc, pos, 1)
-                ents.append(StepEntry(rc, [t], pos, [0]))
-            logits = runner.step(ents)
-            kern.argmax(logits, out)
-            pos += 1
-        end.record()
-        torch.cuda.synchronize()
-        ms = start.elapsed_time(end) / steps
-        launches = runner.launches - launches0 + steps
-        for rc in caches:
-            mgr.free(rc)
-        ctx_avg = PROMPT_LEN + warm + (steps + 1) / 2
-        return ms, launches, ctx_avg
+    src = wl.TokenSource(cfg.vocab_size, 1234)
 
     # ---- timed: decode at the headline batch (device clock) -------------------------------------
     sampler = ClockSampler(0)
     sampler.start()
     B = args.batch
-    ms_step, launches, ctx_avg = decode_device_timed(B, W, K)
-    value = B / (ms_step * 1e-3)
-    bytes_step = weight_bytes_step + B * ctx_avg * kv_bytes_token
+    head = wl.measure_decode(runner, src, B, PROMPT_LEN, W, K)
+    ms_step, launches, ctx_avg = head["ms_per_step"], head["launches"], head["ctx_avg"]
+    value = head["tokens_per_s"]
+    bytes_step = acc.decode_bytes(B, ctx_avg)
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
 
     # ---- timed: the same through the Python entry point (host tokens in and out) -----------------
     sp = SamplingParams(temperature=0.0, max_tokens=W + K + 8, ignore_eos=True)
-    reqs = [engine.submit(rand_tokens(PROMPT_LEN), sp) for _ in range(B)]
+    reqs = [engine.submit(src.take(PROMPT_LEN), sp) for _ in range(B)]
     while any(r.n_output < W for r in reqs):
         engine.step()
     torch.cuda.synchronize()
@@ -223,36 +163,72 @@ def main() -> int:
         engine.abort(r.id)
     engine.step()
 
-    points, prefill = {}, None
+    points, prefill, check = {}, None, None
     if not args.skip_points:
         for b in (1, 64):
-            ms_b, _, _ = decode_device_timed(b, W, K)
-            points[f"decode_b{b}"] = b / (ms_b * 1e-3)
-        # ---- prefill of one 2,048-token prompt --------------------------------------------------
-        toks = rand_tokens(PREFILL_TOKENS)
-        times = []
-        for i in range(W + 5):
-            rc = mgr.new_request()
-            mgr.allot_state(rc)
-            assert mgr.allocate(rc, 0, PREFILL_TOKENS)
-            s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            s_ev.record()
-            runner.step([StepEntry(rc, toks, 0, [PREFILL_TOKENS - 1])])
-            e_ev.record()
-            torch.cuda.synchronize()
-            if i >= W:
-                times.append(s_ev.elapsed_time(e_ev))
-            mgr.free(rc)
-        p_ms = statistics.median(times)
-        T = PREFILL_TOKENS
-        flops = 2.0 * T * cfg.num_hidden_layers * layer_w + 2.0 * head_w \
-            + cfg.num_hidden_layers * 4.0 * cfg.q_size * T * (T + 1) / 2
-        prefill = {"value": T / (p_ms * 1e-3), "tokens": T, "ms": p_ms,
-                   "frac": flops / (p_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / (p_ms * 1e-3) / 1e12}
+            r = wl.measure_decode(runner, src, b, PROMPT_LEN, W, K)
+            points[f"decode_b{b}"] = r["tokens_per_s"]
+            points[f"decode_b{b}_hbm_frac"] = acc.decode_bytes(b, r["ctx_avg"]) / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+        # ---- prefill of one 2,048-token prompt (and of 512 and 8,192 tokens) ---------------------------
+        for T in (PREFILL_TOKENS, 512, 8192):
+            r = wl.measure_prefill(runner, src, T, warmup=W if T == PREFILL_TOKENS else 2, repeats=5 if T == PREFILL_TOKENS else 3)
+            flops = acc.prefill_flops(T)
+            if T == PREFILL_TOKENS:
+                prefill = {"value": r["tokens_per_s"], "tokens": T, "ms": r["ms"],
+                           "frac": flops / (r["ms"] * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / (r["ms"] * 1e-3) / 1e12}
+            else:
+                points[f"prefill_{T}"] = r["tokens_per_s"]
+                points[f"prefill_{T}_frac"] = flops / (r["ms"] * 1e-3) / (peaks["bf16_tflops"] * 1e12)
     sampler.stop()
     if hasattr(kern, "tcgen05_check"):
         kern.tcgen05_check(dev)          # a tcgen05 kernel that gave up on a barrier would have left garbage
+
+    if not args.skip_points:
+        # ---- untimed: the bfloat16 path against the true 32-bit path on a 2-layer cut of the same model ------
+        # (the generator is keyed by tensor name, so the cut has the full model's embedding, first layers and head)
+        del engine, runner, model
+        gc.collect()
+        torch.cuda.empty_cache()
+        toks = src.take(96)
+        rows = {}
+        for dt in ("float32", "bfloat16"):
+            m2 = wl.random_model("8b", dt, dev, seed=0, layers=2)
+            e2 = Engine(m2, EngineConfig(dtype=dt, max_model_len=256, kv_cache_tokens=256, enable_prefix_caching=False,
+                                         warmup=False, cuda_graphs=False, sched=SchedulerConfig(max_num_seqs=1)))
+            rc = e2.runner.manager.new_request()
+            e2.runner.manager.allot_state(rc)
+            assert e2.runner.manager.allocate(rc, 0, len(toks))
+            rows[dt] = e2.runner.step([StepEntry(rc, toks, 0, [len(toks) - 1])]).float().cpu()
+            del e2, m2
+            gc.collect()
+            torch.cuda.empty_cache()
+        check = {"layers": 2, "tokens": len(toks), "max_abs_err_bf16_vs_fp32": (rows["float32"] - rows["bfloat16"]).abs().max().item(),
+                 "logit_max_abs": rows["float32"].abs().max().item()}
+
+        # ---- the continuous-batching workload at the Qwen3-0.6B shape (scheduler, prefix reuse, preemption, graphs) ----
+        if not args.skip_serve:
+            res = wl.serving_workload("0.6b", 256, device=dev)
+            for k_ in ("total_tok_s", "gen_tok_s", "ttft_ms", "tpot_ms", "prefix_hit_rate", "preemptions", "kv_usage_peak",
+                       "wall_s", "errors", "alone_identical", "alone_agreeing_token_share"):
+                points[f"serve06b_{k_}"] = res[k_]
+            gc.collect()
+            torch.cuda.empty_cache()
+
+        # ---- the Qwen3-32B shape: decode 1 / 8 / 64 from 2,048-token prompts, prefill of 2,048 tokens ---------
+        if not args.skip_32b:
+            m32 = wl.random_model("32b", "bfloat16", dev, seed=0)
+            res = wl.decode_and_prefill_points(m32, (1, 8, 64), 2048, min(K, 32), W, (2048,), 4096, peaks,
+                                               cuda_graphs=not args.no_cuda_graphs)
+            for b, r in res["decode"].items():
+                points[f"q32b_decode_b{b}"] = r["tokens_per_s"]
+                points[f"q32b_decode_b{b}_hbm_frac"] = r["roofline_frac"]
+            for t, r in res["prefill"].items():
+                points[f"q32b_prefill_{t}"] = r["tokens_per_s"]
+                points[f"q32b_prefill_{t}_frac"] = r["frac"]
+            kern.tcgen05_check(dev)
+            del res, m32
+            gc.collect()
+            torch.cuda.empty_cache()
 
     line = {
         "metric": "decode tokens/s (Qwen3-8B shape, batch 8)" if B == 8 else f"decode tokens/s (Qwen3-8B shape, batch {B})",
@@ -273,6 +249,8 @@ def main() -> int:
     }
     if prefill is not None:
         line["prefill"] = prefill
+    if check is not None:
+        line["check"] = check
     print(json.dumps(line))
     return 0
 

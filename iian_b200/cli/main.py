@@ -132,29 +132,80 @@ def cmd_complete(argv: List[str]) -> int:
 
 
 def cmd_bench(argv: List[str]) -> int:
-    o = Options("iian bench", "Prompt and generation throughput: N concurrent requests with distinct random prompts "
-                              "(so the prefix cache cannot help); aggregate tokens/s, time to first token, time per token.")
-    o.positional("model", "model folder")
+    o = Options("iian bench", "Throughput.  With --concurrency (the reference's form): N concurrent requests with distinct "
+                              "random prompts through the scheduler; aggregate tokens/s, time to first token, time per token.  "
+                              "With --batch / --prefill-tokens: decode steps and whole-prompt steps timed on the device, with "
+                              "the achieved fraction of the HBM and tensor-core rooflines.  With --requests: continuous "
+                              "batching of many requests of random lengths, half behind a shared prefix.")
+    o.positional("model", "model folder (or leave out and name a --shape with random weights)", nargs="?")
     o.group("Benchmark")
+    o.add("--shape", "Random-weight model of a named shape instead of a folder: tinyA | tinyB | 0.6b | 8b | 32b", "NAME", "", str)
+    o.add("--layers", "With --shape: run this many layers of the shape (0 = all)", "N", 0, int)
     o.add("--concurrency", "Comma-separated concurrency levels", "LIST", "1,4,16", str)
     o.add("--prompt-tokens", "Prompt length per request", "N", 256, int)
-    o.add("--gen-tokens", "Tokens to generate per request", "N", 128, int)
+    o.add("--gen-tokens", "Tokens to generate per request (timed decode steps with --batch)", "N", 128, int)
+    o.add("--batch", "Comma-separated decode batches, timed on the device with their HBM roofline fraction", "LIST", "", str)
+    o.add("--prefill-tokens", "Comma-separated prompt lengths run as one step each, with their tensor-core roofline fraction", "LIST", "", str)
+    o.add("--requests", "Continuous batching of this many requests: prompts U[16, 4096], outputs U[16, 512], half sharing "
+                        "a 512-token prefix; reports tokens/s, prefix hit rate, preemptions", "N", 0, int)
     o.flag("--json", "Machine-readable output")
     _add_engine_flags(o)
     ns = o.parse(argv)
     from ..engine.engine import Engine
     from ..engine.model import Model
     from ..sampling.params import SamplingParams
+    from . import workloads
+    if not ns.model and not ns.shape:
+        print("iian bench: name a model folder or a --shape", file=sys.stderr)
+        return 1
     try:
-        model = Model.from_folder(ns.model, ns.dtype, f"cuda:{ns.device}")
+        if ns.shape:
+            model = workloads.random_model(ns.shape, ns.dtype, f"cuda:{ns.device}", layers=ns.layers or None)
+        else:
+            model = Model.from_folder(ns.model, ns.dtype, f"cuda:{ns.device}")
     except (ValueError, FileNotFoundError, KeyError, RuntimeError) as e:
         print(f"iian bench: {e}", file=sys.stderr)
         return 1
+    what = ns.shape or ns.model
+    ints = lambda text: [int(x) for x in text.split(",") if x.strip()]
+    if ns.requests > 0:
+        res = workloads.serving_workload(ns.shape or "model", ns.requests, kv_cache_tokens=ns.kv_cache_tokens,
+                                         max_num_seqs=ns.max_num_seqs if "max_num_seqs" in ns.given else 64,
+                                         max_num_batched_tokens=ns.max_num_batched_tokens if "max_num_batched_tokens" in ns.given else 2048,
+                                         model=model)
+        if ns.json:
+            print(json.dumps(res, indent=2))
+        else:
+            print(f"bench {what} | {res['requests']} requests | {res['prompt_tokens']} prompt + {res['generated_tokens']} generated tokens")
+            print(f"total {res['total_tok_s']:.0f} tok/s | generation {res['gen_tok_s']:.0f} tok/s | TTFT {res['ttft_ms']:.0f} ms | "
+                  f"TPOT {res['tpot_ms']:.1f} ms | prefix hit rate {res['prefix_hit_rate']:.2f} | preemptions {res['preemptions']} | "
+                  f"peak cache use {res['kv_usage_peak']:.2f} | wall {res['wall_s']:.1f} s")
+        return 0
+    if ns.batch or ns.prefill_tokens:
+        peaks, kind = workloads.load_peaks()
+        res = workloads.decode_and_prefill_points(model, ints(ns.batch), ns.prompt_tokens, ns.gen_tokens, 5, ints(ns.prefill_tokens),
+                                                  ns.max_model_len or 8192, peaks, cuda_graphs=not ns.no_cuda_graphs)
+        res.pop("engine")
+        if ns.json:
+            print(json.dumps({"peaks": dict(peaks, kind=kind), "decode": list(res["decode"].values()),
+                              "prefill": list(res["prefill"].values())}, indent=2))
+            return 0
+        print(f"bench {what} | prompt {ns.prompt_tokens} tok | {ns.gen_tokens} timed steps | peaks ({kind}): "
+              f"{peaks['hbm_gbs']:.0f} GB/s, {peaks['bf16_tflops']:.0f} TFLOP/s")
+        if res["decode"]:
+            print(f"{'batch':<8} {'tok/s':>12} {'ms/step':>10} {'GB/s':>10} {'of HBM peak':>12}")
+            for b, r in res["decode"].items():
+                print(f"{b:<8d} {r['tokens_per_s']:>12.1f} {r['ms_per_step']:>10.3f} {r['hbm_gbs']:>10.0f} {r['roofline_frac']:>12.3f}")
+        if res["prefill"]:
+            print(f"{'prefill':<8} {'tok/s':>12} {'ms':>10} {'TFLOP/s':>10} {'of bf16 peak':>12}")
+            for t, r in res["prefill"].items():
+                print(f"{t:<8d} {r['tokens_per_s']:>12.0f} {r['ms']:>10.2f} {r['tflops']:>10.0f} {r['frac']:>12.3f}")
+        return 0
     rows = []
     if not ns.json:
-        print(f"bench {ns.model} | prompt {ns.prompt_tokens} tok | gen {ns.gen_tokens} tok | dtype {ns.dtype}")
+        print(f"bench {what} | prompt {ns.prompt_tokens} tok | gen {ns.gen_tokens} tok | dtype {ns.dtype}")
         print(f"{'concurrency':<12} {'prompt tok/s':>14} {'gen tok/s':>14} {'total tok/s':>14} {'TTFT ms':>10} {'TPOT ms':>10} {'wall s':>10}")
-    for c in [int(x) for x in ns.concurrency.split(",") if x.strip()]:
+    for c in ints(ns.concurrency):
         cfg = engine_config_from_args(ns)
         cfg.sched.max_num_seqs = c                                       # src/iian/cli/cmd_bench.cpp:52-55
         if "max_model_len" not in ns.given:

@@ -254,7 +254,7 @@ def run_serving(engine, requests, check_alone: int = 0) -> dict:
         reqs.append(engine.submit(toks, SamplingParams(temperature=0.0, max_tokens=n_out, ignore_eos=True)))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    peak_usage, steps, mixed_steps = 0.0, 0, 0
+    peak_usage, steps = 0.0, 0
     while any(not r.is_finished for r in reqs):
         if not engine.step():
             break
@@ -277,7 +277,7 @@ def run_serving(engine, requests, check_alone: int = 0) -> dict:
     if check_alone:
         step = max(1, len(reqs) // check_alone)
         agree, total, full = 0, 0, 0
-        for i in range(0, len(reqs), step)[:check_alone] if False else list(range(0, len(reqs), step))[:check_alone]:
+        for i in list(range(0, len(reqs), step))[:check_alone]:
             toks, n_out, _ = requests[i]
             n_cmp = min(n_out, 32)
             r = engine.submit(toks, SamplingParams(temperature=0.0, max_tokens=n_cmp, ignore_eos=True))
