@@ -35,6 +35,9 @@ SOURCES = ["elementwise", "rope_kv", "attention_generic", "gemm_simt", "sampling
 BF16_SOURCES: List[str] = ["gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05", "attention_tc"]
 # extra link flags per source
 EXTRA_FLAGS: Dict[str, List[str]] = {}
+# extra compiler flags for every source, from the environment (e.g. "-DIIAN_SOMETHING=1" to build a variant of a
+# kernel for a measurement); they are part of the cache key, so variants live side by side
+ENV_FLAGS: List[str] = os.environ.get("IIAN_NVCC_FLAGS", "").split()
 
 
 class KernelBuildError(RuntimeError):
@@ -92,7 +95,7 @@ def _source_hash(name: str) -> str:
     if os.path.isfile(extra):
         with open(extra, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + EXTRA_FLAGS.get(name, [])).encode())
+    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + EXTRA_FLAGS.get(name, []) + ENV_FLAGS).encode())
     return h.hexdigest()[:16]
 
 
@@ -108,7 +111,7 @@ def _compile(name: str, verbose: bool = True) -> str:
     if os.path.isfile(out):
         return out
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [_nvcc()] + ARCH_FLAGS + BASE_FLAGS + EXTRA_FLAGS.get(name, []) + ["-I", HERE, "-o", tmp, src]
+    cmd = [_nvcc()] + ARCH_FLAGS + BASE_FLAGS + EXTRA_FLAGS.get(name, []) + ENV_FLAGS + ["-I", HERE, "-o", tmp, src]
     t0 = time.time()
     if verbose:
         print(f"[iian_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
@@ -131,9 +134,9 @@ def _compile(name: str, verbose: bool = True) -> str:
             os.remove(tmp)
         raise KernelBuildError(f"nvcc failed for {name}.cu (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
-    # drop stale builds of the same source
+    # drop stale builds of the same source (variants built with extra flags are kept beside the default)
     prefix = f"{name}."
-    for fn in os.listdir(os.path.dirname(out)):
+    for fn in ([] if ENV_FLAGS else os.listdir(os.path.dirname(out))):
         if fn.startswith(prefix) and fn.endswith(".so") and os.path.join(os.path.dirname(out), fn) != out:
             try:
                 os.remove(os.path.join(os.path.dirname(out), fn))

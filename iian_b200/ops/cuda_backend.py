@@ -592,7 +592,9 @@ class CudaKernels:
     @property
     def DECODE_SLOTS(self) -> int:
         """CTAs of the decode kernel one launch should not exceed: two per SM."""
-        return 2 * self.sm_count()
+        return self.DECODE_CTAS_PER_SM * self.sm_count()
+
+    DECODE_CTAS_PER_SM = int(os.environ.get("IIAN_DECODE_CTAS_PER_SM", "2"))
     _stages_set = None
 
     def set_decode_stages(self, stages: int) -> None:
@@ -604,20 +606,24 @@ class CudaKernels:
         type(self)._stages_set = stages
         type(self).DECODE_STAGES = stages
     CLUSTER_MERGE = os.environ.get("IIAN_ATTENTION_CLUSTER", "1") not in ("0", "false", "off")
-    MAX_SPLITS = 32
+    MAX_SPLITS = int(os.environ.get("IIAN_DECODE_MAX_SPLITS", "32"))
     _scratch = {}
     _scratch_keep = []
 
     def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
         """How many parts the keys of a decode step are cut into, so that few long sequences still fill
-        the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128, contexts of 1k and 8k, batches 1 to
+        the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128, contexts of 1k to 8k, batches 1 to
         64): the CTAs of one launch should number at most two per SM (more slow each other down, and a second
         wave repeats the whole chain of dependent loads), and a CTA should keep at least two key tiles.  Up to
-        8 parts merge inside a thread-block cluster, so 9 to 11 are rounded down to 8."""
+        8 parts merge inside a thread-block cluster, which saves three trips through L2 (write the parts, count
+        arrivals, read them back: 3.36 -> 3.23 ms per step at batch 1 and 1k context), so more than 8 parts are
+        only taken when each still gets four tiles or more (contexts beyond 4k); 9 to 11 are rounded down to 8."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
         n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 2), self.MAX_SPLITS))
-        return 8 if 8 < n < 12 else n
+        if n > 8 and (n < 12 or tiles < 64):
+            n = 8
+        return n
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
         t = self._scratch.get(device)
