@@ -34,10 +34,62 @@ PREFILL_TOKENS = 2048
 
 
 def reference_arm(args) -> int:
-    """``--impl reference``: the unmodified reference through its own command line, if it could be built here."""
-    print(json.dumps({"impl": "reference", "unavailable": "CocoRoF/iian is a C++/CMake program with no setup.py or "
-                      "pyproject.toml (pip: 'not installable'), reads GGUF checkpoints only and has no sm_100 build; "
-                      "there is nothing to install under baseline/_ref"}))
+    """``--impl reference``: the unmodified reference (built with CMake under ``baseline/_ref``) through its own
+    command line, ``iian bench <gguf> --concurrency B --prompt-tokens 1024 --gen-tokens N --json``, on the same shape
+    with the same random weights, written as a bfloat16 GGUF into a temporary folder.  Nothing of this repository's
+    engine is on that path.  ``value`` is its decode rate, B / TPOT (its own mean time between a request's tokens);
+    the same figure stands as ``e2e``, because the reference's bench is end to end by construction (token ids from
+    the host through its public Engine API, tokens and text back)."""
+    import shutil
+    import tempfile
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+    why = ra.available()
+    if why is None and args.gpus != 1:
+        why = "the reference's bench runs on one GPU"
+    if why is not None:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    K, W, B = args.steps, max(3, args.warmup), args.batch
+    shape = dict(SHAPE_8B, num_hidden_layers=args.layers)
+    work = tempfile.mkdtemp(prefix="iian_ref_")
+    try:
+        import torch
+        t0 = time.time()
+        path = os.path.join(work, "model.gguf")
+        nbytes = ra.write_gguf(path, shape, seed=0, device="cuda:0" if torch.cuda.is_available() else "cpu")
+        print(f"[bench] reference model written in {time.time() - t0:.1f} s ({nbytes / 1e9:.2f} GB)", file=sys.stderr)
+        torch.cuda.empty_cache()
+        sampler = ClockSampler(0)
+        sampler.start()
+        try:
+            row = ra.run_bench(path, B, PROMPT_LEN, W + K, extra=["--block-size", "16"])
+        finally:
+            sampler.stop()
+    except Exception as e:  # noqa: BLE001  (whatever went wrong, the arm says so in one line and the run goes on)
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference did not run: {str(e)[:300]}"}))
+        return 0
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    decode_tps = B * 1000.0 / row["tpot_ms"] if row.get("tpot_ms") else 0.0
+    line = {
+        "impl": "reference",
+        "metric": "decode tokens/s (Qwen3-8B shape, batch 8)" if B == 8 else f"decode tokens/s (Qwen3-8B shape, batch {B})",
+        "value": decode_tps, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": row.get("tpot_ms"),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) (the same values as the other arm), uniform random token ids (the reference's own)",
+        "config": {"model": "Qwen3-8B shape (BASELINE.json configs[2])", "global_batch": B, "seq_len": PROMPT_LEN,
+                   "parallelism": "single GPU", "layers": shape["num_hidden_layers"], "layers_of_config": SHAPE_8B["num_hidden_layers"],
+                   "hidden": shape["hidden_size"], "heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
+                   "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+                   "context_len": PROMPT_LEN + W + K + 16, "prompt_len": PROMPT_LEN, "kv_block": 16,
+                   "command": "iian bench --concurrency B --prompt-tokens 1024 --gen-tokens W+K --json", "kv_dtype": "f16 (its default)"},
+        "e2e": {"value": decode_tps, "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "ms_per_step": row.get("tpot_ms")},
+        "clocks": sampler.summary(),
+        "reference_row": {k: row[k] for k in ("concurrency", "prompt_tps", "gen_tps", "total_tps", "ttft_ms", "tpot_ms", "wall_s") if k in row},
+    }
+    print(json.dumps(line))
     return 0
 
 

@@ -620,6 +620,8 @@ class CudaKernels:
         only taken when each still gets four tiles or more (contexts beyond 4k); 9 to 11 are rounded down to 8."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
+        if os.environ.get("IIAN_DECODE_FORCE_SPLITS"):
+            return int(os.environ["IIAN_DECODE_FORCE_SPLITS"])
         n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 2), self.MAX_SPLITS))
         if n > 8 and (n < 12 or tiles < 64):
             n = 8
