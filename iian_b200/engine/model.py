@@ -168,6 +168,13 @@ class Model:
         ``ctx.out_rows`` (None if no row is wanted; the caches are still updated)."""
         if hasattr(ctx, "step_cache"):
             ctx.step_cache.clear()          # a context may be run twice (eagerly, then under graph capture)
+        if self.device.type == "cuda":
+            from ..ops.cuda_backend import pin_stream
+            with pin_stream():
+                return self._forward(ctx, storage)
+        return self._forward(ctx, storage)
+
+    def _forward(self, ctx, storage) -> Optional[torch.Tensor]:
         residual = self.embedding.forward(ctx.tokens, ctx)
         delta = None
         order = self.spec.order

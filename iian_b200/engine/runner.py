@@ -46,9 +46,21 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}      # (name, dtype, shape) -> the view handed out last time
         self.frozen = False          # set while a CUDA graph that uses these buffers is alive
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        vkey = (name, dtype, tuple(shape))
+        v = self._views.get(vkey)
+        if v is not None:
+            return v
+        v = self._get(name, shape, dtype)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[vkey] = v
+        return v
+
+    def _get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1
         for s in shape:
             n *= int(s)
@@ -60,6 +72,7 @@ class Workspace:
             cap = max(n, 1)
             t = torch.empty(cap, dtype=dtype, device=self.device)
             self._bufs[key] = t
+            self._views = {k: v for k, v in self._views.items() if (k[0], k[1]) != key}     # views of the old buffer
         return t[:n].view(*shape)
 
 

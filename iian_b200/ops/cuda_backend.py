@@ -66,8 +66,27 @@ def _cuda(t: Optional[torch.Tensor], what: str, dtype=None) -> int:
     return t.data_ptr()
 
 
+_PINNED_STREAM = [0]
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The CUDA stream the kernels are launched on: torch's current stream, looked up once per forward pass
+    (``pin_stream``) rather than once per launch -- the lookup costs more than the launch itself."""
+    return _PINNED_STREAM[0] or torch.cuda.current_stream().cuda_stream
+
+
+class pin_stream:
+    """``with pin_stream():`` every launch inside goes to the stream that is current on entry.  Code that
+    switches streams inside (the weight prefetcher's side stream) passes its stream explicitly."""
+
+    def __enter__(self):
+        self.before = _PINNED_STREAM[0]
+        _PINNED_STREAM[0] = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        _PINNED_STREAM[0] = self.before
+        return False
 
 
 _sigs_done = set()
@@ -478,9 +497,9 @@ class CudaKernels:
         _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"),
                   t_rows, n, k, epilogue, bn, status, in_p, in_tiles, inv_w, eps, res, nw, out_p, _stream()), "gemm_tcgen05")
 
-    def prefetch_l2(self, ptr: int, nbytes: int) -> None:
+    def prefetch_l2(self, ptr: int, nbytes: int, stream: Optional[int] = None) -> None:
         fn = _fn("prefetch", "iian_prefetch_l2", [c_void_p, c_longlong, c_void_p])
-        _check(fn(ptr, nbytes, _stream()), "prefetch_l2")
+        _check(fn(ptr, nbytes, _stream() if stream is None else stream), "prefetch_l2")
 
     # ---- attention -----------------------------------------------------------------------
     def qk_norm_rope_store(self, qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
@@ -879,7 +898,7 @@ class WeightPrefetcher:
                 lo = max(begin, self.starts[j]) - self.starts[j]
                 hi = min(end, self.starts[j] + nbytes) - self.starts[j]
                 if hi > lo:
-                    kernels.prefetch_l2(ptr + lo, hi - lo)
+                    kernels.prefetch_l2(ptr + lo, hi - lo, stream=self.side.cuda_stream)
                     self.launches += 1
                 j += 1
         self.cursor = end
