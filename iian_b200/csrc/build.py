@@ -201,6 +201,68 @@ def _compile_host(verbose: bool = True) -> str:
     return out
 
 
+# ---- the native step function and engine loop: C++17 host code that calls CUDA's runtime and cuBLAS and opens the
+# kernel libraries above with dlopen; it carries a copy of the host runtime's sources (it packs decode steps itself) ----
+ENGINE_NAME = "engine"
+ENGINE_DIR = os.path.join(HERE, "engine")
+ENGINE_FLAGS = ["-shared", "-std=c++17", "-O2", "-Xcompiler", "-fPIC", "-Wno-deprecated-gpu-targets"]
+ENGINE_LIBS = ["-lcublas", "-ldl"]
+
+
+def _engine_sources() -> List[str]:
+    return sorted(os.path.join(ENGINE_DIR, f) for f in os.listdir(ENGINE_DIR) if f.endswith(".cc")) + _host_sources()
+
+
+def _engine_hash() -> str:
+    h = hashlib.sha256()
+    headers = sorted(os.path.join(INCLUDE_DIR, "iian_b200", f) for f in os.listdir(os.path.join(INCLUDE_DIR, "iian_b200")))
+    for p in _engine_sources() + headers:
+        with open(p, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(ENGINE_FLAGS + ENGINE_LIBS).encode())
+    return h.hexdigest()[:16]
+
+
+def _compile_engine(verbose: bool = True) -> str:
+    out = os.path.join(build_dir(), f"{ENGINE_NAME}.{_engine_hash()}.so")
+    if os.path.isfile(out):
+        return out
+    tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
+    cmd = [_nvcc()] + ENGINE_FLAGS + ["-I", INCLUDE_DIR, "-o", tmp] + _engine_sources() + ENGINE_LIBS
+    t0 = time.time()
+    if verbose:
+        print("[iian_b200] compiling the native engine ...", file=sys.stderr, flush=True)
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+        raise KernelBuildError(f"compiling the native engine failed (exit {proc.returncode}):\n{' '.join(cmd)}\n{proc.stdout}")
+    os.replace(tmp, out)
+    for fn in os.listdir(os.path.dirname(out)):
+        if fn.startswith(f"{ENGINE_NAME}.") and fn.endswith(".so") and os.path.join(os.path.dirname(out), fn) != out:
+            try:
+                os.remove(os.path.join(os.path.dirname(out), fn))
+            except OSError:
+                pass
+    if verbose:
+        print(f"[iian_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    return out
+
+
+def load_engine() -> ctypes.CDLL:
+    """The native step function and engine loop, compiled first if needed (needs nvcc for its CUDA headers and libraries)."""
+    with _lock:
+        lib = _loaded.get(ENGINE_NAME)
+        if lib is None:
+            path = _compile_engine()
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelBuildError(f"cannot load {path}: {e}") from None
+            _loaded[ENGINE_NAME] = lib
+        return lib
+
+
 def load_host() -> ctypes.CDLL:
     """The host runtime library, compiled first if needed (needs a C++ compiler, no GPU and no nvcc)."""
     with _lock:
@@ -223,6 +285,7 @@ def build(names: Optional[Iterable[str]] = None, verbose: bool = True) -> List[s
         built = list(pool.map(lambda n: _compile(n, verbose), names))
     if everything:
         built.append(_compile_host(verbose))
+        built.append(_compile_engine(verbose))
     return built
 
 

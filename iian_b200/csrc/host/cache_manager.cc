@@ -5,7 +5,13 @@
 
 namespace iian_b200 {
 
-static std::atomic<long long> g_next_serial{1};
+// Serial numbers of request records: unique for the life of the process, also when this source is part of more than
+// one loaded library (each copy then counts in a range of its own, set apart by where the copy was loaded).
+static std::atomic<long long> g_next_serial{0};
+static long long next_serial() {
+    const long long base = (long long) ((reinterpret_cast<uintptr_t>(&g_next_serial) >> 4) & 0x3FFFFFF) << 36;
+    return base + 1 + g_next_serial++;
+}
 
 bool RequestCache::holds_pages() const {
     for (const auto & t : tables)
@@ -41,7 +47,7 @@ CacheManager::CacheManager(const std::vector<PageGroup> & groups, int block_size
 
 RequestCache * CacheManager::new_request() const {
     auto * rc = new RequestCache();
-    rc->serial = g_next_serial++;
+    rc->serial = next_serial();
     rc->tables.resize(groups_.size());
     rc->committed.assign(groups_.size(), 0);
     return rc;

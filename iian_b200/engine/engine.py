@@ -217,9 +217,7 @@ class Engine:
                 if lp is not None:
                     r.pending_logprobs.append(lp)
                     r.logprobs.append(lp)
-        kernels = ops.kernels()
-        if hasattr(kernels, "check_device_status"):
-            kernels.check_device_status()      # the tokens are on the host: a kernel that gave up has said so by now
+        self.runner.check_device_status()      # the tokens are on the host: a kernel that gave up has said so by now
         now = time.monotonic()
         for r, tok in zip(reqs, tokens):
             r.tokens.append(tok)

@@ -25,20 +25,22 @@ class TraceError(RuntimeError):
 
 
 class TraceReplayer:
-    def __init__(self, model: Model, max_tokens: int, block_size: int = 16, max_requests: int = 8):
+    def __init__(self, model: Model, max_tokens: int, block_size: int = 16, max_requests: int = 8, native=None):
         bs = block_size
         self.model = model
         self.max_tokens = max_tokens
         capacity = ((max_tokens + bs - 1) // bs) * bs
         self.runner = ModelRunner(model, block_size=bs, capacity_tokens=capacity, max_num_seqs=max_requests,
-                                  enable_prefix_caching=False)
+                                  enable_prefix_caching=False, native=native)
         self.max_requests = max_requests
         self.live: Dict[object, list] = {}      # id -> [RequestCache, tokens held]
 
     @classmethod
     def from_folder(cls, model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, max_requests: int = 8,
-                    device: str = "cuda:0") -> "TraceReplayer":
-        return cls(Model.from_folder(model_dir, dtype, device), max_tokens, block_size, max_requests)
+                    device: str = "cuda:0", native=None) -> "TraceReplayer":
+        """``native``: True / False picks the step function in C++ or the one in Python; None takes the default (the
+        C++ one for models made of built-in parts)."""
+        return cls(Model.from_folder(model_dir, dtype, device), max_tokens, block_size, max_requests, native=native)
 
     def run_step(self, rec: dict) -> Optional[torch.Tensor]:
         """Run one step; float32 logits ``[wanted, vocab]`` on the device, or None."""

@@ -124,9 +124,10 @@ class StepContext:
 class ModelRunner:
     def __init__(self, model: Model, *, block_size: int = 16, capacity_tokens: int, max_num_seqs: int = 4,
                  enable_prefix_caching: bool = False, window_capacity_tokens: Optional[int] = None,
-                 cuda_graphs: bool = False, max_model_len: Optional[int] = None):
+                 cuda_graphs: bool = False, max_model_len: Optional[int] = None, native: Optional[bool] = None):
         self.model = model
         # decode steps are replayed from graphs only if every part of the model can be recorded
+        self.native = None
         self.cuda_graphs = cuda_graphs and model.device.type == "cuda" and model.graph_safe()
         self.weight_prefetch = os.environ.get("IIAN_WEIGHT_PREFETCH", "1") not in ("0", "false", "off")
         self.max_model_len = max_model_len or capacity_tokens
@@ -152,6 +153,57 @@ class ModelRunner:
         if self.device.type == "cuda":
             from ..csrc import build
             build.preload(model.kernel_libraries())      # compile what this model needs, together
+        # The step function in C++ (include/iian_b200/engine.h) for models made of built-in parts only: the same kernels
+        # in the same order, issued without a Python call per launch.  ``native=None``: as IIAN_NATIVE_STEP says (default on).
+        if native is None:
+            native = os.environ.get("IIAN_NATIVE_STEP", "1") not in ("0", "false", "off")
+        if native and self.device.type == "cuda":
+            from . import native as _native
+            from .. import ops as _ops
+            if _native.supports(model) and getattr(_ops.kernels(), "name", "") == "cuda":
+                self.native = _native.NativeStep(model, self.manager, self.storage, max_num_seqs=max_num_seqs,
+                                                 max_model_len=self.max_model_len, cuda_graphs=self.cuda_graphs,
+                                                 weight_prefetch=self.weight_prefetch)
+
+    @property
+    def cuda_graphs(self) -> bool:
+        return self._cuda_graphs
+
+    @cuda_graphs.setter
+    def cuda_graphs(self, on: bool) -> None:
+        self._cuda_graphs = bool(on)
+        if self.native is not None:
+            self.native.set_cuda_graphs(self._cuda_graphs)
+
+    ENTRIES = ("embedding", "add_rms_norm", "swiglu", "gather_rows", "add_bias", "rotary_table", "qk_norm_rope_store",
+               "paged_attention_generic", "gemm_simt", "gemm_skinny", "gemm_skinny_fused", "gemm_tcgen05", "attention_tc",
+               "attention_mma", "attention_decode_fused", "prefetch_l2", "library_gemm")
+
+    def launches_by_entry(self) -> Dict[str, int]:
+        """Launches so far by the kernel layer's entry point, whichever step function issued them (the Python kernel
+        layer counts for the whole process, the native step function for this runner)."""
+        from ..ops import cuda_backend
+        out = dict(cuda_backend.LAUNCHES_BY_ENTRY)
+        if self.native is not None:
+            for name in self.ENTRIES:
+                n = self.native.launches_of(name)
+                if n:
+                    out[name] = out.get(name, 0) + n
+        return out
+
+    def check_device_status(self) -> None:
+        """Raise if a tcgen05 kernel gave up waiting on a barrier since the last call (its output would be garbage)."""
+        from .. import ops
+        k = ops.kernels()
+        if hasattr(k, "check_device_status"):
+            k.check_device_status()
+        if self.native is not None:
+            self.native.check_status()
+
+    @property
+    def num_graphs(self) -> int:
+        """Decode graphs captured so far (by whichever step function runs)."""
+        return self.native.num_graphs if self.native is not None else len(self._graphs)
 
     # ---- batch building ---------------------------------------------------------------------
     def _stage(self, n_ints: int) -> Tuple[np.ndarray, torch.Tensor]:
@@ -388,6 +440,12 @@ class ModelRunner:
             return None
         if len(entries) > self.max_num_seqs:
             raise ValueError(f"{len(entries)} requests in one step, the runner was built for {self.max_num_seqs}")
+        if self.native is not None:
+            before = self.native.launches
+            out = self.native.step(entries)
+            self.launches += self.native.launches - before
+            self.last_upload_bytes = self.native.last_upload_bytes
+            return out
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._step_graph(entries)
         ctx = self.build_context(entries)

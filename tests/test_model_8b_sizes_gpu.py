@@ -75,7 +75,7 @@ def test_bfloat16_engine_against_the_plain_implementation(big, models, monkeypat
     _, _, _, reqs, want = big
     rp = TraceReplayer(models["bfloat16"], 256, 16, 4)
     got = replay_and_collect(rp, traces(reqs)[mode])
-    cuda_backend.CudaKernels().check_device_status()
+    rp.runner.check_device_status()
     tol = TOL16_REL * max(v.abs().max().item() for v in want.values())
     worst, where = max_error(got, want)
     print(f"[8B sizes, bfloat16, {mode}, min tiles {min_tiles}] max abs err {worst:.3g} at {where}, tol {tol:.3g}")
@@ -104,11 +104,12 @@ def test_a_step_of_more_than_1024_rows(big, models, monkeypatch, min_tiles):
     steps = [{"step": 0, "entries": [{"id": "p", "tokens": toks[:1100], "want": [0, 127, 128, 511, 1023, 1024, 1099]}], "end": []}]
     for i in range(3):
         steps.append({"step": 1 + i, "entries": [{"id": "p", "tokens": [toks[1100 + i]], "want": [0]}], "end": ["p"] if i == 2 else []})
-    cuda_backend.LAUNCHES_BY_ENTRY.clear()
-    (a, _), (b, _) = _both(models, steps, 1152, 2, graphs=False)
-    cuda_backend.CudaKernels().check_device_status()
-    assert {"gemm_tcgen05", "attention_tc"} <= set(cuda_backend.LAUNCHES_BY_ENTRY)
-    assert ("library_gemm" in cuda_backend.LAUNCHES_BY_ENTRY) == (min_tiles > 0)
+    before = dict(cuda_backend.LAUNCHES_BY_ENTRY)
+    (a, _), (b, rp) = _both(models, steps, 1152, 2, graphs=False)
+    rp.runner.check_device_status()
+    seen = {k for k, v in rp.runner.launches_by_entry().items() if v > before.get(k, 0)}
+    assert {"gemm_tcgen05", "attention_tc"} <= seen
+    assert ("library_gemm" in seen) == (min_tiles > 0)
     scale = max(v.abs().max().item() for v in a.values())
     worst = max((a[k] - b[k]).abs().max().item() for k in a)
     print(f"[8B sizes, 1100 rows, min tiles {min_tiles}] bfloat16 against float32: {worst:.3g} (scale {scale:.3g})")
@@ -143,7 +144,7 @@ def test_decoding_from_graphs_at_batches_of_64_16_8_and_1(big, models):
     decode(ids[:8], 40, end=ids[1:8])
     decode(ids[:1], 3, end=ids[:1])
     (a, _), (b, rp) = _both(models, steps, 64 * 80, 64, graphs=True)
-    assert {k[0] for k in rp.runner._graphs} >= {64, 16, 8, 1}, f"graphs captured for batches {sorted(rp.runner._graphs)}"
+    assert rp.runner.num_graphs >= 4, f"{rp.runner.num_graphs} graphs captured for batches of 64, 16, 8 and 1"
     scale = max(v_.abs().max().item() for v_ in a.values())
     worst, where = 0.0, None
     for k in a:

@@ -58,7 +58,11 @@ def check(folders, plains, name, dtype, reqs, steps, max_tokens):
     from iian_b200.engine.replay import TraceReplayer
     want = plains(name, reqs)
     rp = TraceReplayer.from_folder(folders[name], dtype, max_tokens, BLOCK_SIZE[name])
+    before = rp.runner.launches_by_entry()
     got = replay_and_collect(rp, steps)
+    after = rp.runner.launches_by_entry()
+    check.seen = {k for k, v in after.items() if v > before.get(k, 0)}       # entry points that served this replay
+    rp.runner.check_device_status()
     rp.runner.manager.check_invariants()
     assert all(p.num_free == p.num_blocks for p in rp.runner.manager.pools), "pages were lost"
     assert len(got) == sum(len(t) for t in reqs.values())
@@ -101,18 +105,17 @@ SERVED_BY = {
 @pytest.mark.parametrize("case", sorted(SERVED_BY))
 @pytest.mark.parametrize("min_tiles", [0, 300])
 def test_the_serving_kernels_run_inside_whole_model_checks(folders, plains, monkeypatch, case, min_tiles):
-    """The logits of D, E and F in bfloat16 come from the kernels that serve the large shapes, not from the general
+    """(``gemm_skinny_fused`` also stands for the plain ``gemm_skinny`` launch.)  The logits of D, E and F in bfloat16 come from the kernels that serve the large shapes, not from the general
     ones -- with the own tcgen05 product from the first tile on (as the other tests run) and with the dispatch
     rule's default threshold, under which these small products go to the library instead."""
     from iian_b200.ops import cuda_backend
     name, mode = case
     monkeypatch.setattr(cuda_backend.CudaKernels, "TCGEN05_MIN_TILES", min_tiles)
-    cuda_backend.LAUNCHES_BY_ENTRY.clear()
     reqs = requests_for(name, LENGTHS[name], 13)
     builder = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions}.get(mode)
     steps = builder(reqs) if builder else trace_mixed(reqs, 256, seed=6)
     check(folders, plains, name, "bfloat16", reqs, steps, 256)
-    seen = set(cuda_backend.LAUNCHES_BY_ENTRY)
+    seen = check.seen
     want = set(SERVED_BY[case])
     if min_tiles:
         want = {("library_gemm" if w == "gemm_tcgen05" else w) for w in want}
