@@ -15,7 +15,7 @@ import torch
 
 from helpers import first_bad, random_tokens, replay_and_collect, trace_mixed, trace_portions, trace_tail, trace_whole
 from iian_b200.parts.base import StateNeed
-from toy_model import CFG, CFG_EMA_ONLY, plain_toy, plain_toy_greedy, register_toy, unregister_toy, write_toy
+from toy_model import CFG, CFG_EMA_ONLY, CFG_ROUTED, plain_toy, plain_toy_greedy, register_toy, unregister_toy, write_toy
 
 pytestmark = pytest.mark.gpu
 
@@ -24,7 +24,8 @@ pytestmark = pytest.mark.gpu
 def toys(tmp_path_factory):
     register_toy()
     out = {"mixed": (write_toy(str(tmp_path_factory.mktemp("toy")), CFG), CFG),
-           "ema_only": (write_toy(str(tmp_path_factory.mktemp("toy_ema")), CFG_EMA_ONLY, seed=10), CFG_EMA_ONLY)}
+           "ema_only": (write_toy(str(tmp_path_factory.mktemp("toy_ema")), CFG_EMA_ONLY, seed=10), CFG_EMA_ONLY),
+           "routed": (write_toy(str(tmp_path_factory.mktemp("toy_routed")), CFG_ROUTED, seed=11), CFG_ROUTED)}
     yield out
     unregister_toy()
 
@@ -49,7 +50,7 @@ def test_toy_is_built_from_registered_parts(toy):
 @pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
-@pytest.mark.parametrize("layout", ["mixed", "ema_only"])
+@pytest.mark.parametrize("layout", ["mixed", "ema_only", "routed"])
 def test_toy_steps_like_its_plain_model(toys, layout, dtype, mode, graphs):
     """With ``graphs`` the decode-only steps are replayed from captured CUDA graphs: the state must advance
     exactly once per step (also on the step that captures a new graph)."""
@@ -62,14 +63,20 @@ def test_toy_steps_like_its_plain_model(toys, layout, dtype, mode, graphs):
     steps = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions}.get(mode)
     steps = steps(reqs) if steps else trace_mixed(reqs, 192, seed=4, max_live=3)
     rp = TraceReplayer.from_folder(toy, dtype, 192, block_size=8, max_requests=3)     # 3 slots: they are used again
+    assert rp.runner.native is None, "a model with parts of the test's own runs through the Python step function"
     rp.runner.cuda_graphs = graphs
     got = replay_and_collect(rp, steps)
     if graphs:
         assert rp.runner.num_graphs, "no decode graph was captured"
     scale = max(v.abs().max().item() for v in want.values())
     tol = 3e-5 * max(scale, 1.0) if dtype == "float32" else 2.5e-2 * scale
-    bad = first_bad(got, want, tol)
-    assert bad is None, f"first wrong logits at request {bad[0]} position {bad[1]} (err {bad[2]:.3g}, tol {tol:.3g})"
+    if layout == "routed" and dtype == "bfloat16":
+        # a token whose second and third best experts tie within rounding may be routed differently: allow a few rows
+        bad_rows = [k for k in got if (got[k].double() - want[k[0]][k[1]]).abs().max().item() > tol]
+        assert len(bad_rows) <= len(got) // 50, f"{len(bad_rows)} of {len(got)} rows beyond tolerance"
+    else:
+        bad = first_bad(got, want, tol)
+        assert bad is None, f"first wrong logits at request {bad[0]} position {bad[1]} (err {bad[2]:.3g}, tol {tol:.3g})"
     assert len(got) == sum(len(t) for t in reqs.values())
     assert rp.runner.manager.slots.num_free == 3 and all(p.num_free == p.num_blocks for p in rp.runner.manager.pools)
 

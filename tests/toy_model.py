@@ -7,7 +7,8 @@ with a cache for each run, and a layer that reads the cache another layer filled
 attention at all, so the model needs no pages.  The toy mixer computes with torch operations on the step's
 device tensors only (never on the host lists), so its steps can be replayed from CUDA graphs; the attention,
 norm and feed-forward parts beside it are the framework's.  ``plain_toy`` is the same model written out
-separately in float64 on whole sequences.
+separately in float64 on whole sequences.  A third layout has a feed-forward with routing (every token goes to 2 of
+5 experts) and a position encoding that is no rotation (offsets added to Q and K), both defined here.
 """
 import math
 import os
@@ -17,12 +18,17 @@ import torch
 import plain_qwen3 as plain
 from iian_b200.config.registry import Architecture, get_architecture, register_architecture, unregister_architecture
 from iian_b200.config.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
-from iian_b200.parts.base import MIXERS, Mixer, StateNeed, register_mixer
+from iian_b200.parts.base import (FEED_FORWARDS, MIXERS, POSITIONS, FeedForward, Mixer, PositionEncoding, StateNeed,
+                                  register_feed_forward, register_mixer, register_position)
 from iian_b200.weights.loader import TensorSpec
 
 CFG = {"architectures": ["ToyForCausalLM"], "vocab_size": 97, "hidden_size": 64, "heads": 4, "kv_heads": 2, "head_dim": 16,
        "ffn": 96, "eps": 1e-5, "theta": 10000.0, "decay": 0.75, "max_position": 256, "layout": "mixed"}
 CFG_EMA_ONLY = dict(CFG, layout="ema_only", vocab_size=61, hidden_size=48, ffn=80, decay=0.6)
+# attention with a position encoding of the test's own (a table of offsets added to Q and K, not a rotation) and a
+# feed-forward that routes every token to 2 of 5 small experts
+CFG_ROUTED = dict(CFG, layout="routed", vocab_size=83, hidden_size=72, heads=6, kv_heads=3, head_dim=24, ffn=40, experts=5, top_k=2,
+                  max_position=160)
 
 
 class ToyEma(Mixer):
@@ -77,6 +83,62 @@ class ToyEma(Mixer):
         return out
 
 
+class ToyRoutedFF(FeedForward):
+    """Routed experts: scores = x Wr^T in float32; the ``top_k`` best experts of a token get weights softmax(their
+    scores); y = sum_e weight_e * W2_e relu(W1_e x).  Torch operations on whole tensors; it branches on nothing."""
+
+    graph_safe = True
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.n_experts, self.top_k = int(spec["experts"]), int(spec["top_k"])
+
+    def tensors(self):
+        return {"router": TensorSpec((self.n_experts, self.hidden)),
+                "w1": TensorSpec((self.n_experts * self.inter, self.hidden)),
+                "w2": TensorSpec((self.n_experts * self.hidden, self.inter))}
+
+    def bind(self, tensors):
+        self.router = tensors["router"].float()
+        self.w1 = tensors["w1"].float().view(self.n_experts, self.inter, self.hidden)
+        self.w2 = tensors["w2"].float().view(self.n_experts, self.hidden, self.inter)
+
+    def forward(self, x, ctx):
+        xf = x.float()
+        scores = xf @ self.router.T                                          # [N, E], float32
+        top, idx = torch.topk(scores, self.top_k, dim=-1)
+        gate = torch.zeros_like(scores).scatter_(1, idx, torch.softmax(top, dim=-1))
+        h = torch.relu(torch.einsum("nh,eih->nei", xf, self.w1))             # every expert on every token (it is a toy)
+        y = torch.einsum("nei,ehi->neh", h, self.w2)
+        return (gate[:, :, None] * y).sum(1).to(x.dtype)
+
+
+class ToyOffsets(PositionEncoding):
+    """A position encoding that is no rotation: a fixed table of offsets, indexed by the position, is added to every
+    head of Q and of K before they are stored and used.  ``fused = False``: the attention mixer calls ``apply`` on the
+    projected heads and hands the kernels unrotated heads."""
+
+    fused = False
+    dim = 0
+    style = 0
+    inv_freq = None
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        hd, n = int(spec["head_dim"]), int(spec["max_position"])
+        pos = torch.arange(n, dtype=torch.float64)[:, None]
+        j = torch.arange(hd, dtype=torch.float64)[None, :]
+        self.table = (0.5 * torch.sin(pos * (j + 1) * 0.37)).to(torch.float32).to(device)    # [max_position, head_dim]
+
+    def apply(self, qkv, num_heads, num_kv_heads, head_dim, ctx):
+        n = qkv.shape[0]
+        off = self.table[ctx.positions.long()]                               # [N, hd]
+        heads = qkv.view(n, num_heads + 2 * num_kv_heads, head_dim)
+        qk = heads[:, :num_heads + num_kv_heads]
+        qk.copy_((qk.float() + off[:, None, :]).to(qkv.dtype))               # V is left alone
+
+
 class ToyArch(Architecture):
     name = "ToyForCausalLM"
 
@@ -98,6 +160,12 @@ class ToyArch(Architecture):
         if c.get("layout", "mixed") == "ema_only":
             layers = (LayerSpec(ema, ffn, norm, norm), LayerSpec(ema, ffn, norm, norm))
             order = (LayerCall(0, 0), LayerCall(1, 1))
+        elif c.get("layout") == "routed":
+            offsets = PartSpec("toy_offsets", {"head_dim": c["head_dim"], "max_position": c["max_position"]})
+            attn_off = PartSpec("attention", dict(attn.params, position=offsets))
+            routed = PartSpec("toy_routed", {"hidden_size": H, "intermediate_size": c["ffn"], "experts": c["experts"], "top_k": c["top_k"]})
+            layers = (LayerSpec(attn_off, routed, norm, norm), LayerSpec(attn_off, ffn, norm, norm), LayerSpec(attn, routed, norm, norm))
+            order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2))
         else:
             layers = (LayerSpec(attn, ffn, norm, norm), LayerSpec(ema, ffn, norm, norm), LayerSpec(attn, ffn, norm, norm))
             # layer 0 runs twice (caches 0 and 2); layer 2 reads the cache layer 0 filled on its first run
@@ -111,6 +179,8 @@ class ToyArch(Architecture):
 
 def register_toy():
     register_mixer("toy_ema")(ToyEma)
+    register_feed_forward("toy_routed")(ToyRoutedFF)
+    register_position("toy_offsets")(ToyOffsets)
     register_architecture(ToyArch)
     return get_architecture("ToyForCausalLM")
 
@@ -118,6 +188,8 @@ def register_toy():
 def unregister_toy():
     unregister_architecture("ToyForCausalLM")
     MIXERS.unregister("toy_ema")
+    FEED_FORWARDS.unregister("toy_routed")
+    POSITIONS.unregister("toy_offsets")
 
 
 def write_toy(d, cfg, seed=9):
@@ -134,12 +206,19 @@ def plain_toy(d, tokens, c=CFG):
     x = w["embedding.weight"][torch.tensor(tokens)]
     kv = {}
 
-    def attn_layer(x, li, cache_id, writes):
+    def place(t, offsets):             # rotation, or the toy table of offsets added to every head
+        if not offsets:
+            return plain.rope_neox(t, pos, c["theta"], hd)
+        j = torch.arange(hd, dtype=torch.float64)[None, :]
+        table = (0.5 * torch.sin(pos.double()[:, None] * (j + 1) * 0.37)).float().double()
+        return t + table[:, None, :]
+
+    def attn_layer(x, li, cache_id, writes, offsets=False):
         p = f"layer.{li}."
         h = plain.rms_norm(x, w[p + "mixer_norm.weight"], c["eps"])
-        q = plain.rope_neox((h @ w[p + "mixer.q_proj.weight"].T).view(T, nh, hd), pos, c["theta"], hd)
+        q = place((h @ w[p + "mixer.q_proj.weight"].T).view(T, nh, hd), offsets)
         if writes:
-            k = plain.rope_neox((h @ w[p + "mixer.k_proj.weight"].T).view(T, nkv, hd), pos, c["theta"], hd)
+            k = place((h @ w[p + "mixer.k_proj.weight"].T).view(T, nkv, hd), offsets)
             v = (h @ w[p + "mixer.v_proj.weight"].T).view(T, nkv, hd)
             kv[cache_id] = (k, v)
         k, v = kv[cache_id]
@@ -162,9 +241,28 @@ def plain_toy(d, tokens, c=CFG):
         return x + plain.gated_mlp(h, w[p + "feed_forward.gate_proj.weight"], w[p + "feed_forward.up_proj.weight"],
                                    w[p + "feed_forward.down_proj.weight"])
 
+    def routed(x, li):
+        p = f"layer.{li}."
+        h = plain.rms_norm(x, w[p + "feed_forward_norm.weight"], c["eps"])
+        E, I, H = c["experts"], c["ffn"], c["hidden_size"]
+        scores = h @ w[p + "feed_forward.router"].T
+        w1 = w[p + "feed_forward.w1"].view(E, I, H)
+        w2 = w[p + "feed_forward.w2"].view(E, H, I)
+        out = torch.zeros_like(x)
+        for t in range(T):
+            top, idx = torch.topk(scores[t], c["top_k"])
+            gate = torch.softmax(top, dim=-1)
+            for g, e in zip(gate, idx):
+                out[t] += g * (w2[e] @ torch.relu(w1[e] @ h[t]))
+        return x + out
+
     if c.get("layout", "mixed") == "ema_only":
         x = ffn(ema_layer(x, 0), 0)
         x = ffn(ema_layer(x, 1), 1)
+    elif c.get("layout") == "routed":
+        x = routed(attn_layer(x, 0, 0, True, offsets=True), 0)
+        x = ffn(attn_layer(x, 1, 1, True, offsets=True), 1)
+        x = routed(attn_layer(x, 2, 2, True), 2)
     else:
         x = ffn(attn_layer(x, 0, 0, True), 0)
         x = ffn(ema_layer(x, 1), 1)
