@@ -28,7 +28,7 @@ SHAPES = {  # name -> (out features, in features) at the Qwen3-8B sizes
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "gemm_library", "attention_decode", "attention_prefill",
+    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_stream", "gemm_tcgen05", "gemm_library", "attention_decode", "attention_prefill",
                                        "rope", "norm", "swiglu", "layer_decode"])
     ap.add_argument("--shape", default="gate_up", choices=sorted(SHAPES))
     ap.add_argument("--rows", type=int, default=8, help="rows of activations (tokens in the step)")
@@ -59,7 +59,7 @@ def main(argv=None) -> int:
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 2
     k = CudaKernels()
-    if args.stages:
+    if args.stages and args.kernel != "gemm_stream":
         k.set_decode_stages(args.stages)
     dev = torch.device("cuda:0")
     bf = torch.bfloat16
@@ -109,6 +109,11 @@ def main(argv=None) -> int:
         out = torch.empty(n, m // 2 if swiglu else m, device=dev, dtype=bf)
         if args.kernel == "gemm_skinny":
             us = timeit(lambda i: k.gemm_skinny(x, ws[i % copies], out, cfg=args.cfg, ksplit=args.ksplit, epilogue=1 if swiglu else 0))
+        elif args.kernel == "gemm_stream":       # (--stages 6 or 12: depth of the ring of shared-memory stages)
+            if args.stages:
+                type(k).STREAM_STAGES = args.stages
+            us = timeit(lambda i: k._gemm_stream(x, ws[i % copies], out, n, m, kd, 1 if swiglu else 0))
+            k.tcgen05_check(dev)
         elif args.kernel == "gemm_tcgen05":
             us = timeit(lambda i: k.gemm_tcgen05(x, ws[i % copies], out, epilogue=1 if swiglu else 0, bn=args.bn))
             k.tcgen05_check(dev)

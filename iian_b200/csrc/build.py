@@ -30,9 +30,9 @@ SHARED_HEADERS = ["common.cuh"]
 
 # every library of the engine; build_all() compiles them all
 SOURCES = ["elementwise", "rope_kv", "attention_generic", "gemm_simt", "sampling", "gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05",
-           "attention_tc"]
+           "attention_tc", "gemm_stream"]
 # libraries only the bfloat16 serving path uses
-BF16_SOURCES: List[str] = ["gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05", "attention_tc"]
+BF16_SOURCES: List[str] = ["gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05", "attention_tc", "gemm_stream"]
 # extra link flags per source
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 # extra compiler flags for every source, from the environment (e.g. "-DIIAN_SOMETHING=1" to build a variant of a

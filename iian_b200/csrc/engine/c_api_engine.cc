@@ -71,9 +71,9 @@ void * iian_runner_new(const IianModel * model, const char * const * libs, void 
             m.calls.push_back(c);
         }
         KernelLibraries kl;
-        std::string * slots[10] = {&kl.elementwise, &kl.rope_kv, &kl.attention_generic, &kl.gemm_simt, &kl.sampling, &kl.gemm_skinny,
-                                   &kl.attention_mma, &kl.prefetch, &kl.gemm_tcgen05, &kl.attention_tc};
-        for (int i = 0; i < 10; i++) if (libs[i] != nullptr) *slots[i] = libs[i];
+        std::string * slots[11] = {&kl.elementwise, &kl.rope_kv, &kl.attention_generic, &kl.gemm_simt, &kl.sampling, &kl.gemm_skinny,
+                                   &kl.attention_mma, &kl.prefetch, &kl.gemm_tcgen05, &kl.attention_tc, &kl.gemm_stream};
+        for (int i = 0; i < 11; i++) if (libs[i] != nullptr) *slots[i] = libs[i];
         RunnerOptions opt;
         opt.max_num_seqs = o->max_num_seqs; opt.max_model_len = o->max_model_len; opt.cuda_graphs = o->cuda_graphs != 0;
         opt.weight_prefetch = o->weight_prefetch != 0; opt.prefetch_window_mb = o->prefetch_window_mb;
@@ -81,6 +81,7 @@ void * iian_runner_new(const IianModel * model, const char * const * libs, void 
         opt.fuse_norm = o->fuse_norm != 0; opt.fused_decode = o->fused_decode != 0; opt.attention_tc = o->attention_tc != 0;
         opt.cluster_merge = o->cluster_merge != 0; opt.tcgen05_pair = o->tcgen05_pair != 0; opt.decode_stages = o->decode_stages;
         opt.max_splits = o->max_splits; opt.decode_ctas_per_sm = o->decode_ctas_per_sm;
+        opt.stream_product = o->stream_product != 0; opt.stream_stages = o->stream_stages;
         r = new NativeRunner(m, kl, static_cast<CacheManager *>(cache), opt);
     });
     return r;

@@ -67,6 +67,9 @@ struct Kernels {
                                   const int *, int, int, int, int, int, int, int, float, int, int, int, const float *,
                                   const float *, const float *, const int *, float, int, S) = nullptr;
     int (*attention_decode_stages)(int) = nullptr;
+    int (*gemm_stream)(const void *, const void *, void *, int, int, int, int, int, const float *, int, float, float, float *,
+                       const float *, float *, int *, S) = nullptr;
+    int (*gemm_stream_stages)(int) = nullptr;
     int (*prefetch_l2)(const void *, long long, S) = nullptr;
 };
 
@@ -295,13 +298,30 @@ struct NativeRunner::Impl {
         if (prefetcher) prefetcher->index++;
     }
 
+    void plain_stream_product(const void * x, const MatrixDesc & w, void * out, int out_dtype, int n, int epilogue) {
+        if (opt.stream_product) {
+            tc_used = true;
+            check(k.gemm_stream(x, w.ptr, out, out_dtype, n, w.rows, w.cols, epilogue, nullptr, 0, 0.0f, 0.0f, nullptr, nullptr, nullptr,
+                                tc_status, stream), "gemm_stream");
+        } else {
+            check(k.gemm_skinny_cfg(x, w.ptr, out, out_dtype, n, w.rows, w.cols, 0, 1, nullptr, nullptr, epilogue, stream), "gemm_skinny");
+        }
+    }
     void gemm_skinny_fused(const void * x, const MatrixDesc & w, void * out, int out_dtype, int n, int epilogue, const Rows * scale,
                            float * res, const float * norm_w, float * out_partial) {
         before_stream_product();
-        check(k.gemm_skinny_fused(x, w.ptr, out, out_dtype, n, w.rows, w.cols, epilogue,
-                                  scale ? scale->partials : nullptr, scale ? scale->parts : 0,
-                                  scale ? 1.0f / (float) scale->width : 0.0f, scale ? scale->eps : 0.0f,
-                                  res, norm_w, out_partial, stream), "gemm_skinny_fused");
+        if (opt.stream_product) {
+            tc_used = true;
+            check(k.gemm_stream(x, w.ptr, out, out_dtype, n, w.rows, w.cols, epilogue,
+                                scale ? scale->partials : nullptr, scale ? scale->parts : 0,
+                                scale ? 1.0f / (float) scale->width : 0.0f, scale ? scale->eps : 0.0f,
+                                res, norm_w, out_partial, tc_status, stream), "gemm_stream");
+        } else {
+            check(k.gemm_skinny_fused(x, w.ptr, out, out_dtype, n, w.rows, w.cols, epilogue,
+                                      scale ? scale->partials : nullptr, scale ? scale->parts : 0,
+                                      scale ? 1.0f / (float) scale->width : 0.0f, scale ? scale->eps : 0.0f,
+                                      res, norm_w, out_partial, stream), "gemm_skinny_fused");
+        }
         after_stream_product(w);
     }
     void gemm_tcgen05(const void * x, const MatrixDesc & w, void * out, int out_dtype, int n, int epilogue, const Rows * scale,
@@ -347,7 +367,7 @@ struct NativeRunner::Impl {
             if (tcgen05_ok(x, x_dtype, w, n)) { gemm_tcgen05(x, w, out, out_dtype, n, 0, nullptr, nullptr, nullptr, nullptr); return; }
             if (n <= 8 && w.cols % 32 == 0 && aligned16(x) && aligned16(w.ptr)) {
                 before_stream_product();
-                check(k.gemm_skinny_cfg(x, w.ptr, out, out_dtype, n, w.rows, w.cols, 0, 1, nullptr, nullptr, 0, stream), "gemm_skinny");
+                plain_stream_product(x, w, out, out_dtype, n, 0);
                 after_stream_product(w);
                 return;
             }
@@ -366,7 +386,7 @@ struct NativeRunner::Impl {
         }
         if (tcgen05_ok(x, act_dtype, w, n)) { gemm_tcgen05(x, w, out, act_dtype, n, 1, nullptr, nullptr, nullptr, nullptr); return; }
         before_stream_product();
-        check(k.gemm_skinny_cfg(x, w.ptr, out, act_dtype, n, w.rows, w.cols, 0, 1, nullptr, nullptr, 1, stream), "gemm_skinny");
+        plain_stream_product(x, w, out, act_dtype, n, 1);
         after_stream_product(w);
     }
 
@@ -846,6 +866,11 @@ NativeRunner::NativeRunner(const ModelDesc & model, const KernelLibraries & libs
             if (k.attention_decode_stages(opt.decode_stages) != 0) fail("attention: the decode kernel has 2 or 3 stages");
         } else fail("the attention_mma kernel library is required for bfloat16");
         if (void * h = open(libs.prefetch)) bind(h, "iian_prefetch_l2", k.prefetch_l2, libs.prefetch);
+        if (void * h = open(libs.gemm_stream)) {
+            bind(h, "iian_gemm_stream", k.gemm_stream, libs.gemm_stream);
+            bind(h, "iian_gemm_stream_stages", k.gemm_stream_stages, libs.gemm_stream);
+            if (k.gemm_stream_stages(opt.stream_stages) != 0) fail("gemm_stream: the ring is chosen by 6 or 12");
+        } else if (opt.stream_product) fail("the gemm_stream kernel library is required for bfloat16");
         cuda_ok(cudaMalloc(reinterpret_cast<void **>(&m.tc_status), 2 * sizeof(int)), "cudaMalloc (status)");
         cuda_ok(cudaMemset(m.tc_status, 0, 2 * sizeof(int)), "cudaMemset");
     }
@@ -899,7 +924,7 @@ void NativeRunner::check_status() {
     cuda_ok(cudaMemcpy(host, m.tc_status, sizeof(host), cudaMemcpyDeviceToHost), "cudaMemcpy (status)");
     if (host[0] != 0) {
         cudaMemset(m.tc_status, 0, sizeof(host));
-        fail("a tcgen05 kernel gave up waiting on a barrier (wait " + std::to_string(host[0]) + ", iteration " + std::to_string(host[1]) + "); its result is not valid");
+        fail("a kernel gave up waiting on a barrier (wait " + std::to_string(host[0]) + ", iteration " + std::to_string(host[1]) + "); its result is not valid");
     }
 }
 

@@ -176,7 +176,7 @@ class ModelRunner:
             self.native.set_cuda_graphs(self._cuda_graphs)
 
     ENTRIES = ("embedding", "add_rms_norm", "swiglu", "gather_rows", "add_bias", "rotary_table", "qk_norm_rope_store",
-               "paged_attention_generic", "gemm_simt", "gemm_skinny", "gemm_skinny_fused", "gemm_tcgen05", "attention_tc",
+               "paged_attention_generic", "gemm_simt", "gemm_skinny", "gemm_skinny_fused", "gemm_stream", "gemm_tcgen05", "attention_tc",
                "attention_mma", "attention_decode_fused", "prefetch_l2", "library_gemm")
 
     def launches_by_entry(self) -> Dict[str, int]:

@@ -249,15 +249,39 @@ class CudaKernels:
             out_p = _cuda(rn.partials, "norm partials", torch.float32)
         if self.prefetcher is not None:
             self.prefetcher.before_product(self)
-        fn = _fn("gemm_skinny", "iian_gemm_skinny_fused",
-                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_float,
-                  c_void_p, c_void_p, c_void_p, c_void_p])
-        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"), n, m, k,
-                  epilogue, in_p, in_tiles, inv_w, eps, res, nw, out_p, _stream()), "gemm_skinny_fused")
+        if self.STREAM_PRODUCT:
+            self._gemm_stream(x, w, out, n, m, k, epilogue, in_p, in_tiles, inv_w, eps, res, nw, out_p)
+        else:
+            fn = _fn("gemm_skinny", "iian_gemm_skinny_fused",
+                     [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_float,
+                      c_void_p, c_void_p, c_void_p, c_void_p])
+            _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"), n, m, k,
+                      epilogue, in_p, in_tiles, inv_w, eps, res, nw, out_p, _stream()), "gemm_skinny_fused")
         if self.weight_log is not None:
             self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
         if self.prefetcher is not None:
             self.prefetcher.after_product(self)
+
+    # Up to 8 rows: the product whose weights stream through a ring of shared-memory stages filled by bulk asynchronous
+    # copies (csrc/gemm_stream.cu) instead of the one that loads them into registers (csrc/gemm_skinny.cu); the results
+    # are the same bits.  IIAN_STREAM_PRODUCT=0 goes back to the register form.
+    STREAM_PRODUCT = os.environ.get("IIAN_STREAM_PRODUCT", "1") not in ("0", "false", "off")
+    STREAM_STAGES = int(os.environ.get("IIAN_STREAM_STAGES", "12"))
+    _stream_stages_set = None
+
+    def _gemm_stream(self, x, w, out, n, m, k, epilogue, in_p=0, in_tiles=0, inv_w=0.0, eps=0.0, res=0, nw=0, out_p=0) -> None:
+        if self._stream_stages_set != self.STREAM_STAGES:
+            fn = _fn("gemm_stream", "iian_gemm_stream_stages", [c_int])
+            if fn(self.STREAM_STAGES) != 0:
+                raise KernelError("gemm_stream: the ring has 6 or 12 stages")
+            type(self)._stream_stages_set = self.STREAM_STAGES
+        status = self.tcgen05_status_buffer(x.device).data_ptr()
+        CudaKernels._tc_used = True
+        fn = _fn("gemm_stream", "iian_gemm_stream",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_float,
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+        _check(fn(_cuda(x, "linear x"), _cuda(w, "linear w"), _cuda(out, "linear out"), _code(out, "linear out"), n, m, k,
+                  epilogue, in_p, in_tiles, inv_w, eps, res, nw, out_p, status, _stream()), "gemm_stream")
 
     # rows up to which the weight-streaming kernel is used; above it the library GEMM takes over
     # (measured on B200 at the Qwen3-8B sizes: the streaming kernel wins up to 8 rows, cuBLAS from 16)
@@ -312,7 +336,10 @@ class CudaKernels:
             return
         if self.prefetcher is not None:
             self.prefetcher.before_product(self)
-        self.gemm_skinny(x, w, out, epilogue=1)
+        if self.STREAM_PRODUCT:
+            self._gemm_stream(x, w, out, n, w.shape[0], k, 1)
+        else:
+            self.gemm_skinny(x, w, out, epilogue=1)
         if self.weight_log is not None:
             self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
         if self.prefetcher is not None:
@@ -326,7 +353,10 @@ class CudaKernels:
             if n <= self.SKINNY_MAX_ROWS and k % 32 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
                 if self.prefetcher is not None:
                     self.prefetcher.before_product(self)
-                self.gemm_skinny(x, w, out)
+                if self.STREAM_PRODUCT:
+                    self._gemm_stream(x, w, out, n, m, k, 0)
+                else:
+                    self.gemm_skinny(x, w, out)
                 if self.weight_log is not None:
                     self.weight_log.append((w.data_ptr(), w.numel() * w.element_size()))
                 if self.prefetcher is not None:
@@ -436,7 +466,7 @@ class CudaKernels:
         code, where = t.tolist()
         if code != 0:
             t.zero_()
-            raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (wait {code}, iteration {where}); its result is not valid")
+            raise KernelError(f"a kernel gave up waiting on a barrier (wait {code}, iteration {where}); its result is not valid")
 
     TCGEN05_PAIR = os.environ.get("IIAN_TCGEN05_PAIR", "1") not in ("0", "false", "off")
 

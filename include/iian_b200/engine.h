@@ -109,12 +109,14 @@ struct RunnerOptions {
     int decode_stages = 2;
     int max_splits = 32;
     int decode_ctas_per_sm = 2;
+    bool stream_product = true;     // products of up to 8 rows: weights through shared memory by bulk copies (gemm_stream.cu)
+    int stream_stages = 12;         // 12: one CTA per SM with the deep ring; 6: two CTAs per SM
 };
 
 // Paths of the kernel libraries (one shared object per source, see iian_b200/csrc/build.py); empty: not needed.
 struct KernelLibraries {
     std::string elementwise, rope_kv, attention_generic, gemm_simt, sampling, gemm_skinny, attention_mma, prefetch,
-        gemm_tcgen05, attention_tc;
+        gemm_tcgen05, attention_tc, gemm_stream;
 };
 
 class StepFunction {

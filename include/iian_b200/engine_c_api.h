@@ -36,13 +36,14 @@ typedef struct {
 
 typedef struct {
     int max_num_seqs, max_model_len, cuda_graphs, weight_prefetch, prefetch_window_mb, tcgen05_min_tiles, library_gemm_only,
-        fuse_norm, fused_decode, attention_tc, cluster_merge, tcgen05_pair, decode_stages, max_splits, decode_ctas_per_sm;
+        fuse_norm, fused_decode, attention_tc, cluster_merge, tcgen05_pair, decode_stages, max_splits, decode_ctas_per_sm,
+        stream_product, stream_stages;
 } IianRunnerOptions;
 
 const char * iian_engine_last_error(void);
 
 // libs: paths of the kernel libraries in the order elementwise, rope_kv, attention_generic, gemm_simt, sampling,
-// gemm_skinny, attention_mma, prefetch, gemm_tcgen05, attention_tc (null or "": not needed); cache: a cache manager
+// gemm_skinny, attention_mma, prefetch, gemm_tcgen05, attention_tc, gemm_stream (null or "": not needed); cache: a cache manager
 // of the host runtime (iian_cache_new).  Null on failure.
 void * iian_runner_new(const IianModel * model, const char * const * libs, void * cache, const IianRunnerOptions * opt);
 void iian_runner_delete(void * runner);

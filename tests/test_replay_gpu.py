@@ -93,11 +93,11 @@ def test_cutting_does_not_change_logits(folders, plains, name, dtype, mode):
 # by the way its work was cut (ops.cuda_backend.LAUNCHES_BY_ENTRY); the general attention kernel must not appear
 SERVED_BY = {
     ("D", "whole"): {"attention_tc", "gemm_tcgen05"},                    # long portions: tcgen05 attention and products
-    ("D", "tail"): {"attention_tc", "attention_decode_fused", "gemm_skinny_fused"},
+    ("D", "tail"): {"attention_tc", "attention_decode_fused", "gemm_stream"},
     ("D", "portions"): {"attention_tc", "attention_mma"},               # portions under 16 tokens go to mma.sync
-    ("D", "mixed"): {"attention_decode_fused", "gemm_skinny_fused"},
+    ("D", "mixed"): {"attention_decode_fused", "gemm_stream"},
     ("E", "whole"): {"attention_mma", "gemm_tcgen05"},
-    ("E", "tail"): {"attention_mma", "attention_decode_fused", "gemm_skinny_fused"},
+    ("E", "tail"): {"attention_mma", "attention_decode_fused", "gemm_stream"},
     ("F", "mixed"): {"attention_mma", "attention_decode_fused"},
 }
 
@@ -105,7 +105,7 @@ SERVED_BY = {
 @pytest.mark.parametrize("case", sorted(SERVED_BY))
 @pytest.mark.parametrize("min_tiles", [0, 300])
 def test_the_serving_kernels_run_inside_whole_model_checks(folders, plains, monkeypatch, case, min_tiles):
-    """(``gemm_skinny_fused`` also stands for the plain ``gemm_skinny`` launch.)  The logits of D, E and F in bfloat16 come from the kernels that serve the large shapes, not from the general
+    """The logits of D, E and F in bfloat16 come from the kernels that serve the large shapes, not from the general
     ones -- with the own tcgen05 product from the first tile on (as the other tests run) and with the dispatch
     rule's default threshold, under which these small products go to the library instead."""
     from iian_b200.ops import cuda_backend
