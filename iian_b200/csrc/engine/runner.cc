@@ -870,6 +870,9 @@ NativeRunner::NativeRunner(const ModelDesc & model, const KernelLibraries & libs
             bind(h, "iian_gemm_stream", k.gemm_stream, libs.gemm_stream);
             bind(h, "iian_gemm_stream_stages", k.gemm_stream_stages, libs.gemm_stream);
             if (k.gemm_stream_stages(opt.stream_stages) != 0) fail("gemm_stream: the ring is chosen by 6 or 12");
+            void (*set_pdl)(int) = nullptr;
+            bind(h, "iian_set_pdl", set_pdl, libs.gemm_stream);
+            set_pdl(opt.pdl_stream ? 1 : 0);
         } else if (opt.stream_product) fail("the gemm_stream kernel library is required for bfloat16");
         cuda_ok(cudaMalloc(reinterpret_cast<void **>(&m.tc_status), 2 * sizeof(int)), "cudaMalloc (status)");
         cuda_ok(cudaMemset(m.tc_status, 0, 2 * sizeof(int)), "cudaMemset");

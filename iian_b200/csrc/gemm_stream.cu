@@ -104,16 +104,24 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(
         s_failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    const bool scaled = ex.in_partial != nullptr;
-    if (scaled && warp < GS_WARPS) {            // row n's factor: one warp adds its partial sums in a fixed order
-        for (int n = warp; n < B; n += GS_WARPS) {
-            float a = 0.0f;
-            for (int i = lane; i < ex.in_tiles; i += 32) a += ex.in_partial[(size_t) n * ex.in_tiles + i];
-            a = warp_sum(a);
-            if (lane == 0) s_rs[n] = rsqrtf(a * ex.inv_width + ex.eps);
-        }
-    }
     __syncthreads();
+    // Launched with programmatic stream serialization, this grid may start while the one before it drains: the
+    // producer fills the ring at once (weights do not depend on the kernel before), the consumers first wait for
+    // the grid before to complete.  The grid after this one may be launched as soon as SMs become free.
+    pdl_launch_dependents();
+    const bool scaled = ex.in_partial != nullptr;
+    if (warp < GS_WARPS) {
+        pdl_wait();
+        if (scaled) {                           // row n's factor: one warp adds its partial sums in a fixed order
+            for (int n = warp; n < B; n += GS_WARPS) {
+                float a = 0.0f;
+                for (int i = lane; i < ex.in_tiles; i += 32) a += ex.in_partial[(size_t) n * ex.in_tiles + i];
+                a = warp_sum(a);
+                if (lane == 0) s_rs[n] = rsqrtf(a * ex.inv_width + ex.eps);
+            }
+        }
+        gs_consumer_sync();
+    }
     volatile int * failed = &s_failed;
 
     if (warp == GS_WARPS) {

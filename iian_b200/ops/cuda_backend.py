@@ -92,12 +92,21 @@ class pin_stream:
 _sigs_done = set()
 
 
-# Programmatic dependent launch for the decode-path kernels (see csrc/common.cuh).  Measured on the whole
-# decode step it does not pay (4.57 ms against 4.33 ms at batch 8), so it is off unless IIAN_PDL=1.
-# IIAN_PDL may also name the kernel libraries whose launches get the attribute ("gemm_skinny,attention_mma").
-_PDL_ENV = os.environ.get("IIAN_PDL", "0")
+# Programmatic dependent launch (see csrc/common.cuh).  IIAN_PDL names the kernel libraries whose launches get the
+# attribute ("gemm_stream,attention_mma"; "1": all, "0": none).  Default: the streaming product alone.  Its CTAs fill
+# their ring of shared memory with weights while the kernel before drains, and they cannot crowd that kernel out (a CTA
+# takes nearly all of an SM's shared memory, so it only becomes resident where one has left): 3.10 -> 2.91 ms per decode
+# step at batch 1, 3.60 -> 3.31 at batch 8.  With the attribute on every kernel of the step the register-bound kernels
+# of the chain did lose resources to their successors (4.16 ms at batch 1 when the products were of that kind).
+_PDL_ENV = os.environ.get("IIAN_PDL", "gemm_stream")
 PDL = _PDL_ENV not in ("0", "false", "off")
 _PDL_LIBS = None if _PDL_ENV in ("0", "false", "off", "1", "true", "on") else {n.strip() for n in _PDL_ENV.split(",")}
+
+
+def pdl_for(lib_name: str) -> bool:
+    return PDL and (_PDL_LIBS is None or lib_name in _PDL_LIBS)
+
+
 _pdl_set = set()
 
 
@@ -108,7 +117,7 @@ def _fn(lib_name: str, fn_name: str, argtypes):
         if hasattr(lib, "iian_set_pdl"):
             lib.iian_set_pdl.argtypes = [c_int]
             lib.iian_set_pdl.restype = None
-            lib.iian_set_pdl(1 if PDL and (_PDL_LIBS is None or lib_name in _PDL_LIBS) else 0)
+            lib.iian_set_pdl(1 if pdl_for(lib_name) else 0)
     fn = getattr(lib, fn_name)
     key = (lib_name, fn_name)
     if key not in _sigs_done:

@@ -97,7 +97,7 @@ struct RunnerOptions {
     int max_num_seqs = 4;
     int max_model_len = 0;          // sizes the block tables of captured graphs
     bool cuda_graphs = false;
-    bool weight_prefetch = true;
+    bool weight_prefetch = false;   // L2 prefetch of the next weights on a side stream inside captured graphs
     int prefetch_window_mb = 8;
     int tcgen05_min_tiles = 300;    // the own tcgen05 product from this many tiles of 256 x 256 on (else the library)
     bool library_gemm_only = false;
@@ -111,6 +111,7 @@ struct RunnerOptions {
     int decode_ctas_per_sm = 2;
     bool stream_product = true;     // products of up to 8 rows: weights through shared memory by bulk copies (gemm_stream.cu)
     int stream_stages = 12;         // 12: one CTA per SM with the deep ring; 6: two CTAs per SM
+    bool pdl_stream = true;         // launch the streaming product with programmatic stream serialization
 };
 
 // Paths of the kernel libraries (one shared object per source, see iian_b200/csrc/build.py); empty: not needed.
