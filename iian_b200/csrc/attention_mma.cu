@@ -362,9 +362,9 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
 // instead of prepared heads.  Every CTA normalises and rotates the query heads of its KV head itself
 // (src/iian/arch/qwen3.cpp:80-87: RMSNorm over the head, then NEOX rotation), with the arithmetic of
 // rope_kv.cu in the same order, so both routes give the same bits.  The CTA whose key range holds the
-// token's own position also normalises and rotates the new key, writes it and the new value to the cache,
-// fences, and only then copies that tile: it reads its own write.  This saves a launch and a round trip of
-// Q through memory.
+// token's own position also normalises and rotates the new key, writes it and the new value to the cache for
+// later steps, and puts both from shared memory into the tile they belong to after that tile's copy has landed:
+// no fence and no reading back lie on the path.  This saves a launch and a round trip of Q through memory.
 // STAGES: tiles of shared memory per CTA.  Three keep two tiles in flight; two leave room for a third CTA
 // on the SM, which pays when a step's CTAs then fit the GPU at once with fewer tiles each.
 template <int HD, bool CLUSTER, bool FUSED, int STAGES>
@@ -468,6 +468,10 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
         for (int st = 0; st < STAGES; st++) lookup_rows(tile_begin + st, st);
     }
     pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 s_new[2][HD];      // FUSED: the new key and value of the token (owner CTA)
+    const int new_tile = k_hi / BN - tile_begin;              // FUSED: which of this CTA's tiles holds the token's own position
+    const bool owner = FUSED && new_tile >= 0 && new_tile < n_my;
+    bool patch = false;
     if (n_my > 0) {
         __syncthreads();
         if (!FUSED) {
@@ -481,10 +485,10 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
             load_ahead();
         } else {
             // (one token per sequence: q_len 1, rows_total G <= 16, row0 0, k_hi the token's position)
-            const int new_tile = k_hi / BN - tile_begin;              // which of this CTA's tiles holds the new key
-            const bool owner = new_tile >= 0 && new_tile < n_my;
-            const bool late = owner && new_tile < STAGES - 1;         // that tile is among those copied up front
-            if (!late) load_ahead();
+            // The CTA whose keys include the token's own position makes the new key and value itself: they go to the
+            // cache for later steps and, through shared memory, straight into the tile they belong to once that tile's
+            // copy has landed (the copy brings whatever the cell held before) -- no fence, no reading back.
+            load_ahead();
             constexpr int half = HD / 2;
             const int heads_total = p.nh + 2 * p.nkv;
             const __nv_bfloat16 * tok_in = p.qkv + (size_t) q0 * heads_total * HD;
@@ -533,20 +537,25 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
             if (owner && p.write_kv) {
                 const int slot = p.slots[q0];
                 if (slot >= 0 && slot < p.num_pages * p.page_size) {
-                    const int page = slot / p.page_size, off = slot - page * p.page_size;
-                    const size_t cell = (((size_t) page * p.nkv + kvh) * p.page_size + off) * HD;
+                    patch = true;
                     if (warp == 0) {
                         const __nv_bfloat16 * src = tok_in + (size_t) (p.nh + kvh) * HD;
-                        norm_rope(src, p.k_weight, tab != nullptr, p.k_cache_w + cell + p0, p.k_cache_w + cell + half + p0);
+                        norm_rope(src, p.k_weight, tab != nullptr, s_new[0] + p0, s_new[0] + half + p0);
                     } else if (warp == 1) {
                         const __nv_bfloat16 * src = tok_in + (size_t) (p.nh + p.nkv + kvh) * HD;
-                        if (lane < CH) *reinterpret_cast<uint4 *>(p.v_cache_w + cell + lane * 8) = *reinterpret_cast<const uint4 *>(src + lane * 8);
+                        if (lane < CH) *reinterpret_cast<uint4 *>(s_new[1] + lane * 8) = *reinterpret_cast<const uint4 *>(src + lane * 8);
                     }
-                    __threadfence();          // the copies below read these rows back through L2
                 }
             }
             __syncthreads();
-            if (late) load_ahead();
+            if (patch && tid < 2 * CH) {                     // the new rows into the cache, 16 bytes a thread
+                const int slot = p.slots[q0];
+                const int page = slot / p.page_size, off = slot - page * p.page_size;
+                const size_t cell = (((size_t) page * p.nkv + kvh) * p.page_size + off) * HD;
+                const int which = tid / CH, ch = tid % CH;
+                __nv_bfloat16 * dst = (which == 0 ? p.k_cache_w : p.v_cache_w) + cell + ch * 8;
+                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(s_new[which] + ch * 8);
+            }
         }
 
         unsigned qf[KS][4];
@@ -555,6 +564,14 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
             cp_async_commit();
             cp_async_wait<STAGES - 1>();
             __syncthreads();
+            if (FUSED && patch && i == new_tile) {               // the token's own key and value replace what the copy brought
+                if (tid < 2 * CH) {
+                    const int which = tid / CH, ch = tid % CH;
+                    unsigned char * tile = (which == 0 ? sK : sV) + (i % STAGES) * TILE_BYTES;
+                    *reinterpret_cast<uint4 *>(tile + swz<HD>(k_hi % BN, ch)) = *reinterpret_cast<const uint4 *>(s_new[which] + ch * 8);
+                }
+                __syncthreads();
+            }
             lookup_rows(tile_begin + i + STAGES, i % STAGES);    // this tile's copies were issued earlier
             if (i == 0) {
 #pragma unroll

@@ -268,7 +268,7 @@ struct NativeRunner::Impl {
         const int base = std::max(1, num_seqs * num_kv_heads);
         const int slots = opt.decode_ctas_per_sm * sm_count;
         int n = std::max(1, std::min(std::min(slots / base, (tiles + 1) / 2), opt.max_splits));
-        if (n > 8 && (n < 12 || tiles < 64)) n = 8;
+        if (n > 8 && (n < 12 || tiles < 256)) n = 8;
         return n;
     }
 

@@ -675,13 +675,14 @@ class CudaKernels:
         wave repeats the whole chain of dependent loads), and a CTA should keep at least two key tiles.  Up to
         8 parts merge inside a thread-block cluster, which saves three trips through L2 (write the parts, count
         arrivals, read them back: 3.36 -> 3.23 ms per step at batch 1 and 1k context), so more than 8 parts are
-        only taken when each still gets four tiles or more (contexts beyond 4k); 9 to 11 are rounded down to 8."""
+        only taken beyond 16k of context (at 4k, 32 parts merged through scratch memory cost 3.63 ms a step at batch 1
+        where 8 parts in a cluster take about 3.2); 9 to 11 are rounded down to 8."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
         if os.environ.get("IIAN_DECODE_FORCE_SPLITS"):
             return int(os.environ["IIAN_DECODE_FORCE_SPLITS"])
         n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 2), self.MAX_SPLITS))
-        if n > 8 and (n < 12 or tiles < 64):
+        if n > 8 and (n < 12 or tiles < 256):
             n = 8
         return n
 
