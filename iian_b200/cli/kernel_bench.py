@@ -36,6 +36,8 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--prefix", type=int, default=0, help="attention_prefill: tokens of the sequence already in the cache before the portion")
+    ap.add_argument("--seqs", type=int, default=1, help="attention_prefill: sequences that each bring such a portion")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -182,8 +184,8 @@ def main(argv=None) -> int:
         return 0
     if args.kernel in ("attention_decode", "attention_prefill"):
         decode = args.kernel == "attention_decode"
-        seqs = args.batch if decode else 1
-        ctx_len = args.ctx if decode else args.tokens
+        seqs = args.batch if decode else args.seqs
+        ctx_len = args.ctx if decode else args.tokens + args.prefix
         q_len = 1 if decode else args.tokens
         blocks = math.ceil(ctx_len / ps)
         n_pages = seqs * blocks
@@ -214,8 +216,9 @@ def main(argv=None) -> int:
             print(f"attention_decode batch {seqs} ctx {ctx_len} heads {nh}/{nkv} x {hd}: {us:.1f} us, {gb / (us * 1e-6):.0f} GB/s of K/V "
                   f"(splits {args.splits or k.attention_splits(seqs, nkv, ctx_len)})")
         else:
-            tf = 4.0 * nh * hd * q_len * (q_len + 1) / 2 / 1e12
-            print(f"attention_prefill tokens {q_len} heads {nh}/{nkv} x {hd}: {us:.1f} us, {tf / (us * 1e-6):.0f} TFLOP/s (causal)")
+            tf = seqs * 4.0 * nh * hd * (q_len * (q_len + 1) / 2 + q_len * args.prefix) / 1e12
+            print(f"attention_prefill {seqs} x {q_len} tokens after {args.prefix} heads {nh}/{nkv} x {hd}: {us:.1f} us, "
+                  f"{tf / (us * 1e-6):.0f} TFLOP/s (causal)")
         return 0
 
     n = args.rows

@@ -196,7 +196,7 @@ def decode_and_prefill_points(model, batches: Sequence[int], prompt_len: int, st
     max_b = max(batches) if batches else 1
     per_req = prompt_len + warmup + steps + 48
     longest = max([per_req] + list(prefill_tokens))
-    max_len = max(context_len, longest + 16)
+    max_len = -(-max(context_len, longest + 16) // 16) * 16       # whole pages
     ecfg = EngineConfig(dtype="bfloat16", max_model_len=max_len, kv_cache_tokens=max(max_len, max_b * per_req),
                         block_size=16, enable_prefix_caching=False, warmup=True, cuda_graphs=cuda_graphs,
                         sched=SchedulerConfig(max_num_seqs=max(1, max_b), max_num_batched_tokens=max(2048, longest)))

@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     unsigned char * sQ = smem;                               // [2 groups][2 halves][128 rows][128 B]
     unsigned char * sK = sQ + 2 * AT_TILE_BYTES;             // [2 stages][2 halves][128 keys][128 B]
     unsigned char * sV = sK + 2 * AT_TILE_BYTES;             // [2 stages][2 halves][128 keys][128 B]
-    __shared__ __align__(8) unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
+    __shared__ __align__(8) unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2], q_full;
     __shared__ unsigned tmem_base_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -200,66 +200,110 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             at_mbar_init(at_smem(&v_full[g]), 1); at_mbar_init(at_smem(&v_empty[g]), 1);
             at_mbar_init(at_smem(&p_full[g]), 4); at_mbar_init(at_smem(&pv_done[g]), 1);
         }
+        at_mbar_init(at_smem(&q_full), AT_THREADS / 32 - 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {          // the producer's first reads: the descriptors and the block table's first entries
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        }
+        const int j0 = tile_lo * AT_BN + lane * p.page_size;
+        if (lane < AT_BN / p.page_size && j0 <= k_hi) asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + j0 / p.page_size));
     }
     if (warp == 1) {          // tensor memory: S of both groups (2 x 128 columns), O of both groups (2 x 128 columns)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_base_s)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q rows into the swizzled K-major layout: row r, 16-byte chunk c of half h at h * 16 KB + r * 128 + ((c ^ (r & 7)) << 4)
-    for (int idx = threadIdx.x; idx < AT_ROWS * 16; idx += AT_THREADS) {
-        const int rr = idx >> 4, c = idx & 15;
-        const int g = rr >> 7, r = rr & 127;
-        const int R = row0 + rr;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (R < rows_total) {
-            const int tok = R / G, head = kvh * G + R % G;
-            v = *reinterpret_cast<const uint4 *>(p.q + ((size_t) (q0 + tok) * p.nh + head) * AT_HD + c * 8);
-        }
-        *reinterpret_cast<uint4 *>(sQ + g * AT_TILE_BYTES + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-    }
-    at_fence_async_smem();
     at_fence_before();
     __syncthreads();
     at_fence_after();
     const unsigned tmem_base = tmem_base_s;
 
+    if (warp > 0) {
+        // Q rows into the swizzled K-major layout: row r, 16-byte chunk c of half h at h * 16 KB + r * 128 + ((c ^ (r & 7)) << 4).
+        // Every warp but the producer takes part, meanwhile the producer's first K and V tiles are on their way; the
+        // loads of a pass are all issued before the first is stored, so that a pass costs one trip to memory.
+        constexpr int kLoaders = AT_THREADS - 32, kPass = 8;
+        const int t = threadIdx.x - 32;
+        for (int base = 0; base < AT_ROWS * 16; base += kLoaders * kPass) {
+            uint4 buf[kPass];
+#pragma unroll
+            for (int u = 0; u < kPass; u++) {
+                const int idx = base + u * kLoaders + t;
+                const int rr = idx >> 4, c = idx & 15;
+                const int R = row0 + rr;
+                buf[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (idx < AT_ROWS * 16 && R < rows_total) {
+                    const int tok = R / G, head = kvh * G + R % G;
+                    buf[u] = *reinterpret_cast<const uint4 *>(p.q + ((size_t) (q0 + tok) * p.nh + head) * AT_HD + c * 8);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kPass; u++) {
+                const int idx = base + u * kLoaders + t;
+                if (idx < AT_ROWS * 16) {
+                    const int rr = idx >> 4, c = idx & 15;
+                    const int g = rr >> 7, r = rr & 127;
+                    *reinterpret_cast<uint4 *>(sQ + g * AT_TILE_BYTES + (c >> 3) * AT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = buf[u];
+                }
+            }
+        }
+        at_fence_async_smem();
+        __syncwarp();
+        if (lane == 0) at_arrive(at_smem(&q_full));
+    }
+
     if (warp == 0) {
-        // ---- producer: lane g fetches page g of a tile (two boxes: the halves of the head); lane 0 posts the byte
-        // count.  Two stages each for K and V.
+        // ---- producer: per step the K tile of the next key tile (lanes 0..15, a lane per page) and the V tile of this
+        // one (lanes 16..31), each page as two boxes (the halves of the head); lanes 0 and 16 wait for the stage to
+        // be free and post the byte counts.  Two stages each for K and V; K runs a tile ahead of V.  The block table
+        // is read three steps ahead, so that a step costs no trip to memory.
         const int ps = p.page_size, pages_per_tile = AT_BN / ps;
-        auto load_tile = [&](int i, bool is_k) -> bool {
-            const int tile = tile_lo + i, st = i & 1;
-            const unsigned ph = (unsigned) (i >> 1) & 1u;
+        const int lp = lane & 15;
+        const bool k_lane = lane < 16;
+        auto page_of = [&](int i) -> int {
             int page = p.num_pages;                          // out of range: the box is filled with zeros
-            if (lane < pages_per_tile) {
-                const int j0 = tile * AT_BN + lane * ps;
+            if (i < n_tiles && lp < pages_per_tile) {
+                const int j0 = (tile_lo + i) * AT_BN + lp * ps;
                 if (j0 <= k_hi) {
                     const int pg = bt[j0 / ps];
                     if (pg >= 0 && pg < p.num_pages) page = pg;
                 }
             }
-            const unsigned empty = at_smem(is_k ? &k_empty[st] : &v_empty[st]), full = at_smem(is_k ? &k_full[st] : &v_full[st]);
-            int ok = 1;
-            if (lane == 0) {
-                ok = at_wait(empty, ph ^ 1u) ? 1 : 0;
-                if (!ok) { status[0] = is_k ? 1 : 2; status[1] = i; }
-                else at_expect_tx(full, AT_TILE_BYTES);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return false;
-            if (lane < pages_per_tile) {
-                unsigned char * base = (is_k ? sK : sV) + st * AT_TILE_BYTES + lane * ps * 128;
-                const CUtensorMap * map = is_k ? &map_k : &map_v;
-                at_tma_4d(at_smem(base), map, 0, 0, kvh, page, full);
-                at_tma_4d(at_smem(base + AT_HALF_BYTES), map, 64, 0, kvh, page, full);
-            }
-            return true;
+            return page;
         };
-        bool ok = load_tile(0, true);
-        for (int i = 0; ok && i < n_tiles; i++) {
-            if (i + 1 < n_tiles) ok = load_tile(i + 1, true);      // K runs a tile ahead of V
-            if (ok) ok = load_tile(i, false);
+        int pg_v = p.num_pages, pg_k = page_of(0), pg_k1 = page_of(1);
+        for (int i = -1; i < n_tiles; i++) {
+            const int pg_k2 = page_of(i + 3);
+            const bool do_k = i + 1 < n_tiles, do_v = i >= 0;
+            int ok = 1;
+            if (lane == 0 && do_k) {
+                const int t = i + 1;
+                ok = at_wait(at_smem(&k_empty[t & 1]), ((unsigned) (t >> 1) & 1u) ^ 1u) ? 1 : 0;
+                if (!ok) { status[0] = 1; status[1] = t; }
+                else at_expect_tx(at_smem(&k_full[t & 1]), AT_TILE_BYTES);
+            }
+            if (lane == 16 && do_v) {
+                ok = at_wait(at_smem(&v_empty[i & 1]), ((unsigned) (i >> 1) & 1u) ^ 1u) ? 1 : 0;
+                if (!ok) { status[0] = 2; status[1] = i; }
+                else at_expect_tx(at_smem(&v_full[i & 1]), AT_TILE_BYTES);
+            }
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (lp < pages_per_tile) {
+                if (k_lane && do_k) {
+                    const int st = (i + 1) & 1;
+                    unsigned char * base = sK + st * AT_TILE_BYTES + lp * ps * 128;
+                    at_tma_4d(at_smem(base), &map_k, 0, 0, kvh, pg_k, at_smem(&k_full[st]));
+                    at_tma_4d(at_smem(base + AT_HALF_BYTES), &map_k, 64, 0, kvh, pg_k, at_smem(&k_full[st]));
+                } else if (!k_lane && do_v) {
+                    const int st = i & 1;
+                    unsigned char * base = sV + st * AT_TILE_BYTES + lp * ps * 128;
+                    at_tma_4d(at_smem(base), &map_v, 0, 0, kvh, pg_v, at_smem(&v_full[st]));
+                    at_tma_4d(at_smem(base + AT_HALF_BYTES), &map_v, 64, 0, kvh, pg_v, at_smem(&v_full[st]));
+                }
+            }
+            pg_v = pg_k; pg_k = pg_k1; pg_k1 = pg_k2;
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer -----------------------------------------------------------------------------------
@@ -281,6 +325,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             }
             at_commit(at_smem(&s_full[g]));
         };
+        if (!at_wait(at_smem(&q_full), 0u)) { status[0] = 4; status[1] = 0; goto done; }
         if (!at_wait(at_smem(&k_full[0]), 0u)) { status[0] = 3; status[1] = 0; goto done; }
         at_fence_after();
         for (int g = 0; g < 2; g++)
@@ -333,9 +378,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             const int hi = row_ok ? min(AT_BN - 1, row_pos - key0) : -1;
             const int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : 0;
             if (!__all_sync(0xffffffffu, lo <= 0 && hi >= AT_BN - 1)) {
+                if (p.window > 0) {
 #pragma unroll
-                for (int j = 0; j < AT_BN; j++)
-                    if (j < lo || j > hi) v[j] = 0xff800000u;        // -inf
+                    for (int j = 0; j < AT_BN; j++)
+                        if (j < lo || j > hi) v[j] = 0xff800000u;        // -inf
+                } else {
+#pragma unroll
+                    for (int j = 0; j < AT_BN; j++)
+                        if (j > hi) v[j] = 0xff800000u;
+                }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -411,23 +462,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                     const int tok = R / G, head = kvh * G + R % G;
                     dst = p.out + ((size_t) (q0 + tok) * p.nh + head) * AT_HD;
                 }
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_HD; c0 += 32) {
-                    unsigned o[32];
-                    at_ld32(tO + lane_addr + (unsigned) c0, o);
-                    at_wait_ld();
-                    if (row_ok) {
+                unsigned o[AT_HD];                  // the whole row at once: one wait for four loads
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; q4++) {
-                            uint4 pk;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 0]) * inv, __uint_as_float(o[8 * q4 + 1]) * inv);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 2]) * inv, __uint_as_float(o[8 * q4 + 3]) * inv);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 4]) * inv, __uint_as_float(o[8 * q4 + 5]) * inv);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[8 * q4 + 6]) * inv, __uint_as_float(o[8 * q4 + 7]) * inv);
-                            pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
-                            pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
-                            *reinterpret_cast<uint4 *>(dst + c0 + 8 * q4) = pk;
-                        }
+                for (int c0 = 0; c0 < AT_HD; c0 += 32) at_ld32(tO + lane_addr + (unsigned) c0, o + c0);
+                at_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int q8 = 0; q8 < AT_HD / 8; q8++) {
+                        uint4 pk;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 0]) * inv, __uint_as_float(o[8 * q8 + 1]) * inv);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 2]) * inv, __uint_as_float(o[8 * q8 + 3]) * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 4]) * inv, __uint_as_float(o[8 * q8 + 5]) * inv);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 6]) * inv, __uint_as_float(o[8 * q8 + 7]) * inv);
+                        pk.x = *reinterpret_cast<unsigned *>(&h0); pk.y = *reinterpret_cast<unsigned *>(&h1);
+                        pk.z = *reinterpret_cast<unsigned *>(&h2); pk.w = *reinterpret_cast<unsigned *>(&h3);
+                        *reinterpret_cast<uint4 *>(dst + 8 * q8) = pk;
                     }
                 }
             } else if (lane == 0) {
