@@ -94,6 +94,12 @@ __device__ __forceinline__ float block_sum(float v, float * scratch) {
     return t;
 }
 
+// Rotation of a pair by an angle: x cos - y sin and x sin + y cos, each as one rounded product and one fused
+// multiply-add, spelled out so that every kernel that rotates (the rotation kernel's forms, the fused decode
+// kernels) gives the same bits whatever the compiler would have contracted.
+__device__ __forceinline__ float rot_lo(float x, float y, float cs, float sn) { return __fmaf_rn(x, cs, -__fmul_rn(y, sn)); }
+__device__ __forceinline__ float rot_hi(float x, float y, float cs, float sn) { return __fmaf_rn(x, sn, __fmul_rn(y, cs)); }
+
 // 8 bf16 (16 bytes) -> 8 floats
 __device__ __forceinline__ void unpack8(const uint4 & raw, float * f) {
     const __nv_bfloat162 * p = reinterpret_cast<const __nv_bfloat162 *>(&raw);

@@ -109,8 +109,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_fast_k
             }
             if (rotate) {
                 const float4 cssn = *reinterpret_cast<const float4 *>(table + (size_t) t * half + p0);   // cos0 sin0 cos1 sin1
-                const float2 r0 = make_float2(a.x * cssn.x - c.x * cssn.y, a.y * cssn.z - c.y * cssn.w);
-                const float2 r1 = make_float2(a.x * cssn.y + c.x * cssn.x, a.y * cssn.w + c.y * cssn.z);
+                const float2 r0 = make_float2(rot_lo(a.x, c.x, cssn.x, cssn.y), rot_lo(a.y, c.y, cssn.z, cssn.w));
+                const float2 r1 = make_float2(rot_hi(a.x, c.x, cssn.x, cssn.y), rot_hi(a.y, c.y, cssn.z, cssn.w));
                 a = r0; c = r1;
             }
             Pair<A>::store(dst + p0, a);
@@ -181,8 +181,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_wide_k
             }
         }
         if ((is_q || is_k) && table != nullptr) {
-            const float2 r0 = make_float2(a.x * cssn.x - c.x * cssn.y, a.y * cssn.z - c.y * cssn.w);
-            const float2 r1 = make_float2(a.x * cssn.y + c.x * cssn.x, a.y * cssn.w + c.y * cssn.z);
+            const float2 r0 = make_float2(rot_lo(a.x, c.x, cssn.x, cssn.y), rot_lo(a.y, c.y, cssn.z, cssn.w));
+            const float2 r1 = make_float2(rot_hi(a.x, c.x, cssn.x, cssn.y), rot_hi(a.y, c.y, cssn.z, cssn.w));
             a = r0; c = r1;
         }
         if (mine) {
@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_vec128
         if ((is_q || is_k) && table != nullptr) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const float r0 = a[i] * cs[i] - c[i] * sn[i], r1 = a[i] * sn[i] + c[i] * cs[i];
+                const float r0 = rot_lo(a[i], c[i], cs[i], sn[i]), r1 = rot_hi(a[i], c[i], cs[i], sn[i]);
                 a[i] = r0; c[i] = r1;
             }
         }
@@ -372,8 +372,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) qk_norm_rope_store_kernel
             float sn, cs;
             if (table != nullptr) { const float2 e = table[(size_t) t * half + p]; cs = e.x; sn = e.y; }
             else sincosf(pos * inv_freq[p], &sn, &cs);
-            dst[i0] = from_f32<A>(a0 * cs - a1 * sn);
-            dst[i1] = from_f32<A>(a0 * sn + a1 * cs);
+            dst[i0] = from_f32<A>(rot_lo(a0, a1, cs, sn));
+            dst[i1] = from_f32<A>(rot_hi(a0, a1, cs, sn));
         }
     }
 #pragma unroll

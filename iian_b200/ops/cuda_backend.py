@@ -735,19 +735,45 @@ class CudaKernels:
             if small_tiles:
                 row_tiles = -(-meta.max_q_len * (num_heads // num_kv_heads) // 16)
                 counters = self.attention_counters(q.device, meta.num_seqs * num_kv_heads * row_tiles).data_ptr()
+        elif n_split == 1 and small_tiles and meta.max_q_len == 1 and head_dim == 128:
+            part_o, counters = self._stream_scratch(q.device, meta.num_seqs * num_kv_heads)
         bt = meta.block_table
         fn = _fn("attention_mma", "iian_attention_mma",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
         _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
                   part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
                   num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split,
-                  (2 if cluster else 1) if small_tiles else 0, _stream()), "attention_mma")
+                  (2 if cluster else 1) if small_tiles else 0, self._decode_status(q.device) if small_tiles else None,
+                  _stream()), "attention_mma")
         if n_split > 1 and not small_tiles:
             LAUNCHES[0] += 1
 
     FUSED_DECODE = os.environ.get("IIAN_FUSED_DECODE_ATTENTION", "1") not in ("0", "false", "off")
+    # decode attention fetches its K/V tiles by TMA (head size 128, pages of 8 to 64 tokens); IIAN_DECODE_TMA=0: cp.async
+    DECODE_TMA = os.environ.get("IIAN_DECODE_TMA", "1") not in ("0", "false", "off")
+
+    # unsplit decode attention walks the key tiles of all (sequence, KV head) pairs as one line shared out evenly
+    # over the resident CTAs (attention_decode_stream_kernel); IIAN_DECODE_STREAM=0: a CTA per pair
+    DECODE_STREAM = os.environ.get("IIAN_DECODE_STREAM", "1") not in ("0", "false", "off")
+
+    def _stream_scratch(self, device, pairs: int):
+        """Scratch and counters for the stream form of the decode kernel, (0, 0) when it is switched off: without
+        them the kernel takes the form with a CTA per pair."""
+        if not (self.DECODE_TMA and self.DECODE_STREAM):
+            return 0, 0
+        fn = _fn("attention_mma", "iian_attention_stream_scratch", [])
+        scratch = self.attention_scratch(device, int(fn()))
+        return scratch.data_ptr(), self.attention_counters(device, pairs).data_ptr()
+
+    def _decode_status(self, device):
+        """The status words the decode kernel's TMA form reports to (the ones of the tcgen05 kernels), or None: the
+        cp.async form."""
+        if not self.DECODE_TMA:
+            return None
+        CudaKernels._tc_used = True
+        return self.tcgen05_status_buffer(device).data_ptr()
 
     def can_fuse_decode_attention(self, qkv, meta, *, num_heads, num_kv_heads, head_dim, rot_dim, rope_style, bias) -> bool:
         """Whether ``attention_decode_fused`` covers this step: one token per sequence, bfloat16, heads of 64 or
@@ -786,18 +812,20 @@ class CudaKernels:
             part_o = scratch.data_ptr()
             part_lse = part_o + rows * n_split * head_dim * 4
             counters = self.attention_counters(qkv.device, s_ * num_kv_heads).data_ptr()
+        elif n_split == 1 and head_dim == 128:
+            part_o, counters = self._stream_scratch(qkv.device, s_ * num_kv_heads)
         bt = meta.block_table
         fn = _fn("attention_mma", "iian_attention_decode_fused",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                   c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                  c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p])
         _check(fn(_cuda(qkv, "qkv"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
                   part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], s_, num_heads, num_kv_heads, head_dim,
                   k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split, 1 if cluster else 0,
                   _cuda(q_weight, "q norm weight", torch.float32), _cuda(k_weight, "k norm weight", torch.float32),
                   _cuda(table, "rotation table", torch.float32), _cuda(slots, "slots", torch.int32), eps,
-                  1 if write_kv else 0, _stream()), "attention_decode_fused")
+                  1 if write_kv else 0, self._decode_status(qkv.device), _stream()), "attention_decode_fused")
 
     def paged_attention_generic(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale,
                                 window) -> None:
