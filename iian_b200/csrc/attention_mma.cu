@@ -897,464 +897,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
     if (tid == 0) *counter = 0;
 }
 
-// ---- decode attention, unsplit keys, as one stream of tiles -----------------------------------------------------
-// With many sequences in a step nobody's keys need splitting, but (sequence, KV head) pairs rarely come in multiples
-// of the CTAs a GPU holds at once: 512 pairs on 296 resident CTAs run as one full round and one round that is
-// three quarters empty, and sequences of unequal length leave the longest to finish alone.  This form lays the key
-// tiles of all pairs end to end (pair-major: sequence, KV head, tile) and gives each of the resident CTAs an equal
-// share of that line.  A CTA's share is a few segments, each a run of tiles of one pair; the TMA producer walks the
-// share without regard to segment borders, so the copies of the next pair are in flight while the last tiles of
-// this one are being multiplied.  A pair that lies wholly inside one share is finished there; one that is cut by a
-// border is written as parts (normalised partial output and log-sum-exp) to scratch memory, and the CTA that brings
-// its last part merges them.  One token per sequence (q_len 1), head size 128, up to 8 query heads per KV head, up to
-// 256 sequences, pages of 8 to 64 tokens.  A CTA writes at most two parts (the segment that opens its share and the
-// one that closes it), so the scratch arrays have two slots of 8 rows per CTA whatever the batch: p.part_o
-// [CTAs, 2, 8, HD] and p.part_lse [CTAs, 2, 8]; p.counters holds one zeroed counter per pair.
-constexpr int STREAM_MAX_SEQS = 256;
-
-template <int HD, bool FUSED, int STAGES>
-__global__ void __launch_bounds__(128, 2) attention_decode_stream_kernel(const AttnParams p, const __grid_constant__ KvMaps maps, const int S) {
-    constexpr int NW = 4, BM = 16;
-    constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
-    constexpr int TILE_BYTES = BN * HD * 2;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned char * smem = (unsigned char *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
-    unsigned char * sQ = smem;                               // [16][HD]
-    unsigned char * sK = sQ + BM * HD * 2;                   // [STAGES][2 halves][BN][128 B]
-    unsigned char * sV = sK + STAGES * TILE_BYTES;
-    __shared__ int s_cum[STREAM_MAX_SEQS + 1];               // tiles of the sequences before s
-    __shared__ int s_ctx[STREAM_MAX_SEQS];
-    __shared__ __align__(8) unsigned long long full_bar[STAGES];
-    __shared__ __align__(16) __nv_bfloat16 s_new[2][HD];
-    __shared__ int s_last;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g_ = lane >> 2, t_ = lane & 3;
-    const int G = p.nh / p.nkv;
-    const int page_shift = __ffs(p.page_size) - 1;           // a power of two here
-
-    // ---- the line of tiles: how many each sequence has, and this CTA's share of it -----------------------------
-    auto k_lo_of = [&](int ctx) { return p.window > 0 ? max(0, ctx - p.window) : 0; };
-    for (int s = tid; s < S; s += NW * 32) {
-        const int ctx = p.ctx_len[s];
-        s_ctx[s] = ctx;
-        s_cum[s + 1] = ctx > 0 ? (ctx - 1) / BN - k_lo_of(ctx) / BN + 1 : 0;
-    }
-    if (tid == 0) {
-        s_cum[0] = 0;
-#pragma unroll
-        for (int st = 0; st < STAGES; st++) dk_mbar_init(smem_u32(&full_bar[st]), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (warp == 0) {                                         // running sums, a lane a run of sequences
-        const int per = (S + 31) / 32, base = lane * per;
-        int sum = 0;
-        for (int i = 0; i < per; i++)
-            if (base + i < S) sum += s_cum[base + i + 1];
-        int incl = sum;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        int run = incl - sum;
-        for (int i = 0; i < per; i++)
-            if (base + i < S) { run += s_cum[base + i + 1]; s_cum[base + i + 1] = run; }
-    }
-    __syncthreads();
-    const long long T = (long long) s_cum[S] * p.nkv;
-    const long long C = min((long long) gridDim.x, T);
-    const long long c = blockIdx.x;
-    if (c >= C) return;
-    const long long f_begin = T * c / C, f_end = T * (c + 1) / C;
-    const int n_my = (int) (f_end - f_begin);                // >= 1: C <= T
-
-    // a place on the line: sequence, KV head, tile within the sequence's range
-    struct Cursor { int s, kvh, t, n, tile_lo, k_hi; };
-    auto set_seq = [&](Cursor & cur, int s) {
-        cur.s = s;
-        if (s < S) {
-            const int ctx = s_ctx[s];
-            cur.n = s_cum[s + 1] - s_cum[s];
-            cur.k_hi = ctx - 1;
-            cur.tile_lo = k_lo_of(ctx) / BN;
-        } else {
-            cur.n = 1; cur.k_hi = -1; cur.tile_lo = 0;
-        }
-    };
-    auto advance = [&](Cursor & cur, int by) {               // by <= tiles left in the pair
-        cur.t += by;
-        if (cur.t < cur.n) return;
-        cur.t = 0;
-        if (++cur.kvh < p.nkv) return;
-        cur.kvh = 0;
-        int s = cur.s + 1;
-        while (s < S && s_cum[s + 1] == s_cum[s]) s++;
-        set_seq(cur, s);
-    };
-    Cursor cc;                                               // where this CTA starts
-    {
-        int lo = 0, hi = S - 1;                              // the sequence whose tiles contain f_begin
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if ((long long) s_cum[mid] * p.nkv <= f_begin) lo = mid; else hi = mid - 1;
-        }
-        set_seq(cc, lo);
-        const int off = (int) (f_begin - (long long) s_cum[lo] * p.nkv);
-        cc.kvh = off / cc.n;
-        cc.t = off % cc.n;
-    }
-
-    // ---- producer state (warp 0): lane l fetches half l & 1 of the head, K or V by bit 1, page l >> 2 of a tile ----
-    const int ld_half = lane & 1, ld_which = (lane >> 1) & 1, ld_pg = lane >> 2;
-    const bool ld_lane = warp == 0 && ld_pg * p.page_size < BN;
-    auto page_at = [&](const Cursor & cur) -> int {
-        int page = p.num_pages;                              // out of range: the box is filled with zeros
-        if (ld_lane && cur.s < S) {
-            const int j0 = (cur.tile_lo + cur.t) * BN + ld_pg * p.page_size;
-            if (j0 <= cur.k_hi) {
-                const int pg = p.block_table[(size_t) cur.s * p.max_blocks + (j0 >> page_shift)];
-                if (pg >= 0 && pg < p.num_pages) page = pg;
-            }
-        }
-        return page;
-    };
-    auto tma_issue = [&](int stage, int page, int kvh) {     // warp 0, all lanes
-        const unsigned bar = smem_u32(&full_bar[stage]);
-        if (lane == 0) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage may have held a merge
-            dk_expect_tx(bar, 2 * TILE_BYTES);
-        }
-        __syncwarp();
-        if (ld_lane) {
-            unsigned char * base = (ld_which == 0 ? sK : sV) + stage * TILE_BYTES + ld_half * (BN * 128) + ld_pg * p.page_size * 128;
-            dk_tma_4d(smem_u32(base), ld_which == 0 ? &maps.k : &maps.v, ld_half * 64, 0, kvh, page, bar);
-        }
-    };
-    // the first STAGES tiles' pages; the walk then stays one look-up ahead of the copies
-    Cursor lc = cc;
-    int pg_q[STAGES], kvh_q[STAGES];
-#pragma unroll
-    for (int st = 0; st < STAGES; st++) {
-        pg_q[st] = page_at(lc);
-        kvh_q[st] = lc.kvh;
-        if (st + 1 < n_my) advance(lc, 1);
-    }
-    // (lc now stands at tile min(STAGES, n_my - 1) of the share; it is only used while tiles remain)
-    pdl_wait();
-    if (warp == 0) {
-#pragma unroll
-        for (int st = 0; st < STAGES - 1; st++)
-            if (st < n_my) tma_issue(st, pg_q[st], kvh_q[st]);
-    }
-    int pg_next = pg_q[STAGES - 1], kvh_next = kvh_q[STAGES - 1];
-
-    constexpr int half = HD / 2;
-    const int heads_total = p.nh + 2 * p.nkv;
-    const int p0 = 2 * lane;                                 // FUSED: a lane owns pairs p0 and p0 + 1
-    bool failed = false;
-    int i = 0;                                               // tiles of the share done so far
-    while (i < n_my) {
-        // ---- a segment: tiles cc.t .. cc.t + seg - 1 of pair (cc.s, cc.kvh) -------------------------------------
-        const int s = cc.s, kvh = cc.kvh;
-        const int slot = i == 0 ? 0 : 1;                     // of this CTA's two places in the scratch arrays
-        const int seg = min(cc.n - cc.t, n_my - i);
-        const bool seg_first = cc.t == 0, seg_last = cc.t + seg == cc.n;
-        const int k_hi = cc.k_hi;
-        const int q0 = p.cu_q[s];
-        bool patch = false;
-        if (!FUSED) {
-            for (int cidx = tid; cidx < BM * CH; cidx += NW * 32) {
-                const int r = cidx / CH, ch = cidx % CH;
-                const bool valid = r < G;
-                cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) q0 * p.nh + kvh * G + (valid ? r : 0)) * HD + ch * 8, valid);
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-        } else {
-            const __nv_bfloat16 * tok_in = p.qkv + (size_t) q0 * heads_total * HD;
-            const float2 * tab = p.table != nullptr ? p.table + (size_t) q0 * half : nullptr;
-            auto norm_rope = [&](const __nv_bfloat16 * src, const float * w, bool rotate, __nv_bfloat16 * dst0, __nv_bfloat16 * dst1) {
-                float2 a = make_float2(0.0f, 0.0f), b = make_float2(0.0f, 0.0f);
-                float ss = 0.0f;
-                if (p0 < half) {
-                    a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(src + p0));
-                    b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(src + half + p0));
-                    ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
-                }
-                float inv = 1.0f;
-                if (w != nullptr) {
-                    ss = warp_sum(ss);
-                    inv = rsqrtf(ss / (float) HD + p.eps);
-                }
-                if (p0 < half) {
-                    if (w != nullptr) {
-                        const float2 wl = *reinterpret_cast<const float2 *>(w + p0), wh = *reinterpret_cast<const float2 *>(w + half + p0);
-                        a.x = a.x * inv * wl.x; a.y = a.y * inv * wl.y;
-                        b.x = b.x * inv * wh.x; b.y = b.y * inv * wh.y;
-                    }
-                    if (rotate) {
-                        const float4 cssn = *reinterpret_cast<const float4 *>(tab + p0);      // cos0 sin0 cos1 sin1
-                        const float2 r0 = make_float2(rot_lo(a.x, b.x, cssn.x, cssn.y), rot_lo(a.y, b.y, cssn.z, cssn.w));
-                        const float2 r1 = make_float2(rot_hi(a.x, b.x, cssn.x, cssn.y), rot_hi(a.y, b.y, cssn.z, cssn.w));
-                        a = r0; b = r1;
-                    }
-                    *reinterpret_cast<__nv_bfloat162 *>(dst0) = __floats2bfloat162_rn(a.x, a.y);
-                    *reinterpret_cast<__nv_bfloat162 *>(dst1) = __floats2bfloat162_rn(b.x, b.y);
-                }
-            };
-            for (int cidx = tid; cidx < BM * CH; cidx += NW * 32) {          // rows beyond the G heads are zero
-                const int r = cidx / CH, ch = cidx % CH;
-                if (r >= G) *reinterpret_cast<uint4 *>(sQ + swz<HD>(r, ch)) = make_uint4(0u, 0u, 0u, 0u);
-            }
-            for (int r = warp; r < G; r += NW) {
-                const __nv_bfloat16 * src = tok_in + (size_t) (kvh * G + r) * HD;
-                __nv_bfloat16 * d0 = reinterpret_cast<__nv_bfloat16 *>(sQ + swz<HD>(r, p0 >> 3)) + (p0 & 7);
-                __nv_bfloat16 * d1 = reinterpret_cast<__nv_bfloat16 *>(sQ + swz<HD>(r, (half + p0) >> 3)) + (p0 & 7);
-                norm_rope(src, p.q_weight, tab != nullptr, d0, d1);
-            }
-            // the CTA that holds the pair's last tile makes the token's own key and value: to the cache for later
-            // steps and, through shared memory, into that tile once its copy has landed
-            if (seg_last && p.write_kv) {
-                const int slot = p.slots[q0];
-                if (slot >= 0 && slot < p.num_pages * p.page_size) {
-                    patch = true;
-                    if (warp == NW - 1) {
-                        const __nv_bfloat16 * src = tok_in + (size_t) (p.nh + kvh) * HD;
-                        norm_rope(src, p.k_weight, tab != nullptr, s_new[0] + p0, s_new[0] + half + p0);
-                    } else if (warp == NW - 2) {
-                        const __nv_bfloat16 * src = tok_in + (size_t) (p.nh + p.nkv + kvh) * HD;
-                        if (lane < CH) *reinterpret_cast<uint4 *>(s_new[1] + lane * 8) = *reinterpret_cast<const uint4 *>(src + lane * 8);
-                    }
-                }
-            }
-        }
-        __syncthreads();
-        if (FUSED && patch && tid < 2 * CH) {                // the new rows into the cache, 16 bytes a thread
-            const int slot = p.slots[q0];
-            const int page = slot / p.page_size, off = slot - page * p.page_size;
-            const size_t cell = (((size_t) page * p.nkv + kvh) * p.page_size + off) * HD;
-            const int which = tid / CH, ch = tid % CH;
-            __nv_bfloat16 * dst = (which == 0 ? p.k_cache_w : p.v_cache_w) + cell + ch * 8;
-            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(s_new[which] + ch * 8);
-        }
-        unsigned qf[KS][4];
-#pragma unroll
-        for (int ks = 0; ks < KS; ks++)
-            ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], smem_u32(sQ + swz<HD>(lane & 15, ks * 2 + (lane >> 4))));
-
-        float o[DT][4];
-#pragma unroll
-        for (int d = 0; d < DT; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
-        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-        const bool row_ok[2] = {g_ < G, g_ + 8 < G};
-
-        int last_stage = 0;
-        for (int tt = 0; tt < seg; tt++, i++) {
-            if (warp == 0 && i + STAGES - 1 < n_my) tma_issue((i + STAGES - 1) % STAGES, pg_next, kvh_next);
-            if (i + STAGES < n_my) {                         // the page of the tile that is issued next time round
-                pg_next = page_at(lc);
-                kvh_next = lc.kvh;
-                if (i + STAGES + 1 < n_my) advance(lc, 1);
-            }
-            const int stage = i % STAGES;
-            last_stage = stage;
-            if (!dk_wait(smem_u32(&full_bar[stage]), (unsigned) (i / STAGES) & 1u)) failed = true;
-            if (FUSED && patch && tt == seg - 1) {           // the token's own key and value replace what the copy brought
-                if (tid < 2 * CH) {
-                    const int which = tid / CH, ch = tid % CH;
-                    unsigned char * tile = (which == 0 ? sK : sV) + stage * TILE_BYTES;
-                    *reinterpret_cast<uint4 *>(tile + kv_off<HD, true>(k_hi % BN, ch)) = *reinterpret_cast<const uint4 *>(s_new[which] + ch * 8);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                }
-                __syncthreads();
-            }
-            const unsigned char * tK = sK + stage * TILE_BYTES;
-            const unsigned char * tV = sV + stage * TILE_BYTES;
-            float sc[2][4];
-#pragma unroll
-            for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
-#pragma unroll
-            for (int ks = 0; ks < KS; ks++) {
-                unsigned b0, b1, b2, b3;
-                const int r = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-                ldmatrix_x4(b0, b1, b2, b3, smem_u32(tK + kv_off<HD, true>(r, ks * 2 + ((lane >> 3) & 1))));
-                mma16816(sc[0], qf[ks], b0, b1);
-                mma16816(sc[1], qf[ks], b2, b3);
-            }
-            // every row is the one token at position k_hi: keys beyond it, before the window, and rows beyond the
-            // G heads are masked
-            const int key0 = (cc.tile_lo + cc.t + tt) * BN + warp * 16;
-#pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                    const bool vis = row_ok[e >> 1] && j <= k_hi && (p.window == 0 || k_hi - j < p.window);
-                    if (!vis) sc[nt][e] = -INFINITY;
-                }
-            }
-            float m_new[2];
-            m_new[0] = fmaxf(m_run[0], fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])));
-            m_new[1] = fmaxf(m_run[1], fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])));
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
-                m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-            }
-            float corr[2], neg[2], sum[2] = {0.0f, 0.0f};
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                corr[h] = (m_new[h] == -INFINITY) ? 1.0f : exp2f((m_run[h] - m_new[h]) * p.scale_log2);
-                neg[h] = (m_new[h] == -INFINITY) ? 0.0f : m_new[h] * p.scale_log2;
-            }
-#pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int h = e >> 1;
-                    const float pv = fast_exp2(fmaf(sc[nt][e], p.scale_log2, -neg[h]));
-                    sc[nt][e] = pv;
-                    sum[h] += pv;
-                }
-            }
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                l_run[h] = l_run[h] * corr[h] + sum[h];
-                m_run[h] = m_new[h];
-            }
-            if (corr[0] != 1.0f || corr[1] != 1.0f) {
-#pragma unroll
-                for (int dt = 0; dt < DT; dt++) {
-                    o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
-                    o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
-                }
-            }
-            unsigned a[4];
-            a[0] = pack_bf16(sc[0][0], sc[0][1]);
-            a[1] = pack_bf16(sc[0][2], sc[0][3]);
-            a[2] = pack_bf16(sc[1][0], sc[1][1]);
-            a[3] = pack_bf16(sc[1][2], sc[1][3]);
-#pragma unroll
-            for (int dp = 0; dp < DT / 2; dp++) {
-                unsigned b0, b1, b2, b3;
-                const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(tV + kv_off<HD, true>(r, dp * 2 + (lane >> 4))));
-                mma16816(o[2 * dp], a, b0, b1);
-                mma16816(o[2 * dp + 1], a, b2, b3);
-            }
-            if (__syncthreads_or(failed ? 1 : 0)) {          // a copy that never landed ends the walk for the whole CTA
-                if (tid == 0 && p.status != nullptr) { p.status[0] = 11; p.status[1] = i; }
-                return;
-            }
-        }
-
-        // ---- the segment's result: merge the four warps in the stage just read (free until the next copy is issued) ----
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-        }
-        float * mo = reinterpret_cast<float *>(sK + last_stage * TILE_BYTES);     // [NW][8][HD]: 16 KB
-        float * ml = reinterpret_cast<float *>(sV + last_stage * TILE_BYTES);     // [NW][8][2]
-        if (g_ < G) {                                        // rows g_ + 8 do not exist (G <= 8)
-#pragma unroll
-            for (int dt = 0; dt < DT; dt++)
-                *reinterpret_cast<float2 *>(mo + ((size_t) warp * 8 + g_) * HD + dt * 8 + 2 * t_) = make_float2(o[dt][0], o[dt][1]);
-            if (t_ == 0) { ml[(warp * 8 + g_) * 2] = m_run[0]; ml[(warp * 8 + g_) * 2 + 1] = l_run[0]; }
-        }
-        __syncthreads();
-        const int mr = tid >> 4, mpart = tid & 15;           // 16 threads per row, HD / 16 columns each
-        const bool m_ok = mr < G;
-        const size_t row_idx = (size_t) q0 * p.nh + kvh * G + (m_ok ? mr : 0);
-        const bool whole = seg_first && seg_last;
-        // which part of the pair this segment is, and how many there are: the shares that cut the pair's tiles [a, b)
-        const long long a_f = ((long long) s_cum[s] * p.nkv) + (long long) kvh * cc.n, b_f = a_f + cc.n;
-        const int c_first = (int) (((a_f + 1) * C + T - 1) / T) - 1, c_last = (int) ((b_f * C + T - 1) / T) - 1;
-        const int n_parts = c_last - c_first + 1;
-        float * my_o = p.part_o + ((size_t) c * 2 + slot) * 8 * HD;
-        float * my_lse = p.part_lse + ((size_t) c * 2 + slot) * 8;
-        if (m_ok) {
-            float mw[NW], m = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < NW; w++) { mw[w] = ml[(w * 8 + mr) * 2]; m = fmaxf(m, mw[w]); }
-            float sw[NW], l = 0.0f;
-#pragma unroll
-            for (int w = 0; w < NW; w++) {
-                sw[w] = (mw[w] == -INFINITY) ? 0.0f : exp2f((mw[w] - m) * p.scale_log2);
-                l += sw[w] * ml[(w * 8 + mr) * 2 + 1];
-            }
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-#pragma unroll
-            for (int cidx = 0; cidx < HD / 16; cidx += 2) {
-                const int d = mpart * (HD / 16) + cidx;
-                float v0 = 0.0f, v1 = 0.0f;
-#pragma unroll
-                for (int w = 0; w < NW; w++) {
-                    const float2 x = *reinterpret_cast<const float2 *>(mo + ((size_t) w * 8 + mr) * HD + d);
-                    v0 += sw[w] * x.x;
-                    v1 += sw[w] * x.y;
-                }
-                if (whole)
-                    *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
-                else
-                    *reinterpret_cast<float2 *>(my_o + mr * HD + d) = make_float2(v0 * inv, v1 * inv);
-            }
-            if (!whole && mpart == 0)                        // log-sum-exp in base 2; -inf marks a part that saw no key
-                my_lse[mr] = l > 0.0f ? m * p.scale_log2 + log2f(l) : -INFINITY;
-        }
-        if (!whole) {
-            // the CTA that brings the pair's last part merges them
-            __threadfence();
-            __syncthreads();
-            int * counter = p.counters + (size_t) s * p.nkv + kvh;
-            if (tid == 0) s_last = (atomicAdd(counter, 1) == n_parts - 1);
-            __syncthreads();
-            if (s_last) {
-                __threadfence();
-                if (m_ok) {
-                    // part k is what CTA c_first + k wrote: in its first place, except that the first of them wrote
-                    // to its second place if its share began before the pair
-                    auto place = [&](int k) -> size_t {
-                        const long long ck = c_first + k;
-                        return (size_t) ck * 2 + ((k == 0 && T * ck / C != a_f) ? 1 : 0);
-                    };
-                    float mx = -INFINITY;
-                    for (int k = 0; k < n_parts; k++) mx = fmaxf(mx, __ldcg(p.part_lse + place(k) * 8 + mr));
-                    float acc[HD / 16];
-#pragma unroll
-                    for (int k = 0; k < HD / 16; k++) acc[k] = 0.0f;
-                    float wsum = 0.0f;
-                    if (mx != -INFINITY) {
-                        for (int k = 0; k < n_parts; k++) {          // in the order of the parts, whatever their timing
-                            const float w = exp2f(__ldcg(p.part_lse + place(k) * 8 + mr) - mx);
-                            if (w == 0.0f) continue;
-                            wsum += w;
-                            const float * po = p.part_o + (place(k) * 8 + mr) * HD + mpart * (HD / 16);
-#pragma unroll
-                            for (int k4 = 0; k4 < HD / 16; k4 += 4) {
-                                const float4 x = __ldcg(reinterpret_cast<const float4 *>(po + k4));
-                                acc[k4] += w * x.x; acc[k4 + 1] += w * x.y; acc[k4 + 2] += w * x.z; acc[k4 + 3] += w * x.w;
-                            }
-                        }
-                    }
-                    const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
-                    __nv_bfloat16 * dst = p.out + row_idx * HD + mpart * (HD / 16);
-#pragma unroll
-                    for (int k2 = 0; k2 < HD / 16; k2 += 2)
-                        *reinterpret_cast<__nv_bfloat162 *>(dst + k2) = __floats2bfloat162_rn(acc[k2] * inv, acc[k2 + 1] * inv);
-                }
-                if (tid == 0) *counter = 0;
-            }
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();                                     // the merge is read: the stage may be filled again
-        advance(cc, seg);
-    }
-    pdl_launch_dependents();
-}
-
 typedef CUresult (*KvEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1424,34 +966,6 @@ static int launch_decode_st(const AttnParams & p, const KvMaps & maps, int S, in
     return e == cudaSuccess ? IIAN_OK : 1000 + (int) e;
 }
 
-static int decode_sm_count() {
-    static int n[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (n[dev] == 0) {
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-        n[dev] = v;
-    }
-    return n[dev];
-}
-
-template <bool FUSED>
-static int launch_decode_stream(const AttnParams & p0, const KvMaps & maps, int S, cudaStream_t stream) {
-    constexpr int HD = 128, STAGES = 3;
-    AttnParams p = p0;
-    const int ctas = 2 * decode_sm_count();
-    p.part_lse = p.part_o + (size_t) ctas * 2 * 8 * HD;
-    const size_t smem = (size_t) 16 * HD * 2 + 2 * STAGES * BN * HD * 2 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<HD, FUSED, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-        if (e != cudaSuccess) return 1000 + (int) e;
-        configured = true;
-    }
-    return iian_launch(attention_decode_stream_kernel<HD, FUSED, STAGES>, dim3(ctas), dim3(128), smem, stream, p, maps, S);
-}
-
 static int g_decode_stages = 2;
 template <int HD, bool CLUSTER, bool FUSED = false>
 static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
@@ -1465,16 +979,6 @@ static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t
             int rc = kv_map_for(p.k_cache, p.num_pages, p.nkv, ps, &maps.k);
             if (rc == IIAN_OK) rc = kv_map_for(p.v_cache, p.num_pages, p.nkv, ps, &maps.v);
             if (rc != IIAN_OK) return rc;
-            if constexpr (!CLUSTER) {
-                // unsplit keys, one token per sequence, scratch for the parts at hand: the tiles of all pairs as one line
-                // (measured: with between three quarters and all of the resident CTAs' number of pairs, a CTA per pair
-                // is the faster form: 53.8 us against 58.4 us at 256 pairs of 2048 keys, every pair cut by a border)
-                const int G = p.nh / p.nkv;
-                const int pairs = S * p.nkv, resident = 2 * decode_sm_count();
-                if (p.n_split == 1 && max_rows == G && G <= 8 && S <= STREAM_MAX_SEQS && pairs >= resident / 2 &&
-                    (pairs > resident || pairs * 4 < resident * 3) && p.part_o != nullptr && p.counters != nullptr)
-                    return launch_decode_stream<FUSED>(p, maps, S, stream);
-            }
             if (deep) return launch_decode_st<HD, CLUSTER, FUSED, 3, true>(p, maps, S, max_rows, stream);
             return launch_decode_st<HD, CLUSTER, FUSED, 2, true>(p, maps, S, max_rows, stream);
         }
@@ -1539,14 +1043,6 @@ using namespace iian;
 // status: two ints on the device, zero before the launch, or null.  With a status buffer the decode form fetches
 // its K/V tiles by TMA where it can (head size 128, pages of 8 to 64 tokens); a wait that gave up leaves {11, tile}
 // there and the output is not valid.  Without one it copies with cp.async as before.
-// Floats of scratch the stream form of the decode kernel wants (part_o; it derives part_lse itself) on the current
-// device, whatever the batch; its counters are one int per (sequence, KV head).  A caller that passes part_o of
-// this size and counters with n_split 1 and a status buffer gets the stream form where it applies (one token per
-// sequence, head size 128, up to 8 heads per KV head, up to 256 sequences, more (sequence, KV head) pairs than CTAs
-// fit the GPU at once, or between half and three quarters as many); without the scratch an unsplit call takes the
-// form with a CTA per pair.
-IIAN_API int iian_attention_stream_scratch(void) { return 2 * decode_sm_count() * 2 * 8 * (128 + 1); }
-
 IIAN_API int iian_attention_decode_stages(int stages) {
     if (stages != 2 && stages != 3) return IIAN_ERR_SHAPE;
     g_decode_stages = stages;

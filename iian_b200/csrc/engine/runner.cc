@@ -67,7 +67,6 @@ struct Kernels {
                                   const int *, int, int, int, int, int, int, int, float, int, int, int, const float *,
                                   const float *, const float *, const int *, float, int, int *, S) = nullptr;
     int (*attention_decode_stages)(int) = nullptr;
-    int (*attention_stream_scratch)() = nullptr;
     int (*gemm_stream)(const void *, const void *, void *, int, int, int, int, int, const float *, int, float, float, float *,
                        const float *, float *, int *, S) = nullptr;
     int (*gemm_stream_stages)(int) = nullptr;
@@ -411,13 +410,6 @@ struct NativeRunner::Impl {
     }
     // The decode kernel's TMA form reports a wait that gave up in the status words the tcgen05 kernels use; without
     // them it copies with cp.async.
-    // Scratch for the stream form of the unsplit decode kernel (one token per sequence, head size 128); without it
-    // the kernel takes the form with a CTA per (sequence, KV head).
-    void stream_scratch(int pairs, int hd, float *& part_o, int *& counters) {
-        if (!opt.decode_tma || !opt.decode_stream || hd != 128) return;
-        part_o = scratch_for((size_t) k.attention_stream_scratch());
-        counters = counters_for((size_t) pairs);
-    }
     int * decode_status() {
         if (!opt.decode_tma) return nullptr;
         tc_used = true;
@@ -449,8 +441,6 @@ struct NativeRunner::Impl {
                     const int row_tiles = (si.max_q_len * (nh / nkv) + 15) / 16;
                     counters = counters_for((size_t) si.S * nkv * row_tiles);
                 }
-            } else if (n_split == 1 && small_tiles && si.max_q_len == 1) {
-                stream_scratch(si.S * nkv, hd, part_o, counters);
             }
             check(k.attention_mma(q, c.k_cache, c.v_cache, out, part_o, part_lse, counters, si.cu_q, si.ctx_len, bt, mb, si.N, si.S,
                                   si.max_q_len, nh, nkv, hd, ps, c.num_pages, L.scale, L.window, n_split,
@@ -520,8 +510,6 @@ struct NativeRunner::Impl {
                 part_o = scratch_for(rows * n_split * (hd + 1));
                 part_lse = part_o + rows * n_split * hd;
                 counters = counters_for((size_t) si.S * L.num_kv_heads);
-            } else if (n_split == 1) {
-                stream_scratch(si.S * L.num_kv_heads, hd, part_o, counters);
             }
             check(k.attention_decode_fused(qkv, c.k_cache, c.v_cache, attn, part_o, part_lse, counters, si.cu_q, si.ctx_len,
                                            si.block_table[g], si.max_blocks[g], si.S, nh, L.num_kv_heads, hd, model.page_size, c.num_pages,
@@ -883,7 +871,6 @@ NativeRunner::NativeRunner(const ModelDesc & model, const KernelLibraries & libs
             bind(h, "iian_attention_mma", k.attention_mma, libs.attention_mma);
             bind(h, "iian_attention_decode_fused", k.attention_decode_fused, libs.attention_mma);
             bind(h, "iian_attention_decode_stages", k.attention_decode_stages, libs.attention_mma);
-            bind(h, "iian_attention_stream_scratch", k.attention_stream_scratch, libs.attention_mma);
             if (k.attention_decode_stages(opt.decode_stages) != 0) fail("attention: the decode kernel has 2 or 3 stages");
         } else fail("the attention_mma kernel library is required for bfloat16");
         if (void * h = open(libs.prefetch)) bind(h, "iian_prefetch_l2", k.prefetch_l2, libs.prefetch);

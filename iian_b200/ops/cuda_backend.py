@@ -735,8 +735,6 @@ class CudaKernels:
             if small_tiles:
                 row_tiles = -(-meta.max_q_len * (num_heads // num_kv_heads) // 16)
                 counters = self.attention_counters(q.device, meta.num_seqs * num_kv_heads * row_tiles).data_ptr()
-        elif n_split == 1 and small_tiles and meta.max_q_len == 1 and head_dim == 128:
-            part_o, counters = self._stream_scratch(q.device, meta.num_seqs * num_kv_heads)
         bt = meta.block_table
         fn = _fn("attention_mma", "iian_attention_mma",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -753,19 +751,6 @@ class CudaKernels:
     FUSED_DECODE = os.environ.get("IIAN_FUSED_DECODE_ATTENTION", "1") not in ("0", "false", "off")
     # decode attention fetches its K/V tiles by TMA (head size 128, pages of 8 to 64 tokens); IIAN_DECODE_TMA=0: cp.async
     DECODE_TMA = os.environ.get("IIAN_DECODE_TMA", "1") not in ("0", "false", "off")
-
-    # unsplit decode attention walks the key tiles of all (sequence, KV head) pairs as one line shared out evenly
-    # over the resident CTAs (attention_decode_stream_kernel); IIAN_DECODE_STREAM=0: a CTA per pair
-    DECODE_STREAM = os.environ.get("IIAN_DECODE_STREAM", "1") not in ("0", "false", "off")
-
-    def _stream_scratch(self, device, pairs: int):
-        """Scratch and counters for the stream form of the decode kernel, (0, 0) when it is switched off: without
-        them the kernel takes the form with a CTA per pair."""
-        if not (self.DECODE_TMA and self.DECODE_STREAM):
-            return 0, 0
-        fn = _fn("attention_mma", "iian_attention_stream_scratch", [])
-        scratch = self.attention_scratch(device, int(fn()))
-        return scratch.data_ptr(), self.attention_counters(device, pairs).data_ptr()
 
     def _decode_status(self, device):
         """The status words the decode kernel's TMA form reports to (the ones of the tcgen05 kernels), or None: the
@@ -812,8 +797,6 @@ class CudaKernels:
             part_o = scratch.data_ptr()
             part_lse = part_o + rows * n_split * head_dim * 4
             counters = self.attention_counters(qkv.device, s_ * num_kv_heads).data_ptr()
-        elif n_split == 1 and head_dim == 128:
-            part_o, counters = self._stream_scratch(qkv.device, s_ * num_kv_heads)
         bt = meta.block_table
         fn = _fn("attention_mma", "iian_attention_decode_fused",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

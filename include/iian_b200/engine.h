@@ -113,7 +113,6 @@ struct RunnerOptions {
     int stream_stages = 12;         // 12: one CTA per SM with the deep ring; 6: two CTAs per SM
     bool pdl_stream = true;         // launch the streaming product with programmatic stream serialization
     bool decode_tma = true;         // decode attention fetches K/V tiles by TMA (head size 128) instead of cp.async
-    bool decode_stream = true;      // unsplit decode attention: the key tiles of all pairs as one line, shared out evenly
 };
 
 // Paths of the kernel libraries (one shared object per source, see iian_b200/csrc/build.py); empty: not needed.

@@ -458,47 +458,6 @@ def test_attention_decode_fused(case, mode):
     fused_decode_check(case, mode)
 
 
-def stream_ctx_lens(n, lo, hi, seed, extra=()):
-    g = torch.Generator().manual_seed(seed)
-    return [int(x) for x in torch.randint(lo, hi + 1, (n,), generator=g)] + list(extra)
-
-
-STREAM_DECODE_CASES = [
-    # at least as many (sequence, KV head) pairs as SMs, so that the unsplit decode kernel takes its stream form:
-    # nh, nkv, hd, page, ctx_lens, window, qk_norm, rotate
-    (8, 4, 128, 16, stream_ctx_lens(38, 1, 700, 1, extra=[1, 64, 65, 128]), None, True, True),      # shares of a few tiles, pairs cut by borders
-    (16, 8, 128, 32, stream_ctx_lens(20, 30, 400, 2), 100, True, True),                           # a window
-    (8, 8, 128, 8, stream_ctx_lens(18, 1, 60, 3, extra=[5000]), None, False, True),               # one pair spread over many CTAs
-    (4, 2, 128, 16, stream_ctx_lens(200, 1, 100, 4), None, True, False),                          # more pairs than CTAs: several pairs a share
-    (8, 1, 128, 64, stream_ctx_lens(150, 1, 300, 5), None, False, False),                         # 8 heads a KV head, big pages
-]
-
-
-@pytest.mark.parametrize("case", STREAM_DECODE_CASES)
-def test_attention_decode_stream(case, monkeypatch):
-    """Unsplit decode attention over many sequences of unequal length (the key tiles of all pairs as one line, an
-    equal share per resident CTA, pairs cut by a border merged by whoever brings the last part): fused and
-    two-kernel routes agree bit for bit, match the plain formulas, and stay close to the form with a CTA per pair."""
-    from iian_b200.ops.cuda_backend import CudaKernels
-    seen = []
-    real = CudaKernels._stream_scratch
-
-    def spy(self, device, pairs):
-        out = real(self, device, pairs)
-        seen.append((pairs, out[0] != 0))
-        return out
-
-    monkeypatch.setattr(CudaKernels, "_stream_scratch", spy)
-    # (the rotation kernel of the two-kernel route sums a head's squares in another order than the fused kernels: over
-    # this many rows a key may differ from it in its last bit, so the caches are compared between the two fused forms)
-    out_stream, kc_s, vc_s = fused_decode_check(case, "one", cache_exact=False)
-    assert seen and all(on for _, on in seen) and seen[0][0] >= 148
-    monkeypatch.setattr(CudaKernels, "DECODE_STREAM", False)
-    out_pairs, kc_p, vc_p = fused_decode_check(case, "one", cache_exact=False)
-    assert torch.equal(kc_s, kc_p) and torch.equal(vc_s, vc_p)
-    assert (out_stream.float() - out_pairs.float()).abs().max() < tol(torch.bfloat16, max(1.0, out_pairs.float().abs().max().item()))
-
-
 def fused_decode_check(case, mode, cache_exact=True):
     nh, nkv, hd, ps, ctx_lens, window, qk_norm, rotate = case
     S = len(ctx_lens)
