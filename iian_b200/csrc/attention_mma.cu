@@ -838,7 +838,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
         for (int idx = tid; idx < n_rows * cols; idx += NW * 32) {
             const int r = idx / cols, d = rank * cols + idx % cols;
             if (d >= HD) continue;
-            float mc[8], m = -INFINITY;
+            float mc[16], m = -INFINITY;
             for (int c = 0; c < ns; c++) {
                 mc[c] = cluster.map_shared_rank(cML, c)[r * 2];
                 m = fmaxf(m, mc[c]);
@@ -950,6 +950,14 @@ static int launch_decode_st(const AttnParams & p, const KvMaps & maps, int S, in
     }
     dim3 grid((max_rows + 15) / 16, p.nkv, S * p.n_split);
     if (!CLUSTER) return iian_launch(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA>, grid, dim3(128), smem, stream, p, maps);
+    if (p.n_split > 8) {                                   // clusters of 9 to 16 CTAs have to be asked for
+        static bool allowed = false;
+        if (!allowed) {
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return 1000 + (int) e;
+            allowed = true;
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(128);
@@ -975,7 +983,10 @@ static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t
     if constexpr (HD == 128) {
         // the TMA form: a status buffer to report to, pages that divide a tile and hold whole swizzle atoms
         const int ps = p.page_size;
-        if (p.status != nullptr && (ps == 8 || ps == 16 || ps == 32 || ps == 64)) {
+        // (measured, one launch: with one or two sequences, whose CTAs have few tiles each and wait for the first of them,
+        // the cp.async form is 2 to 7 % faster -- 26.4 against 28.2 us at batch 1 and 8k of context; from 8 sequences
+        // on the TMA form is as fast or up to 4 % faster)
+        if (p.status != nullptr && (ps == 8 || ps == 16 || ps == 32 || ps == 64) && S * p.nkv >= 32) {
             int rc = kv_map_for(p.k_cache, p.num_pages, p.nkv, ps, &maps.k);
             if (rc == IIAN_OK) rc = kv_map_for(p.v_cache, p.num_pages, p.nkv, ps, &maps.v);
             if (rc != IIAN_OK) return rc;
@@ -1038,7 +1049,7 @@ using namespace iian;
 // Scratch needed for n_split > 1: part_o = N * nh * n_split * hd floats, part_lse = N * nh * n_split floats,
 // and for the decode form (small_tiles 1) counters = S * nkv * ceil(max_q_len * nh / nkv / 16) ints that are
 // zero before the first launch (the kernel leaves them zero).  small_tiles 2 is the decode form with the parts
-// of a row tile merged inside a thread-block cluster: n_split 2 to 8, no scratch at all.
+// of a row tile merged inside a thread-block cluster: n_split 2 to 16, no scratch at all.
 // Tiles of shared memory per CTA of the decode form: 2 (three CTAs per SM) or 3 (two CTAs, two tiles in flight).
 // status: two ints on the device, zero before the launch, or null.  With a status buffer the decode form fetches
 // its K/V tiles by TMA where it can (head size 128, pages of 8 to 64 tokens); a wait that gave up leaves {11, tile}
@@ -1058,7 +1069,7 @@ IIAN_API int iian_attention_mma(
     if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
     const bool cluster = small_tiles == 2 && n_split > 1;   // decode form, parts merged inside a thread-block cluster
-    if (cluster && n_split > 8) return IIAN_ERR_SHAPE;
+    if (cluster && n_split > 16) return IIAN_ERR_SHAPE;
     if (n_split > 1 && !cluster && (part_o == nullptr || part_lse == nullptr)) return IIAN_ERR_SHAPE;
     if (n_split > 1 && !cluster && small_tiles && counters == nullptr) return IIAN_ERR_SHAPE;
     if ((long long) S * n_split > 65535 || nkv > 65535) return IIAN_ERR_LIMIT;
@@ -1088,7 +1099,7 @@ IIAN_API int iian_attention_mma(
 // token (token i belongs to sequence i, N == S): per-head RMSNorm (weights may be null: no norm), NEOX
 // rotation over the whole head with the (cos, sin) table [N, hd / 2] (null: no rotation), the write of the
 // new key and value to cache cell slots[i] (write_kv; a negative slot stores nothing), and attention over
-// the cache, in one launch.  Scratch as for iian_attention_mma's decode form; cluster != 0 (n_split 2..8)
+// the cache, in one launch.  Scratch as for iian_attention_mma's decode form; cluster != 0 (n_split 2..16)
 // needs none.  Up to 16 query heads per KV head.
 IIAN_API int iian_attention_decode_fused(
     const void * qkv, void * k_cache, void * v_cache, void * out, float * part_o, float * part_lse, int * counters,
@@ -1100,7 +1111,7 @@ IIAN_API int iian_attention_decode_fused(
     if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
     const bool cl = cluster != 0 && n_split > 1;
-    if (cl && n_split > 8) return IIAN_ERR_SHAPE;
+    if (cl && n_split > 16) return IIAN_ERR_SHAPE;
     if (n_split > 1 && !cl && (part_o == nullptr || part_lse == nullptr || counters == nullptr)) return IIAN_ERR_SHAPE;
     if (write_kv && slots == nullptr) return IIAN_ERR_SHAPE;
     if ((long long) S * n_split > 65535 || nkv > 65535) return IIAN_ERR_LIMIT;
@@ -1167,7 +1178,7 @@ IIAN_API int iian_attention_mma_noalloc(
     float scale, int window, int n_split, int small_tiles, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
     if (n_split < 1 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || (hd != 64 && hd != 128)) return IIAN_ERR_SHAPE;
-    // which form runs decides what it needs of the array: the cluster form (small_tiles == 2, n_split 2..8)
+    // which form runs decides what it needs of the array: the cluster form (small_tiles == 2, n_split 2..16)
     // merges in shared memory and needs nothing; the prefill form (small_tiles == 0) needs the partial results
     // but no counters; an unsplit call needs neither
     const bool uses_scratch = n_split > 1 && small_tiles != 2;

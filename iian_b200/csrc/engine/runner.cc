@@ -268,7 +268,8 @@ struct NativeRunner::Impl {
         const int base = std::max(1, num_seqs * num_kv_heads);
         const int slots = opt.decode_ctas_per_sm * sm_count;
         int n = std::max(1, std::min(std::min(slots / base, (tiles + 1) / 2), opt.max_splits));
-        if (n > 8 && (n < 12 || tiles < 256)) n = 8;
+        if (n > 8 && n < 16) n = 8;                          // up to 16 parts merge inside a thread-block cluster
+        else if (n > 16 && tiles < 512) n = 16;
         return n;
     }
 
@@ -430,7 +431,7 @@ struct NativeRunner::Impl {
             const bool decode = si.max_q_len * (nh / nkv) <= 16;
             const bool small_tiles = decode;
             int n_split = si.n_split > 0 ? si.n_split : (decode ? attention_splits(si.S, nkv, si.max_ctx) : 1);
-            const bool cluster = opt.cluster_merge && small_tiles && (n_split == 2 || n_split == 4 || n_split == 8);
+            const bool cluster = opt.cluster_merge && small_tiles && (n_split == 2 || n_split == 4 || n_split == 8 || n_split == 16);
             float * part_o = nullptr, * part_lse = nullptr;
             int * counters = nullptr;
             if (n_split > 1 && !cluster) {
@@ -502,7 +503,7 @@ struct NativeRunner::Impl {
                           L.num_kv_heads > 0 && nh % L.num_kv_heads == 0 && nh / L.num_kv_heads <= 16 && (rot_dim == 0 || table != nullptr);
         if (fuse) {
             int n_split = si.n_split > 0 ? si.n_split : attention_splits(si.S, L.num_kv_heads, si.max_ctx);
-            const bool cluster = opt.cluster_merge && n_split >= 2 && n_split <= 8;
+            const bool cluster = opt.cluster_merge && n_split >= 2 && n_split <= 16;
             float * part_o = nullptr, * part_lse = nullptr;
             int * counters = nullptr;
             if (n_split > 1 && !cluster) {

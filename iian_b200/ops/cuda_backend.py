@@ -673,17 +673,21 @@ class CudaKernels:
         the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128, contexts of 1k to 8k, batches 1 to
         64): the CTAs of one launch should number at most two per SM (more slow each other down, and a second
         wave repeats the whole chain of dependent loads), and a CTA should keep at least two key tiles.  Up to
-        8 parts merge inside a thread-block cluster, which saves three trips through L2 (write the parts, count
-        arrivals, read them back: 3.36 -> 3.23 ms per step at batch 1 and 1k context), so more than 8 parts are
-        only taken beyond 16k of context (at 4k, 32 parts merged through scratch memory cost 3.63 ms a step at batch 1
-        where 8 parts in a cluster take about 3.2); 9 to 11 are rounded down to 8."""
+        16 parts merge inside a thread-block cluster (more than 8 is a size a kernel has to ask for), which saves
+        three trips through L2 (write the parts, count arrivals, read them back: 3.36 -> 3.23 ms per step at batch 1
+        and 1k context; one launch at batch 1 and 8k context: 27.9 us with 8 parts, 18.6 us with 16 in a cluster,
+        25.9 us with 16 and 30.8 us with 32 merged through scratch memory), so 9 to 15 parts are rounded down to 8,
+        more to 16, and more than 16 are only taken from 32k of context on (48.8 us with 32 parts through scratch
+        memory against 52.9 us with 16 in a cluster)."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
         if os.environ.get("IIAN_DECODE_FORCE_SPLITS"):
             return int(os.environ["IIAN_DECODE_FORCE_SPLITS"])
         n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 2), self.MAX_SPLITS))
-        if n > 8 and (n < 12 or tiles < 256):
+        if 8 < n < 16:
             n = 8
+        elif n > 16 and tiles < 512:
+            n = 16
         return n
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
@@ -725,7 +729,7 @@ class CudaKernels:
             n_split = getattr(meta, "n_split", None) or (self.attention_splits(meta.num_seqs, num_kv_heads, meta.max_ctx) if decode else 1)
         if cluster is None:
             cluster = self.CLUSTER_MERGE
-        cluster = bool(cluster and small_tiles and n_split in (2, 4, 8))
+        cluster = bool(cluster and small_tiles and n_split in (2, 4, 8, 16))
         part_o = part_lse = counters = 0
         if n_split > 1 and not cluster:
             rows = n * num_heads
@@ -789,7 +793,7 @@ class CudaKernels:
             n_split = getattr(meta, "n_split", None) or self.attention_splits(s_, num_kv_heads, meta.max_ctx)
         if cluster is None:
             cluster = self.CLUSTER_MERGE
-        cluster = bool(cluster and 2 <= n_split <= 8)
+        cluster = bool(cluster and 2 <= n_split <= 16)
         part_o = part_lse = counters = 0
         if n_split > 1 and not cluster:
             rows = s_ * num_heads

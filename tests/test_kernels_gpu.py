@@ -447,11 +447,15 @@ FUSED_DECODE_CASES = [
     (16, 1, 64, 16, [500, 16], 100, False, True),
     (4, 4, 128, 32, [2100, 33], None, True, False),
     (12, 4, 128, 12, [130, 90, 12, 13], 33, False, False),
+    # 32 and more (sequence, KV head) pairs: the form that fetches its K/V tiles by TMA
+    (32, 8, 128, 16, [1152, 64, 65, 300, 17], None, True, True),
+    (16, 8, 128, 64, [200, 130, 64, 1], 100, False, True),
+    (8, 4, 128, 8, [90, 500, 33, 8, 1, 129, 64, 77], None, True, False),
 ]
 
 
 @pytest.mark.parametrize("case", FUSED_DECODE_CASES)
-@pytest.mark.parametrize("mode", ["auto", "one", "cluster3", "cluster8", "scratch5"])
+@pytest.mark.parametrize("mode", ["auto", "one", "cluster3", "cluster8", "cluster16", "scratch5"])
 def test_attention_decode_fused(case, mode):
     """Norm, rotation, cache write and attention in one launch: the same bits as the two-kernel route (same
     arithmetic in the same order), the same cache contents, and right against the plain formulas."""
@@ -486,6 +490,7 @@ def fused_decode_check(case, mode, cache_exact=True):
                             n_split=1, small_tiles=True)
     # route B: fused
     kw = {"auto": {}, "one": dict(n_split=1), "cluster3": dict(n_split=3, cluster=True), "cluster8": dict(n_split=8, cluster=True),
+          "cluster16": dict(n_split=16, cluster=True),
           "scratch5": dict(n_split=5, cluster=False)}[mode]
     for _ in range(2):       # twice: the scratch route leaves its counters at zero
         kc_b, vc_b = kc.clone(), vc.clone()
@@ -531,12 +536,16 @@ MMA_CASES = [
     (16, 2, 128, 32, [2100], [2048], None),
     (8, 8, 128, 8, [700, 129], [257, 129], 200),
     (24, 4, 128, 64, [1000, 300, 40], [130, 300, 7], None),
+    # decode steps of 32 and more (sequence, KV head) pairs: K/V tiles by TMA
+    (32, 8, 128, 16, [1152, 700, 64, 65], [1, 1, 1, 1], None),
+    (8, 8, 128, 8, [300, 129, 40, 33], [1, 1, 1, 1], 200),
+    (16, 4, 128, 32, [2100, 64, 31, 500, 96, 97, 1000, 5], [1] * 8, None),
 ]
 
 
 @pytest.mark.parametrize("case", MMA_CASES)
 @pytest.mark.parametrize("standout", [False, True, "outside"])
-@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles", "cluster2", "cluster4", "cluster8", "split4_scratch", "tc"])
+@pytest.mark.parametrize("mode", ["auto", "split5", "big_tiles", "cluster2", "cluster4", "cluster8", "cluster16", "split4_scratch", "tc"])
 def test_paged_attention_mma(case, standout, mode):
     nh, nkv, hd, ps, ctx_lens, q_lens, window = case
     dtype = torch.bfloat16
