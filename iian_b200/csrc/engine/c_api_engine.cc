@@ -82,7 +82,7 @@ void * iian_runner_new(const IianModel * model, const char * const * libs, void 
         opt.cluster_merge = o->cluster_merge != 0; opt.tcgen05_pair = o->tcgen05_pair != 0; opt.decode_stages = o->decode_stages;
         opt.max_splits = o->max_splits; opt.decode_ctas_per_sm = o->decode_ctas_per_sm;
         opt.stream_product = o->stream_product != 0; opt.stream_stages = o->stream_stages; opt.pdl_stream = o->pdl_stream != 0;
-        opt.decode_tma = o->decode_tma != 0;
+        opt.decode_tma = o->decode_tma != 0; opt.split_mixed = o->split_mixed != 0;
         r = new NativeRunner(m, kl, static_cast<CacheManager *>(cache), opt);
     });
     return r;

@@ -119,6 +119,9 @@ struct StepInts {
     std::vector<int> max_blocks;                      // per group
     int n_split = 0;                                  // fixed number of key splits (captured graphs); 0: chosen per launch
     int upload_bytes = 0;
+    // A step that brings single decoded tokens beside portions of prompts has the sequences of the former first:
+    int decode_seqs = 0;                              // how many (0 unless the step is mixed), and their longest context
+    int decode_max_ctx = 0;
 };
 
 struct Staging {
@@ -222,6 +225,8 @@ struct NativeRunner::Impl {
     };
     Prefetcher * prefetcher = nullptr;
     cudaStream_t cap_stream = nullptr, side_stream = nullptr;
+    cudaStream_t mixed_stream = nullptr;              // the decoded tokens' attention of a mixed step
+    cudaEvent_t mixed_fork = nullptr, mixed_join = nullptr;
     std::map<int, void *> rotary_tables;    // rope_key -> table of the current forward pass
     std::vector<int32_t> scratch_tokens, scratch_starts, scratch_fresh;
     std::vector<void *> scratch_caches;
@@ -423,6 +428,39 @@ struct NativeRunner::Impl {
         const bool pow2_page = ps == 8 || ps == 16 || ps == 32 || ps == 64 || ps == 128;
         if (opt.attention_tc && bf16_mode() && hd == 128 && pow2_page && nkv > 0 && nh % nkv == 0 && si.max_q_len * (nh / nkv) >= 64) {
             tc_used = true;
+            const int Sd = si.decode_seqs;
+            if (Sd > 0 && opt.split_mixed && nh / nkv <= 16) {
+                // A mixed step: the single decoded tokens (the first Sd sequences) go to the decode kernel, which reads
+                // their K/V at the memory's rate, on a second stream, while the portions of prompts run on the tensor
+                // cores beside it; in the prefill kernel a decoded token would be a CTA of 256 rows with one token's
+                // heads in it, walking its sequence's keys alone.
+                if (mixed_stream == nullptr) {
+                    cuda_ok(cudaStreamCreateWithFlags(&mixed_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+                    cuda_ok(cudaEventCreateWithFlags(&mixed_fork, cudaEventDisableTiming), "cudaEventCreate");
+                    cuda_ok(cudaEventCreateWithFlags(&mixed_join, cudaEventDisableTiming), "cudaEventCreate");
+                }
+                cuda_ok(cudaEventRecord(mixed_fork, stream), "cudaEventRecord");
+                cuda_ok(cudaStreamWaitEvent(mixed_stream, mixed_fork, 0), "cudaStreamWaitEvent");
+                const int n_split = attention_splits(Sd, nkv, si.decode_max_ctx);
+                const bool cluster = opt.cluster_merge && (n_split == 2 || n_split == 4 || n_split == 8 || n_split == 16);
+                float * part_o = nullptr, * part_lse = nullptr;
+                int * counters = nullptr;
+                if (n_split > 1 && !cluster) {
+                    const size_t rows = (size_t) Sd * nh;
+                    part_o = scratch_for(rows * n_split * (hd + 1));
+                    part_lse = part_o + rows * n_split * hd;
+                    counters = counters_for((size_t) Sd * nkv);
+                }
+                check(k.attention_mma(q, c.k_cache, c.v_cache, out, part_o, part_lse, counters, si.cu_q, si.ctx_len, bt, mb, Sd, Sd, 1,
+                                      nh, nkv, hd, ps, c.num_pages, L.scale, L.window, n_split, cluster ? 2 : 1, decode_status(),
+                                      mixed_stream), "attention_mma");
+                check(k.attention_tc(q, c.k_cache, c.v_cache, out, si.cu_q + Sd, si.ctx_len + Sd, bt + (size_t) Sd * mb, mb, si.N,
+                                     si.S - Sd, si.max_q_len, nh, nkv, hd, ps, c.num_pages, L.scale, L.window, tc_status, stream),
+                      "attention_tc");
+                cuda_ok(cudaEventRecord(mixed_join, mixed_stream), "cudaEventRecord");
+                cuda_ok(cudaStreamWaitEvent(stream, mixed_join, 0), "cudaStreamWaitEvent");
+                return;
+            }
             check(k.attention_tc(q, c.k_cache, c.v_cache, out, si.cu_q, si.ctx_len, bt, mb, si.N, si.S, si.max_q_len, nh, nkv, hd, ps,
                                  c.num_pages, L.scale, L.window, tc_status, stream), "attention_tc");
             return;
@@ -648,11 +686,29 @@ struct NativeRunner::Impl {
                 for (size_t i = 0; i < (size_t) S * max_blocks[g]; i++) host[o_bt[g] + i] = 0;
             }
         }
-        int t0 = 0, r = 0, max_q = 0, max_ctx = 0;
-        bool identity = true;
+        // The sequences of a step are laid out with the single decoded tokens first (in their given order), the
+        // portions of prompts after them, so that attention can give each kind to its kernel; the wanted rows keep
+        // the order of the entries as given.
+        std::vector<int> order(n_real), row_base(n_real + 1, 0);
+        int n_single = 0;
+        for (int i = 0; i < n_real; i++) {
+            row_base[i + 1] = row_base[i] + batch.entries[i].n_want;
+            if (batch.entries[i].n_tokens == 1) n_single++;
+        }
+        const bool mixed = slot == nullptr && n_single > 0 && n_single < n_real;
+        {
+            int a = 0, b = mixed ? n_single : 0;
+            for (int i = 0; i < n_real; i++) {
+                if (!mixed) order[i] = i;
+                else if (batch.entries[i].n_tokens == 1) order[a++] = i;
+                else order[b++] = i;
+            }
+        }
+        int t0 = 0, max_q = 0, max_ctx = 0, decode_max_ctx = 0;
         host[o_cu] = 0;
         for (int s = 0; s < n_real; s++) {
-            const StepEntry & e = batch.entries[s];
+            const StepEntry & e = batch.entries[order[s]];
+            int r = row_base[order[s]];
             const int n = e.n_tokens;
             for (int i = 0; i < n; i++) {
                 host[o_tok + t0 + i] = e.tokens[i];
@@ -667,7 +723,6 @@ struct NativeRunner::Impl {
                 for (int i = 0; i < e.n_want; i++) {
                     const int w = e.want[i];
                     if (w < 0 || w >= n) throw std::invalid_argument("wanted place " + std::to_string(w) + " is outside this step's " + std::to_string(n) + " tokens");
-                    if (t0 + w != r) identity = false;
                     host[o_rows + r++] = t0 + w;
                 }
             }
@@ -688,9 +743,12 @@ struct NativeRunner::Impl {
             }
             max_q = std::max(max_q, n);
             max_ctx = std::max(max_ctx, e.start + n);
+            if (mixed && s < n_single) decode_max_ctx = std::max(decode_max_ctx, e.start + n);
             t0 += n;
         }
-        if (slot == nullptr && r != N) identity = false;
+        bool identity = R == N;                               // every token's logits wanted, in the order of the tokens
+        if (slot == nullptr)
+            for (int i = 0; identity && i < R; i++) identity = host[o_rows + i] == i;
         st.upload(total, stream);
         const int32_t * dev = st.dev;
         si = StepInts();
@@ -702,6 +760,8 @@ struct NativeRunner::Impl {
         si.max_q_len = max_q; si.max_ctx = max_ctx;
         if (slot != nullptr) { si.max_q_len = 1; si.max_ctx = slot->ctx_bucket; si.n_split = slot->n_split; }
         si.decode_only = si.max_q_len == 1;
+        si.decode_seqs = mixed ? n_single : 0;
+        si.decode_max_ctx = decode_max_ctx;
         si.rows_identity = slot != nullptr || identity;
         si.upload_bytes = (int) (total * sizeof(int32_t));
     }
@@ -899,6 +959,7 @@ NativeRunner::~NativeRunner() {
     if (m.attn_counters) cudaFree(m.attn_counters);
     for (void * p : m.retired_scratch) cudaFree(p);
     if (m.cap_stream) cudaStreamDestroy(m.cap_stream);
+    if (m.mixed_stream) { cudaStreamDestroy(m.mixed_stream); cudaEventDestroy(m.mixed_fork); cudaEventDestroy(m.mixed_join); }
     if (m.side_stream) cudaStreamDestroy(m.side_stream);
     for (void * h : m.libs) dlclose(h);
 }

@@ -52,7 +52,7 @@ class _RunnerOptions(Structure):
     _fields_ = [(n, c_int) for n in ("max_num_seqs", "max_model_len", "cuda_graphs", "weight_prefetch", "prefetch_window_mb",
                                      "tcgen05_min_tiles", "library_gemm_only", "fuse_norm", "fused_decode", "attention_tc",
                                      "cluster_merge", "tcgen05_pair", "decode_stages", "max_splits", "decode_ctas_per_sm",
-                                     "stream_product", "stream_stages", "pdl_stream", "decode_tma")]
+                                     "stream_product", "stream_stages", "pdl_stream", "decode_tma", "split_mixed")]
 
 
 class _Sampling(Structure):
@@ -191,7 +191,7 @@ class NativeStep:
         opt = _RunnerOptions(max_num_seqs, max_model_len, int(cuda_graphs), int(weight_prefetch),
                              int(os.environ.get("IIAN_PREFETCH_WINDOW_MB", "8")), K.TCGEN05_MIN_TILES, int(K.LIBRARY_GEMM_ONLY),
                              int(K.FUSE_NORM), int(K.FUSED_DECODE), int(K.ATTENTION_TC), int(K.CLUSTER_MERGE), int(K.TCGEN05_PAIR),
-                             K.DECODE_STAGES, K.MAX_SPLITS, K.DECODE_CTAS_PER_SM, int(K.STREAM_PRODUCT), K.STREAM_STAGES, int(pdl_for("gemm_stream")), int(K.DECODE_TMA))
+                             K.DECODE_STAGES, K.MAX_SPLITS, K.DECODE_CTAS_PER_SM, int(K.STREAM_PRODUCT), K.STREAM_STAGES, int(pdl_for("gemm_stream")), int(K.DECODE_TMA), int(K.SPLIT_MIXED))
         self._keep += [layers, calls, paths, desc]
         with torch.cuda.device(model.device):
             self._h = lib().iian_runner_new(ctypes.byref(desc), paths, manager._h, ctypes.byref(opt))

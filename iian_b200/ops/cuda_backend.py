@@ -756,6 +756,10 @@ class CudaKernels:
     # decode attention fetches its K/V tiles by TMA (head size 128, pages of 8 to 64 tokens); IIAN_DECODE_TMA=0: cp.async
     DECODE_TMA = os.environ.get("IIAN_DECODE_TMA", "1") not in ("0", "false", "off")
 
+    # native step function, mixed steps: the decoded tokens' attention runs on the decode kernel on a second stream
+    # beside the prefill kernel; IIAN_SPLIT_MIXED=0: one launch of the prefill kernel for all sequences of the step
+    SPLIT_MIXED = os.environ.get("IIAN_SPLIT_MIXED", "1") not in ("0", "false", "off")
+
     def _decode_status(self, device):
         """The status words the decode kernel's TMA form reports to (the ones of the tcgen05 kernels), or None: the
         cp.async form."""

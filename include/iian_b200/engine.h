@@ -113,6 +113,7 @@ struct RunnerOptions {
     int stream_stages = 12;         // 12: one CTA per SM with the deep ring; 6: two CTAs per SM
     bool pdl_stream = true;         // launch the streaming product with programmatic stream serialization
     bool decode_tma = true;         // decode attention fetches K/V tiles by TMA (head size 128) instead of cp.async
+    bool split_mixed = true;        // mixed steps: decoded tokens' attention on the decode kernel, on a second stream
 };
 
 // Paths of the kernel libraries (one shared object per source, see iian_b200/csrc/build.py); empty: not needed.

@@ -37,7 +37,7 @@ typedef struct {
 typedef struct {
     int max_num_seqs, max_model_len, cuda_graphs, weight_prefetch, prefetch_window_mb, tcgen05_min_tiles, library_gemm_only,
         fuse_norm, fused_decode, attention_tc, cluster_merge, tcgen05_pair, decode_stages, max_splits, decode_ctas_per_sm,
-        stream_product, stream_stages, pdl_stream, decode_tma;
+        stream_product, stream_stages, pdl_stream, decode_tma, split_mixed;
 } IianRunnerOptions;
 
 const char * iian_engine_last_error(void);
