@@ -141,3 +141,51 @@ def test_trace_run_with_the_native_step_function(folders, tmp_path):
     assert outs[0].keys() == outs[1].keys() and len(outs[0]) > 0
     for f in outs[0]:
         assert np.array_equal(outs[0][f], outs[1][f]), f"{f}: the two step functions wrote different logits"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixed_step_in_any_order_of_its_entries(folders, dtype, monkeypatch):
+    """The native step function lays a mixed step out with the single decoded tokens first and, in bfloat16 at head
+    size 128, gives their attention to the decode kernel beside the prefill kernel; the logits come back in the order
+    of the entries as given, and match the plain implementation and the Python step function, whatever that order."""
+    from iian_b200.engine.model import Model
+    from iian_b200.engine.replay import TraceReplayer
+    from iian_b200.ops import cuda_backend
+    from helpers import max_error, plain_logits
+    monkeypatch.setattr(cuda_backend.CudaKernels, "TCGEN05_MIN_TILES", 0)
+    name = "D"
+    v = TINY[name]["vocab_size"]
+    reqs = {rid: random_tokens(v, n, 70 + i) for i, (rid, n) in enumerate([("a", 90), ("b", 41), ("c", 77), ("d", 30)])}
+    # b and d are fed whole first; then steps in which portions of a and c stand before, between and behind single
+    # tokens of b and d (which are fed again from their caches: a request may end and start anew under the same name)
+    head = {"b": 36, "d": 25}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": reqs[r][:n], "want": [n - 1]} for r, n in head.items()], "end": []}]
+    cuts = {"a": [0, 20, 52, 70, 90], "c": [0, 33, 50, 61, 77]}
+    for k in range(4):
+        ents = []
+        order = [["a", "b", "c", "d"], ["b", "a", "d", "c"], ["a", "c", "b", "d"], ["d", "c", "b", "a"]][k]
+        for r in order:
+            if r in head:
+                p = head[r] + k
+                ents.append({"id": r, "tokens": [reqs[r][p]], "want": [0]})
+            else:
+                lo, hi = cuts[r][k], cuts[r][k + 1]
+                ents.append({"id": r, "tokens": reqs[r][lo:hi], "want": [0, hi - lo - 1]})
+        steps.append({"step": k + 1, "entries": ents, "end": []})
+    steps[-1]["end"] = list(reqs)
+    model = Model.from_folder(folders[name], dtype, "cuda:0")
+    got = []
+    for native in (False, True):
+        rp = TraceReplayer(model, 512, BLOCK_SIZE[name], 4, native=native)
+        got.append(replay_and_collect(rp, steps))
+        rp.runner.check_device_status()
+        if native and dtype == "bfloat16":
+            by = rp.runner.launches_by_entry()
+            assert rp.runner.native.launches_of("attention_mma") > 0 and by.get("attention_tc", 0) > 0
+    want = plain_logits(folders[name], reqs)
+    limit = 2e-5 if dtype == "float32" else 2.5e-2 * max(w.abs().max().item() for w in want.values())
+    for g in got:
+        err, where = max_error(g, want)
+        assert err <= limit, (dtype, err, where)
+    if dtype == "float32":
+        assert all(torch.equal(got[0][k], got[1][k]) for k in got[0])
