@@ -176,8 +176,9 @@ def main() -> int:
     max_b = max(args.batch, 1 if args.skip_points else 64)
     per_req = PROMPT_LEN + W + K + 48
     longest_prefill = PREFILL_TOKENS if args.skip_points else max(PREFILL_TOKENS, 8192)
-    ecfg = EngineConfig(dtype="bfloat16", max_model_len=max(CONTEXT_LEN, longest_prefill + 64),
-                        kv_cache_tokens=max(CONTEXT_LEN, longest_prefill + 64, max_b * per_req),
+    long_ctx = 0 if args.skip_points else 8192 + W + K + 64          # the decode points at 8,192 tokens of context
+    ecfg = EngineConfig(dtype="bfloat16", max_model_len=max(CONTEXT_LEN, longest_prefill + 64, long_ctx),
+                        kv_cache_tokens=max(CONTEXT_LEN, longest_prefill + 64, max_b * per_req, 8 * long_ctx),
                         block_size=16, enable_prefix_caching=False, warmup=True, cuda_graphs=not args.no_cuda_graphs,
                         sched=SchedulerConfig(max_num_seqs=max_b, max_num_batched_tokens=2048))
     engine = Engine(model, ecfg)
@@ -221,6 +222,11 @@ def main() -> int:
             r = wl.measure_decode(runner, src, b, PROMPT_LEN, W, K)
             points[f"decode_b{b}"] = r["tokens_per_s"]
             points[f"decode_b{b}_hbm_frac"] = acc.decode_bytes(b, r["ctx_avg"]) / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+        # ---- decode at a context of 8,192 tokens (attention reads eight times the K/V of the headline's) ----------
+        for b in (1, 8):
+            r = wl.measure_decode(runner, src, b, 8192, W, max(8, K // 2))
+            points[f"decode_b{b}_ctx8k"] = r["tokens_per_s"]
+            points[f"decode_b{b}_ctx8k_hbm_frac"] = acc.decode_bytes(b, r["ctx_avg"]) / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
         # ---- prefill of one 2,048-token prompt (and of 512 and 8,192 tokens) ---------------------------
         for T in (PREFILL_TOKENS, 512, 8192):
             r = wl.measure_prefill(runner, src, T, warmup=W if T == PREFILL_TOKENS else 2, repeats=5 if T == PREFILL_TOKENS else 3)
