@@ -10,7 +10,7 @@ parts a global hyper-parameter struct; here every constant travels in ``PartSpec
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Sequence
+from typing import Any, Mapping, Optional, Sequence, Tuple
 
 
 @dataclass(frozen=True)
@@ -30,14 +30,28 @@ class LayerSpec:
     """The parts of one layer and how they are arranged.
 
     ``arrangement`` names a block implementation (``"pre_norm_residual"``: x += mixer(norm(x));
-    x += ffn(norm(x)), the order of src/iian/arch/qwen3.cpp:74-100).
+    x += ffn(norm(x)), the order of src/iian/arch/qwen3.cpp:74-100).  The four named slots are what that
+    arrangement uses; another arrangement takes the slots it needs (a slot it does not use stays ``None``) and may
+    define further ones in ``extra`` as (slot name, part specification) pairs -- a norm after the mixer, a second
+    mixer.  The block that implements the arrangement builds its parts from these and says under which slot names
+    their tensors go (``parts()``).
     """
 
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
     arrangement: str = "pre_norm_residual"
+    extra: Tuple[Tuple[str, PartSpec], ...] = ()
+
+    def slot(self, name: str) -> Optional[PartSpec]:
+        """The specification in slot ``name`` (one of the four named slots or one of ``extra``), or None."""
+        if name in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm"):
+            return getattr(self, name)
+        for n, spec in self.extra:
+            if n == name:
+                return spec
+        return None
 
 
 @dataclass(frozen=True)

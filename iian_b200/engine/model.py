@@ -130,15 +130,19 @@ class Model:
     def cache_needs(self) -> Dict[int, object]:
         """cache id -> KVNeed | StateNeed, taken from the mixer of the call that writes it."""
         needs: Dict[int, object] = {}
+
+        def need_of(block):
+            return block.cache_need() if hasattr(block, "cache_need") else block.mixer.cache_need()
+
         for call in self.spec.order:
-            need = self.blocks[call.layer].mixer.cache_need()
+            need = need_of(self.blocks[call.layer])
             if need is None:
                 continue
             if call.writes_cache:
                 needs[call.cache] = need
         for call in self.spec.order:
             if not call.writes_cache:
-                need = self.blocks[call.layer].mixer.cache_need()
+                need = need_of(self.blocks[call.layer])
                 if need is not None and needs.get(call.cache) != need:
                     raise ValueError(f"layer {call.layer} reads cache {call.cache}, whose owner stores something else")
         return needs

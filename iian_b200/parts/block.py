@@ -1,5 +1,12 @@
 """How a layer's parts are arranged.
 
+A block implements one arrangement (``LayerSpec.arrangement``) and is registered under its name with
+``register_block``.  What the model asks of a block: ``__init__(spec, dtype, device)`` builds its parts from the
+slots of the ``LayerSpec`` it understands; ``parts()`` lists them with the slot names their tensors go under;
+``cache_need()`` says what the cache of a call to this layer must hold (a ``KVNeed``, a ``StateNeed`` or None);
+``forward(residual, delta, ctx, cache, writes_cache, select_rows)`` takes the float32 residual stream and the
+not-yet-added output of whatever ran before, and returns the same pair.
+
 ``pre_norm_residual`` (src/iian/arch/qwen3.cpp:74-100): ``x += mixer(norm(x))``; ``x += ffn(norm(x))``.
 The add that closes one sub-layer is fused into the norm that opens the next: a block receives the
 float32 residual and the not-yet-added output of the previous sub-layer (``delta``) and returns the
@@ -23,6 +30,9 @@ from .base import FEED_FORWARDS, MIXERS, NORMS, NormOut, Prenormed, register_blo
 @register_block("pre_norm_residual")
 class PreNormResidualBlock:
     def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        missing = [s for s in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm") if spec.slot(s) is None]
+        if missing:
+            raise ValueError(f"arrangement pre_norm_residual needs the slots {', '.join(missing)}")
         self.spec = spec
         self.dtype = dtype
         self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
@@ -34,6 +44,9 @@ class PreNormResidualBlock:
         """(slot name, part) pairs; the slot name is what the architecture maps to file names."""
         return (("mixer_norm", self.mixer_norm), ("mixer", self.mixer),
                 ("feed_forward_norm", self.feed_forward_norm), ("feed_forward", self.feed_forward))
+
+    def cache_need(self):
+        return self.mixer.cache_need()
 
     accepts_next_norm = True
 

@@ -15,7 +15,7 @@ import torch
 
 from helpers import first_bad, random_tokens, replay_and_collect, trace_mixed, trace_portions, trace_tail, trace_whole
 from iian_b200.parts.base import StateNeed
-from toy_model import CFG, CFG_EMA_ONLY, CFG_ROUTED, plain_toy, plain_toy_greedy, register_toy, unregister_toy, write_toy
+from toy_model import CFG, CFG_EMA_ONLY, CFG_PARALLEL, CFG_ROUTED, plain_toy, plain_toy_greedy, register_toy, unregister_toy, write_toy
 
 pytestmark = pytest.mark.gpu
 
@@ -25,7 +25,8 @@ def toys(tmp_path_factory):
     register_toy()
     out = {"mixed": (write_toy(str(tmp_path_factory.mktemp("toy")), CFG), CFG),
            "ema_only": (write_toy(str(tmp_path_factory.mktemp("toy_ema")), CFG_EMA_ONLY, seed=10), CFG_EMA_ONLY),
-           "routed": (write_toy(str(tmp_path_factory.mktemp("toy_routed")), CFG_ROUTED, seed=11), CFG_ROUTED)}
+           "routed": (write_toy(str(tmp_path_factory.mktemp("toy_routed")), CFG_ROUTED, seed=11), CFG_ROUTED),
+           "parallel": (write_toy(str(tmp_path_factory.mktemp("toy_parallel")), CFG_PARALLEL, seed=12), CFG_PARALLEL)}
     yield out
     unregister_toy()
 
@@ -50,7 +51,7 @@ def test_toy_is_built_from_registered_parts(toy):
 @pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
-@pytest.mark.parametrize("layout", ["mixed", "ema_only", "routed"])
+@pytest.mark.parametrize("layout", ["mixed", "ema_only", "routed", "parallel"])
 def test_toy_steps_like_its_plain_model(toys, layout, dtype, mode, graphs):
     """With ``graphs`` the decode-only steps are replayed from captured CUDA graphs: the state must advance
     exactly once per step (also on the step that captures a new graph)."""

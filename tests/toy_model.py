@@ -8,7 +8,9 @@ attention at all, so the model needs no pages.  The toy mixer computes with torc
 device tensors only (never on the host lists), so its steps can be replayed from CUDA graphs; the attention,
 norm and feed-forward parts beside it are the framework's.  ``plain_toy`` is the same model written out
 separately in float64 on whole sequences.  A third layout has a feed-forward with routing (every token goes to 2 of
-5 experts) and a position encoding that is no rotation (offsets added to Q and K), both defined here.
+5 experts) and a position encoding that is no rotation (offsets added to Q and K), both defined here.  A fourth
+arranges a layer's parts otherwise than the framework's block does: one norm feeds mixer and feed-forward side by
+side, another layer has no feed-forward and norms its mixer's output (a slot of its own in ``LayerSpec.extra``).
 """
 import math
 import os
@@ -18,8 +20,8 @@ import torch
 import plain_qwen3 as plain
 from iian_b200.config.registry import Architecture, get_architecture, register_architecture, unregister_architecture
 from iian_b200.config.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
-from iian_b200.parts.base import (FEED_FORWARDS, MIXERS, POSITIONS, FeedForward, Mixer, PositionEncoding, StateNeed,
-                                  register_feed_forward, register_mixer, register_position)
+from iian_b200.parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer, PositionEncoding, StateNeed,
+                                  register_block, register_feed_forward, register_mixer, register_position)
 from iian_b200.weights.loader import TensorSpec
 
 CFG = {"architectures": ["ToyForCausalLM"], "vocab_size": 97, "hidden_size": 64, "heads": 4, "kv_heads": 2, "head_dim": 16,
@@ -27,6 +29,9 @@ CFG = {"architectures": ["ToyForCausalLM"], "vocab_size": 97, "hidden_size": 64,
 CFG_EMA_ONLY = dict(CFG, layout="ema_only", vocab_size=61, hidden_size=48, ffn=80, decay=0.6)
 # attention with a position encoding of the test's own (a table of offsets added to Q and K, not a rotation) and a
 # feed-forward that routes every token to 2 of 5 small experts
+# layers arranged otherwise than Qwen3's: one norm feeding mixer and feed-forward side by side, a layer without a
+# feed-forward whose mixer output passes a norm of its own -- an arrangement defined here, beside the framework's own
+CFG_PARALLEL = dict(CFG, layout="parallel", vocab_size=71, hidden_size=80, heads=5, kv_heads=5, head_dim=16, ffn=112, decay=0.7)
 CFG_ROUTED = dict(CFG, layout="routed", vocab_size=83, hidden_size=72, heads=6, kv_heads=3, head_dim=24, ffn=40, experts=5, top_k=2,
                   max_position=160)
 
@@ -139,6 +144,45 @@ class ToyOffsets(PositionEncoding):
         qk.copy_((qk.float() + off[:, None, :]).to(qkv.dtype))               # V is left alone
 
 
+class ToyParallelBlock:
+    """Another arrangement of a layer's parts than the framework's: ``x += mixer(norm(x)) + ffn(norm(x))`` with one
+    norm feeding both (the feed-forward slot may be empty), and optionally a norm of the mixer's output before it is
+    added (slot ``mixer_post_norm`` in ``LayerSpec.extra``).  The interface is what the model asks of any block."""
+
+    def __init__(self, spec, dtype, device):
+        self.dtype = dtype
+        self.norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.ffn = FEED_FORWARDS.build(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        post = spec.slot("mixer_post_norm")
+        self.post = NORMS.build(post, dtype, device) if post is not None else None
+
+    def parts(self):
+        out = [("mixer_norm", self.norm), ("mixer", self.mixer)]
+        if self.ffn is not None:
+            out.append(("feed_forward", self.ffn))
+        if self.post is not None:
+            out.append(("mixer_post_norm", self.post))
+        return tuple(out)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, residual, delta, ctx, cache, writes_cache, select_rows):
+        h = self.norm.forward(residual, delta, ctx)              # residual += delta; h = norm(residual)
+        h_ffn = h.clone() if self.ffn is not None else None      # the mixer may reuse the norm's buffer
+        y = self.mixer.forward(h, ctx, cache, writes_cache)
+        if self.post is not None:
+            y32 = y.float()
+            y = (y32 * torch.rsqrt(y32.pow(2).mean(dim=-1, keepdim=True) + self.post.eps) * self.post.weight).to(self.dtype)
+        if self.ffn is not None:
+            y = (y.float() + self.ffn.forward(h_ffn, ctx).float()).to(self.dtype)
+        if select_rows is not None:
+            idx = select_rows.long()
+            residual, y = residual.index_select(0, idx), y.index_select(0, idx)
+        return residual, y
+
+
 class ToyArch(Architecture):
     name = "ToyForCausalLM"
 
@@ -160,6 +204,11 @@ class ToyArch(Architecture):
         if c.get("layout", "mixed") == "ema_only":
             layers = (LayerSpec(ema, ffn, norm, norm), LayerSpec(ema, ffn, norm, norm))
             order = (LayerCall(0, 0), LayerCall(1, 1))
+        elif c.get("layout") == "parallel":
+            layers = (LayerSpec(mixer=attn, feed_forward=ffn, mixer_norm=norm, arrangement="toy_parallel"),
+                      LayerSpec(mixer=ema, mixer_norm=norm, arrangement="toy_parallel", extra=(("mixer_post_norm", norm),)),
+                      LayerSpec(attn, ffn, norm, norm))
+            order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2))
         elif c.get("layout") == "routed":
             offsets = PartSpec("toy_offsets", {"head_dim": c["head_dim"], "max_position": c["max_position"]})
             attn_off = PartSpec("attention", dict(attn.params, position=offsets))
@@ -181,6 +230,7 @@ def register_toy():
     register_mixer("toy_ema")(ToyEma)
     register_feed_forward("toy_routed")(ToyRoutedFF)
     register_position("toy_offsets")(ToyOffsets)
+    register_block("toy_parallel")(ToyParallelBlock)
     register_architecture(ToyArch)
     return get_architecture("ToyForCausalLM")
 
@@ -190,6 +240,7 @@ def unregister_toy():
     MIXERS.unregister("toy_ema")
     FEED_FORWARDS.unregister("toy_routed")
     POSITIONS.unregister("toy_offsets")
+    BLOCKS.pop("toy_parallel", None)
 
 
 def write_toy(d, cfg, seed=9):
@@ -213,9 +264,8 @@ def plain_toy(d, tokens, c=CFG):
         table = (0.5 * torch.sin(pos.double()[:, None] * (j + 1) * 0.37)).float().double()
         return t + table[:, None, :]
 
-    def attn_layer(x, li, cache_id, writes, offsets=False):
+    def attn_out(h, li, cache_id, writes, offsets=False):
         p = f"layer.{li}."
-        h = plain.rms_norm(x, w[p + "mixer_norm.weight"], c["eps"])
         q = place((h @ w[p + "mixer.q_proj.weight"].T).view(T, nh, hd), offsets)
         if writes:
             k = place((h @ w[p + "mixer.k_proj.weight"].T).view(T, nkv, hd), offsets)
@@ -223,17 +273,23 @@ def plain_toy(d, tokens, c=CFG):
             kv[cache_id] = (k, v)
         k, v = kv[cache_id]
         a = plain.attention(q, k, v, 1 / math.sqrt(hd), None).reshape(T, nh * hd)
-        return x + a @ w[p + "mixer.o_proj.weight"].T
+        return a @ w[p + "mixer.o_proj.weight"].T
 
-    def ema_layer(x, li):
-        p = f"layer.{li}."
-        h = plain.rms_norm(x, w[p + "mixer_norm.weight"], c["eps"])
+    def attn_layer(x, li, cache_id, writes, offsets=False):
+        h = plain.rms_norm(x, w[f"layer.{li}.mixer_norm.weight"], c["eps"])
+        return x + attn_out(h, li, cache_id, writes, offsets)
+
+    def ema_out(h, li):
         state = torch.zeros(c["hidden_size"], dtype=torch.float64)
         ys = []
         for t in range(T):
             state = c["decay"] * state + h[t]
-            ys.append(w[p + "mixer.w"] @ state)
-        return x + torch.stack(ys)
+            ys.append(w[f"layer.{li}.mixer.w"] @ state)
+        return torch.stack(ys)
+
+    def ema_layer(x, li):
+        h = plain.rms_norm(x, w[f"layer.{li}.mixer_norm.weight"], c["eps"])
+        return x + ema_out(h, li)
 
     def ffn(x, li):
         p = f"layer.{li}."
@@ -259,6 +315,13 @@ def plain_toy(d, tokens, c=CFG):
     if c.get("layout", "mixed") == "ema_only":
         x = ffn(ema_layer(x, 0), 0)
         x = ffn(ema_layer(x, 1), 1)
+    elif c.get("layout") == "parallel":
+        h = plain.rms_norm(x, w["layer.0.mixer_norm.weight"], c["eps"])        # one norm feeds mixer and feed-forward
+        x = x + attn_out(h, 0, 0, True) + plain.gated_mlp(h, w["layer.0.feed_forward.gate_proj.weight"],
+                                                        w["layer.0.feed_forward.up_proj.weight"], w["layer.0.feed_forward.down_proj.weight"])
+        h = plain.rms_norm(x, w["layer.1.mixer_norm.weight"], c["eps"])        # no feed-forward; the mixer's output is normed
+        x = x + plain.rms_norm(ema_out(h, 1), w["layer.1.mixer_post_norm.weight"], c["eps"])
+        x = ffn(attn_layer(x, 2, 2, True), 2)
     elif c.get("layout") == "routed":
         x = routed(attn_layer(x, 0, 0, True, offsets=True), 0)
         x = ffn(attn_layer(x, 1, 1, True, offsets=True), 1)
