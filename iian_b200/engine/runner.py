@@ -77,8 +77,9 @@ class Workspace:
 
 
 @dataclass
-class AttentionMeta:
-    """What the attention kernels need for one page group."""
+class PageMeta:
+    """What a mixer that keeps its past in pages needs for one page group: where each token of the step goes, and each
+    sequence's block table and length."""
 
     positions: torch.Tensor        # i32 [N]
     seq_of_token: torch.Tensor     # i32 [N]   (-1: padding token)
@@ -93,7 +94,9 @@ class AttentionMeta:
     decode_only: bool
     h_q_len: Sequence[int] = ()
     h_ctx_len: Sequence[int] = ()
-    n_split: Optional[int] = None  # fixed number of key splits (captured decode graphs); None: the kernel layer decides
+
+
+AttentionMeta = PageMeta
 
 
 class StepContext:
@@ -101,7 +104,8 @@ class StepContext:
         self.workspace = workspace
         self.tokens = self.positions = self.seq_of_token = self.cu_q = self.ctx_len = None
         self.state_slots = self.out_rows = None
-        self.metas: List[AttentionMeta] = []
+        self.metas: List[PageMeta] = []
+        self.plans: Dict[int, object] = {}             # captured graphs: what each mixer asked to keep fixed (Mixer.graph_plan)
         self.step_cache: Dict[object, object] = {}     # what parts compute once per forward pass and share (cleared by Model.forward)
         self.num_tokens = self.num_seqs = 0
         self.h_q_start: List[int] = []
@@ -117,8 +121,15 @@ class StepContext:
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
 
-    def attention_meta(self, group: int) -> AttentionMeta:
+    def page_meta(self, group: int) -> PageMeta:
         return self.metas[group]
+
+    attention_meta = page_meta
+
+    def graph_plan(self, part):
+        """What ``part`` asked to keep fixed inside the captured graph this step is replayed from (its own
+        ``graph_plan`` answer), or None on an eager step."""
+        return self.plans.get(id(part))
 
 
 class ModelRunner:
@@ -343,12 +354,13 @@ class ModelRunner:
         ctx.rows_identity = slot is not None or rows == list(range(N))
         ctx.upload_bytes = total * 4
         for g in range(n_groups):
-            ctx.metas.append(AttentionMeta(
+            ctx.metas.append(PageMeta(
                 positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
                 block_table=view(r_bt[g], (S, max_blocks[g])), slots=view(r_slots[g]),
                 num_seqs=S, num_tokens=N, max_q_len=ctx.max_q_len, max_ctx=ctx.max_ctx,
-                decode_only=ctx.decode_only, h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len,
-                n_split=slot.n_split if slot is not None else None))
+                decode_only=ctx.decode_only, h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len))
+        if slot is not None:
+            ctx.plans = slot.plans
         return ctx
 
     def build_decode_context(self, entries: Sequence[StepEntry], slot: "_GraphSlot") -> StepContext:
@@ -423,11 +435,12 @@ class ModelRunner:
             ctx.rows_identity = True
             ctx.upload_bytes = total * 4
             for g in range(n_groups):
-                ctx.metas.append(AttentionMeta(
+                ctx.metas.append(PageMeta(
                     positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
                     block_table=view(lay["bt"][g], S * mb, (S, mb)), slots=view(lay["slots"][g], S),
                     num_seqs=S, num_tokens=S, max_q_len=1, max_ctx=slot.ctx_bucket, decode_only=True,
-                    h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len, n_split=slot.n_split))
+                    h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len))
+            ctx.plans = slot.plans
             slot.ctx = ctx
         ctx.h_q_start[:] = range(n)
         ctx.h_q_len[:] = [1] * n
@@ -495,9 +508,13 @@ class ModelRunner:
         slot.pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
         slot.workspace = Workspace(self.device)
         slot.copy_done = None
-        kv_heads = [n.num_kv_heads for n in self.model.cache_needs().values() if isinstance(n, KVNeed)]
         k = ops.kernels()
-        slot.n_split = k.attention_splits(num_seqs, min(kv_heads), ctx_bucket) if kv_heads and hasattr(k, "attention_splits") else 1
+        # what every mixer wants kept fixed inside this graph (attention: its number of key splits)
+        slot.plans = {}
+        for part in self.model.all_parts():
+            plan = part.graph_plan(num_seqs, ctx_bucket) if hasattr(part, "graph_plan") else None
+            if plan is not None:
+                slot.plans[id(part)] = plan
         # Warm up eagerly on a batch of padding sequences only (it loads the kernels, sizes every buffer and
         # records the order in which weights are streamed, but stores nothing: padding tokens have cache cell
         # -1 and state slot -1), then capture the same launches -- with a side stream that prefetches the next
@@ -536,8 +553,8 @@ class ModelRunner:
 class _GraphSlot:
     """Everything a captured decode graph owns: fixed-shape integer buffers, workspace, output."""
 
-    num_seqs = ctx_bucket = max_blocks = n_split = launches = 0
-    staging = pinned = workspace = copy_done = graph = logits = None
+    num_seqs = ctx_bucket = max_blocks = launches = 0
+    staging = pinned = workspace = copy_done = graph = logits = plans = None
     layout = host_ptr = sig = c_caches = c_tokens = c_starts = c_fresh = ctx = None      # kept between steps by build_decode_context
     n_last = -1
 

@@ -587,11 +587,12 @@ class CudaKernels:
 
     def paged_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                         meta, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                        window: Optional[int]) -> None:
+                        window: Optional[int], n_split: Optional[int] = None) -> None:
         """``meta``: an object with ``positions``, ``seq_of_token``, ``block_table`` [S, max_blocks],
         ``ctx_len`` [S] (int32 CUDA tensors) and host-side hints (``num_seqs``, ``max_q_len``, ``max_ctx``,
-        ``decode_only``)."""
-        self._attention_dispatch(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale, window)
+        ``decode_only``).  ``n_split``: a fixed number of key splits for the decode form (a captured graph's); None:
+        chosen per launch."""
+        self._attention_dispatch(q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, head_dim, scale, window, n_split)
 
     # prefill portions on tcgen05 (csrc/attention_tc.cu); IIAN_ATTENTION_TC=0 keeps them on the mma.sync kernel
     ATTENTION_TC = os.environ.get("IIAN_ATTENTION_TC", "1") not in ("0", "false", "off")
@@ -621,14 +622,14 @@ class CudaKernels:
                   num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0,
                   status.data_ptr(), _stream()), "attention_tc")
 
-    def _attention_dispatch(self, q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, window) -> None:
+    def _attention_dispatch(self, q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, window, n_split=None) -> None:
         if self._attention_tc_ok(q, k_cache, meta, nh, nkv, hd):
             self.paged_attention_tc(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                                     scale=scale, window=window)
             return
         if q.dtype == torch.bfloat16 and hd in (64, 128):
             self.paged_attention_mma(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
-                                     scale=scale, window=window)
+                                     scale=scale, window=window, n_split=n_split)
         else:
             self.paged_attention_generic(q, k_cache, v_cache, out, meta, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                                          scale=scale, window=window)
@@ -726,7 +727,7 @@ class CudaKernels:
         if small_tiles is None:
             small_tiles = decode
         if n_split is None:
-            n_split = getattr(meta, "n_split", None) or (self.attention_splits(meta.num_seqs, num_kv_heads, meta.max_ctx) if decode else 1)
+            n_split = self.attention_splits(meta.num_seqs, num_kv_heads, meta.max_ctx) if decode else 1
         if cluster is None:
             cluster = self.CLUSTER_MERGE
         cluster = bool(cluster and small_tiles and n_split in (2, 4, 8, 16))
@@ -794,7 +795,7 @@ class CudaKernels:
         if self._stages_set != self.DECODE_STAGES:
             self.set_decode_stages(self.DECODE_STAGES)
         if n_split is None:
-            n_split = getattr(meta, "n_split", None) or self.attention_splits(s_, num_kv_heads, meta.max_ctx)
+            n_split = self.attention_splits(s_, num_kv_heads, meta.max_ctx)
         if cluster is None:
             cluster = self.CLUSTER_MERGE
         cluster = bool(cluster and 2 <= n_split <= 16)

@@ -82,6 +82,13 @@ class Attention(Mixer):
             self.q_norm_w = tensors["q_norm.weight"].to(torch.float32).contiguous()
             self.k_norm_w = tensors["k_norm.weight"].to(torch.float32).contiguous()
 
+    def graph_plan(self, num_seqs: int, max_ctx: int):
+        """The number of key splits of decode attention is part of a captured graph (grid and cluster sizes)."""
+        k = ops.kernels()
+        if not hasattr(k, "attention_splits"):
+            return None
+        return {"n_split": k.attention_splits(num_seqs, self.nkv, max_ctx)}
+
     def cache_need(self) -> KVNeed:
         return KVNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 
@@ -124,7 +131,9 @@ class Attention(Mixer):
             k.linear(x, w, qkv)
         if not pos.fused:
             pos.apply(qkv, self.nh, nkv, self.hd, ctx)
-        meta = ctx.attention_meta(cache.group)
+        meta = ctx.page_meta(cache.group)
+        plan = ctx.graph_plan(self)
+        n_split = plan["n_split"] if plan else None         # fixed inside a captured graph, else chosen per launch
         attn = ctx.buf("attn", (n, self.q_size), self.dtype)
         rot_dim = pos.dim if pos.fused else 0
         table = pos.table(ctx) if pos.fused and hasattr(pos, "table") and pos.inv_freq is not None else None
@@ -135,7 +144,7 @@ class Attention(Mixer):
             k.attention_decode_fused(qkv, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
                                      head_dim=self.hd, scale=self.scale, window=self.window,
                                      q_weight=self.q_norm_w, k_weight=self.k_norm_w, eps=self.eps,
-                                     table=table if rot_dim else None, slots=meta.slots, write_kv=True)
+                                     table=table if rot_dim else None, slots=meta.slots, write_kv=True, n_split=n_split)
             return self._project_out(k, attn, ctx, norm_out)
         q = ctx.buf("q", (n, self.nh, self.hd), self.dtype)
         k.qk_norm_rope_store(
@@ -147,5 +156,5 @@ class Attention(Mixer):
             positions=ctx.positions, slots=meta.slots if writes_cache else None, write_kv=writes_cache, bias=bias,
             **({"table": table} if table is not None else {}))
         k.paged_attention(q, cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
-                          head_dim=self.hd, scale=self.scale, window=self.window)
+                          head_dim=self.hd, scale=self.scale, window=self.window, n_split=n_split)
         return self._project_out(k, attn, ctx, norm_out)

@@ -152,6 +152,13 @@ class Mixer(Part):
     def cache_need(self):
         return None
 
+    def graph_plan(self, num_seqs: int, max_ctx: int):
+        """What this mixer must keep fixed inside a captured graph for ``num_seqs`` sequences of one token with
+        contexts up to ``max_ctx`` (grid sizes, split counts: anything it would otherwise derive from the step's host
+        values), or None.  The runner asks once per captured graph and hands the answer back through
+        ``ctx.graph_plan(self)`` on every replayed step; on eager steps that returns None."""
+        return None
+
     def forward(self, x: torch.Tensor, ctx, cache, writes_cache: bool) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 

@@ -89,7 +89,7 @@ class FakeKernels:
                 k_cache[s // ps, :, s % ps, :] = k[t].to(k_cache.dtype)
                 v_cache[s // ps, :, s % ps, :] = v[t].to(v_cache.dtype)
 
-    def paged_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window):
+    def paged_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window, n_split=None):
         n = q.shape[0]
         ps = k_cache.shape[2]
         g = num_heads // num_kv_heads

@@ -9,7 +9,7 @@ import torch
 import plain_qwen3 as plain
 from iian_b200.cache.storage import KVView
 from iian_b200.config.spec import LayerSpec, PartSpec
-from iian_b200.engine.runner import AttentionMeta, StepContext, Workspace
+from iian_b200.engine.runner import PageMeta, StepContext, Workspace
 from iian_b200.parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, KVNeed
 
 pytestmark = pytest.mark.gpu
@@ -54,7 +54,7 @@ def make_ctx(seqs, page_size, num_pages, tables, rows=None):
     ctx.decode_only = ctx.max_q_len == 1
     ctx.out_rows = i32(rows if rows is not None else list(range(len(pos))))
     ctx.rows_identity = rows is None
-    ctx.metas = [AttentionMeta(positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
+    ctx.metas = [PageMeta(positions=ctx.positions, seq_of_token=ctx.seq_of_token, cu_q=ctx.cu_q, ctx_len=ctx.ctx_len,
                                block_table=bt.to(DEV), slots=i32(slots), num_seqs=len(seqs), num_tokens=len(pos),
                                max_q_len=ctx.max_q_len, max_ctx=ctx.max_ctx, decode_only=ctx.decode_only,
                                h_q_len=ctx.h_q_len, h_ctx_len=ctx.h_ctx_len)]
