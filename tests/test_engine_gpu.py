@@ -138,6 +138,43 @@ def test_temperature_sampling_follows_the_plain_walk(setup):
     assert r2.output_tokens == greedy, "top_k = 1 is greedy"
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_temperature_sampling_with_graphs_few_pages_and_shared_prefixes(setup, name):
+    """Sampling, CUDA-graph decode, preemption and prefix reuse together: in float32 every sampled token is still the
+    one the plain walk picks for the request's i-th uniform number, although requests are cut into portions, thrown
+    out for lack of pages and recomputed, start behind a cached prefix, and decode from replayed graphs."""
+    from iian_b200 import SamplingParams
+    d, cfg, w = setup[name]
+    v, bs = cfg["vocab_size"], BLOCK_SIZE[name]
+    shared = random_tokens(v, 2 * bs + 3, 500)
+    prompts = [shared + random_tokens(v, 4 + 7 * i, 510 + i) if i % 2 else random_tokens(v, 9 + 11 * i, 520 + i) for i in range(6)]
+    longest = max(len(p) for p in prompts) + 12
+    kv = -(-longest // bs) * bs + 2 * bs                                  # room for one long request and little more
+    eng = make_engine(d, "float32", name, budget=17, seqs=6, kv_cache_tokens=kv, max_model_len=kv, enable_prefix_caching=True,
+                      cuda_graphs=True)
+    reqs = [eng.submit(p, SamplingParams(temperature=0.8, seed=30 + i, max_tokens=12, ignore_eos=True)) for i, p in enumerate(prompts)]
+    for _ in range(5000):
+        if all(r.is_finished for r in reqs):
+            break
+        eng.step()
+    assert all(r.is_finished and len(r.output_tokens) == 12 for r in reqs)
+    st = eng.stats()
+    assert st.preemptions >= 1 and st.prefix_cache_hits >= 1 and eng.runner.num_graphs >= 1
+    for i, r in enumerate(reqs):
+        toks = list(prompts[i])
+        for k, tok in enumerate(r.output_tokens):
+            probs = plain.candidate_probs(plain.forward(cfg, w, toks)[-1].float(), 0.8)
+            u = stream(30 + i, k)
+            want = plain.sample_from(probs, u)
+            if tok != want:
+                cum = torch.cumsum(probs, 0)
+                target = u * cum[-1].item()
+                edge = min(abs(cum[tok].item() - target), abs(cum[tok].item() - probs[tok].item() - target))
+                assert edge < 1e-5 * cum[-1].item(), f"request {i} token {k}: engine {tok}, plain {want}"
+            toks.append(tok)
+    assert all(p.num_free == p.num_blocks for p in eng.cache.pools)
+
+
 def _collect_logits(eng):
     """(request id, position) -> the logits row the engine sampled that position's next token from."""
     rows = {}
