@@ -255,9 +255,7 @@ def run_serving(engine, requests, check_alone: int = 0) -> dict:
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     peak_usage, steps = 0.0, 0
-    while any(not r.is_finished for r in reqs):
-        if not engine.step():
-            break
+    while engine.step():               # False once no request is left to run
         steps += 1
         if steps % 8 == 0:
             peak_usage = max(peak_usage, engine.cache.usage)
@@ -266,7 +264,7 @@ def run_serving(engine, requests, check_alone: int = 0) -> dict:
     st = engine.stats()
     n_prompt = sum(len(t) for t, _, _ in requests)
     n_gen = sum(r.n_output for r in reqs)
-    errors = sum(1 for r in reqs if r.finish_reason.value == "error")
+    errors = sum(1 for r in reqs if not r.is_finished or r.finish_reason.value == "error")
     out = {"requests": len(reqs), "wall_s": secs, "steps": steps, "prompt_tokens": n_prompt, "generated_tokens": n_gen,
            "total_tok_s": (n_prompt + n_gen) / secs, "gen_tok_s": n_gen / secs, "prompt_tok_s": n_prompt / secs,
            "ttft_ms": st.ttft_ms_avg, "tpot_ms": st.tpot_ms_avg,
