@@ -44,6 +44,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="key splits of decode attention (0: the engine's choice)")
     ap.add_argument("--stages", type=int, default=0, help="decode attention: shared-memory tiles per CTA (2 or 3; 0: the default)")
+    ap.add_argument("--unsplit-stages", type=int, default=0, help="decode attention with unsplit keys: 2 or 3 tiles per CTA (0: the kernel's rule)")
     ap.add_argument("--tc", action="store_true", help="attention_prefill: the tcgen05 kernel instead of the mma.sync kernel")
     ap.add_argument("--no-cluster", action="store_true", help="decode attention: merge key splits through scratch memory")
     ap.add_argument("--iters", type=int, default=20)
@@ -63,6 +64,11 @@ def main(argv=None) -> int:
     k = CudaKernels()
     if args.stages and args.kernel != "gemm_stream":
         k.set_decode_stages(args.stages)
+    if args.unsplit_stages:
+        from ..ops.cuda_backend import _fn
+        from ctypes import c_int
+        if _fn("attention_mma", "iian_attention_unsplit_stages", [c_int])(args.unsplit_stages) != 0:
+            raise SystemExit("kernel_bench: --unsplit-stages takes 2 or 3")
     dev = torch.device("cuda:0")
     bf = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(0)

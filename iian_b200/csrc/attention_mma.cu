@@ -974,11 +974,34 @@ static int launch_decode_st(const AttnParams & p, const KvMaps & maps, int S, in
     return e == cudaSuccess ? IIAN_OK : 1000 + (int) e;
 }
 
+static int decode_sm_count() {
+    static int n[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (n[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev] = v;
+    }
+    return n[dev];
+}
+
 static int g_decode_stages = 2;
+static int g_unsplit_stages = 0;        // 0: the rule below; 2 or 3: that many for unsplit keys
 template <int HD, bool CLUSTER, bool FUSED = false>
 static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
     // unsplit keys mean many sequences, each CTA walking a whole context: the deeper pipeline pays there
-    const bool deep = g_decode_stages == 3 || p.n_split == 1;
+    bool deep = g_decode_stages == 3;
+    if (p.n_split == 1) {
+        // Unsplit keys: two CTAs per SM with three stages each stream faster than three CTAs with two (a round of the
+        // former takes about 0.87 of a round of the latter), unless the former need a round more: 320 (sequence, KV
+        // head) pairs of 2048 keys take 99.7 us as two rounds of 296 and 59.6 us as one round of 444; 512 pairs 103.9
+        // against 118.4 us (two rounds either way); 640 pairs 150.3 against 122.9 us (three rounds against two).
+        const int sms = decode_sm_count();
+        const long long ctas = (long long) ((max_rows + 15) / 16) * p.nkv * S;
+        const long long rounds3 = (ctas + 2 * sms - 1) / (2 * sms), rounds2 = (ctas + 3 * sms - 1) / (3 * sms);
+        deep = g_unsplit_stages != 0 ? g_unsplit_stages == 3 : rounds3 * 100 <= rounds2 * 115;
+    }
     KvMaps maps = {};
     if constexpr (HD == 128) {
         // the TMA form: a status buffer to report to, pages that divide a tile and hold whole swizzle atoms
@@ -1054,6 +1077,12 @@ using namespace iian;
 // status: two ints on the device, zero before the launch, or null.  With a status buffer the decode form fetches
 // its K/V tiles by TMA where it can (head size 128, pages of 8 to 64 tokens); a wait that gave up leaves {11, tile}
 // there and the output is not valid.  Without one it copies with cp.async as before.
+IIAN_API int iian_attention_unsplit_stages(int stages) {
+    if (stages != 0 && stages != 2 && stages != 3) return IIAN_ERR_SHAPE;
+    g_unsplit_stages = stages;
+    return IIAN_OK;
+}
+
 IIAN_API int iian_attention_decode_stages(int stages) {
     if (stages != 2 && stages != 3) return IIAN_ERR_SHAPE;
     g_decode_stages = stages;

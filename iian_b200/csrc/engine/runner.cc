@@ -271,11 +271,13 @@ struct NativeRunner::Impl {
     int attention_splits(int num_seqs, int num_kv_heads, int max_ctx) const {
         const int tiles = std::max(1, (max_ctx + 63) / 64);
         const int base = std::max(1, num_seqs * num_kv_heads);
-        const int slots = opt.decode_ctas_per_sm * sm_count;
+        const int slots = opt.decode_ctas_per_sm * sm_count / 10;      // tenths: 2.7 CTAs per SM by default
         int n = std::max(1, std::min(std::min(slots / base, (tiles + 1) / 2), opt.max_splits));
-        if (n > 8 && n < 16) n = 8;                          // up to 16 parts merge inside a thread-block cluster
-        else if (n > 16 && tiles < 512) n = 16;
-        return n;
+        // a power of two, merged inside a thread-block cluster of up to 16 (of which only a few fit the GPU at once);
+        // 32 through scratch memory for a single sequence from 32k of context on
+        if (n >= 32 && tiles >= 512) return n;
+        if (n >= 16) return base * 16 <= 2 * sm_count ? 16 : 8;
+        return n >= 8 ? 8 : n >= 4 ? 4 : n >= 2 ? 2 : 1;
     }
 
     // ---- products ---------------------------------------------------------------------------------------------
@@ -850,8 +852,11 @@ struct NativeRunner::Impl {
 
     const float * step_graph(const StepBatch & batch, int * n_rows) {
         const int n = (int) batch.entries.size();
+        // batches are padded to 1, 2, 4, 8, then to multiples of 4 up to 32 and of 8 beyond: padding sequences are CTAs
+        // of the attention launch too, and whether those fit the GPU at once decides its form
         int bucket = 1;
-        while (bucket < n) bucket *= 2;
+        if (n <= 8) { while (bucket < n) bucket *= 2; }
+        else { const int step = n <= 32 ? 4 : 8; bucket = (n + step - 1) / step * step; }
         bucket = std::min(bucket, std::max(opt.max_num_seqs, n));
         int max_ctx = 0;
         for (const auto & e : batch.entries) max_ctx = std::max(max_ctx, e.start + 1);

@@ -191,10 +191,12 @@ class NativeStep:
         opt = _RunnerOptions(max_num_seqs, max_model_len, int(cuda_graphs), int(weight_prefetch),
                              int(os.environ.get("IIAN_PREFETCH_WINDOW_MB", "8")), K.TCGEN05_MIN_TILES, int(K.LIBRARY_GEMM_ONLY),
                              int(K.FUSE_NORM), int(K.FUSED_DECODE), int(K.ATTENTION_TC), int(K.CLUSTER_MERGE), int(K.TCGEN05_PAIR),
-                             K.DECODE_STAGES, K.MAX_SPLITS, K.DECODE_CTAS_PER_SM, int(K.STREAM_PRODUCT), K.STREAM_STAGES, int(pdl_for("gemm_stream")), int(K.DECODE_TMA), int(K.SPLIT_MIXED))
+                             K.DECODE_STAGES, K.MAX_SPLITS, K.DECODE_CTAS_PER_SM_X10, int(K.STREAM_PRODUCT), K.STREAM_STAGES, int(pdl_for("gemm_stream")), int(K.DECODE_TMA), int(K.SPLIT_MIXED))
         self._keep += [layers, calls, paths, desc]
         with torch.cuda.device(model.device):
             self._h = lib().iian_runner_new(ctypes.byref(desc), paths, manager._h, ctypes.byref(opt))
+            if model.dtype == torch.bfloat16:
+                K.apply_unsplit_stages()          # (the kernel library is the same instance the runner has opened)
         if not self._h:
             raise NativeError(lib().iian_engine_last_error().decode("utf-8", "replace"))
         self.vocab = model.vocab_size

@@ -478,9 +478,15 @@ class ModelRunner:
         sequences, context bucket); its kernels read the step's integers from fixed device buffers, so a
         replay needs one upload and one launch."""
         n = len(entries)
-        bucket = 1
-        while bucket < n:
-            bucket *= 2
+        # batches are padded to 1, 2, 4, 8, then to multiples of 4 up to 32 and of 8 beyond: padding sequences are CTAs
+        # of the attention launch too, and whether those fit the GPU at once decides its form
+        if n <= 8:
+            bucket = 1
+            while bucket < n:
+                bucket *= 2
+        else:
+            step = 4 if n <= 32 else 8
+            bucket = -(-n // step) * step
         bucket = min(bucket, max(self.max_num_seqs, n))
         max_ctx = max(e.start + 1 for e in entries)
         ctx_bucket = 256

@@ -650,11 +650,21 @@ class CudaKernels:
 
     @property
     def DECODE_SLOTS(self) -> int:
-        """CTAs of the decode kernel one launch should not exceed: two per SM."""
-        return self.DECODE_CTAS_PER_SM * self.sm_count()
+        """CTAs of the decode kernel with split keys one launch should not exceed: 2.7 per SM (three fit; clusters
+        need their CTAs inside one GPC, which leaves some places empty)."""
+        return self.DECODE_CTAS_PER_SM_X10 * self.sm_count() // 10
 
-    DECODE_CTAS_PER_SM = int(os.environ.get("IIAN_DECODE_CTAS_PER_SM", "2"))
+    DECODE_CTAS_PER_SM_X10 = int(round(10 * float(os.environ.get("IIAN_DECODE_CTAS_PER_SM", "2.7"))))
     _stages_set = None
+
+    @staticmethod
+    def apply_unsplit_stages() -> None:
+        """IIAN_DECODE_UNSPLIT_STAGES=2|3 fixes the tiles per CTA of decode attention with unsplit keys (a measurement
+        switch; by default the kernel library chooses by the number of rounds each form needs)."""
+        v = os.environ.get("IIAN_DECODE_UNSPLIT_STAGES")
+        if v:
+            if _fn("attention_mma", "iian_attention_unsplit_stages", [c_int])(int(v)) != 0:
+                raise KernelError("IIAN_DECODE_UNSPLIT_STAGES takes 2 or 3")
 
     def set_decode_stages(self, stages: int) -> None:
         """2: three CTAs per SM with one tile in flight each; 3: two CTAs with two tiles in flight."""
@@ -664,6 +674,7 @@ class CudaKernels:
             raise KernelError("attention: the decode kernel has 2 or 3 stages")
         type(self)._stages_set = stages
         type(self).DECODE_STAGES = stages
+        self.apply_unsplit_stages()
     CLUSTER_MERGE = os.environ.get("IIAN_ATTENTION_CLUSTER", "1") not in ("0", "false", "off")
     MAX_SPLITS = int(os.environ.get("IIAN_DECODE_MAX_SPLITS", "32"))
     _scratch = {}
@@ -672,24 +683,26 @@ class CudaKernels:
     def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
         """How many parts the keys of a decode step are cut into, so that few long sequences still fill
         the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128, contexts of 1k to 8k, batches 1 to
-        64): the CTAs of one launch should number at most two per SM (more slow each other down, and a second
-        wave repeats the whole chain of dependent loads), and a CTA should keep at least two key tiles.  Up to
-        16 parts merge inside a thread-block cluster (more than 8 is a size a kernel has to ask for), which saves
-        three trips through L2 (write the parts, count arrivals, read them back: 3.36 -> 3.23 ms per step at batch 1
-        and 1k context; one launch at batch 1 and 8k context: 27.9 us with 8 parts, 18.6 us with 16 in a cluster,
-        25.9 us with 16 and 30.8 us with 32 merged through scratch memory), so 9 to 15 parts are rounded down to 8,
-        more to 16, and more than 16 are only taken from 32k of context on (48.8 us with 32 parts through scratch
-        memory against 52.9 us with 16 in a cluster)."""
+        128): all CTAs of a launch should be resident at once (a second round repeats the whole chain of dependent
+        loads: 24.6 us with 8 parts against 14.7 us with 4 at batch 8), which with split keys means up to 2.7 per SM
+        (35.0 us with 2 parts against 51.8 us unsplit at batch 20, 21.9 against 30.7 us with 4 against 2 at batch 10;
+        but 65 against 53 us at batch 28, where two parts no longer fit), and a CTA should keep at least two key
+        tiles.  The parts of a sequence are a power of two and merge inside a thread-block cluster, up to 16 of them
+        (more than 8 is a size a kernel has to ask for, and only some 24 such clusters fit the GPU: 13.6 us with 8
+        against 22.7 us with 16 parts at batch 3), which saves three trips through L2 (write the parts, count
+        arrivals, read them back: one launch at batch 1 and 8k context takes 27.9 us with 8 parts, 18.6 us with 16 in
+        a cluster, 25.9 us with 16 and 30.8 us with 32 merged through scratch memory); 32 parts through scratch
+        memory are only taken for a single sequence from 32k of context on (48.8 against 52.9 us)."""
         tiles = max(1, (max_ctx + 63) // 64)
         base = max(1, num_seqs * num_kv_heads)
         if os.environ.get("IIAN_DECODE_FORCE_SPLITS"):
             return int(os.environ["IIAN_DECODE_FORCE_SPLITS"])
         n = max(1, min(self.DECODE_SLOTS // base, -(-tiles // 2), self.MAX_SPLITS))
-        if 8 < n < 16:
-            n = 8
-        elif n > 16 and tiles < 512:
-            n = 16
-        return n
+        if n >= 32 and tiles >= 512:
+            return n
+        if n >= 16:
+            return 16 if base * 16 <= 2 * self.sm_count() else 8
+        return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 1
 
     def attention_scratch(self, device, n_floats: int) -> torch.Tensor:
         t = self._scratch.get(device)

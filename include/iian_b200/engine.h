@@ -108,7 +108,7 @@ struct RunnerOptions {
     bool tcgen05_pair = true;
     int decode_stages = 2;
     int max_splits = 32;
-    int decode_ctas_per_sm = 2;
+    int decode_ctas_per_sm = 27;    // in tenths: CTAs per SM a decode attention launch with split keys may use
     bool stream_product = true;     // products of up to 8 rows: weights through shared memory by bulk copies (gemm_stream.cu)
     int stream_stages = 12;         // 12: one CTA per SM with the deep ring; 6: two CTAs per SM
     bool pdl_stream = true;         // launch the streaming product with programmatic stream serialization
