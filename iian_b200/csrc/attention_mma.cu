@@ -1077,6 +1077,9 @@ using namespace iian;
 // status: two ints on the device, zero before the launch, or null.  With a status buffer the decode form fetches
 // its K/V tiles by TMA where it can (head size 128, pages of 8 to 64 tokens); a wait that gave up leaves {11, tile}
 // there and the output is not valid.  Without one it copies with cp.async as before.
+// iian_attention_decode_stages(3) gives every decode launch three stages; by default launches with split keys have two,
+// and launches with unsplit keys the number that needs fewer rounds of CTAs (iian_attention_unsplit_stages(2 | 3)
+// fixes it for a measurement, 0 gives the choice back).
 IIAN_API int iian_attention_unsplit_stages(int stages) {
     if (stages != 0 && stages != 2 && stages != 3) return IIAN_ERR_SHAPE;
     g_unsplit_stages = stages;
