@@ -852,11 +852,12 @@ struct NativeRunner::Impl {
 
     const float * step_graph(const StepBatch & batch, int * n_rows) {
         const int n = (int) batch.entries.size();
-        // batches are padded to 1, 2, 4, 8, then to multiples of 4 up to 32 and of 8 beyond: padding sequences are CTAs
-        // of the attention launch too, and whether those fit the GPU at once decides its form
+        // batches are padded to 1, 2, 4, 8, then to multiples of 4 up to 32, of 8 up to 64, of 16 up to 128 and of 32
+        // beyond: padding sequences are CTAs of the attention launch too, and whether those fit the GPU at once decides
+        // its form
         int bucket = 1;
         if (n <= 8) { while (bucket < n) bucket *= 2; }
-        else { const int step = n <= 32 ? 4 : 8; bucket = (n + step - 1) / step * step; }
+        else { const int step = n <= 32 ? 4 : n <= 64 ? 8 : n <= 128 ? 16 : 32; bucket = (n + step - 1) / step * step; }
         bucket = std::min(bucket, std::max(opt.max_num_seqs, n));
         int max_ctx = 0;
         for (const auto & e : batch.entries) max_ctx = std::max(max_ctx, e.start + 1);

@@ -478,14 +478,15 @@ class ModelRunner:
         sequences, context bucket); its kernels read the step's integers from fixed device buffers, so a
         replay needs one upload and one launch."""
         n = len(entries)
-        # batches are padded to 1, 2, 4, 8, then to multiples of 4 up to 32 and of 8 beyond: padding sequences are CTAs
-        # of the attention launch too, and whether those fit the GPU at once decides its form
+        # batches are padded to 1, 2, 4, 8, then to multiples of 4 up to 32, of 8 up to 64, of 16 up to 128 and of 32
+        # beyond: padding sequences are CTAs of the attention launch too, and whether those fit the GPU at once decides
+        # its form
         if n <= 8:
             bucket = 1
             while bucket < n:
                 bucket *= 2
         else:
-            step = 4 if n <= 32 else 8
+            step = 4 if n <= 32 else 8 if n <= 64 else 16 if n <= 128 else 32
             bucket = -(-n // step) * step
         bucket = min(bucket, max(self.max_num_seqs, n))
         max_ctx = max(e.start + 1 for e in entries)
