@@ -993,14 +993,14 @@ static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t
     // unsplit keys mean many sequences, each CTA walking a whole context: the deeper pipeline pays there
     bool deep = g_decode_stages == 3;
     if (p.n_split == 1) {
-        // Unsplit keys: two CTAs per SM with three stages each stream faster than three CTAs with two (a round of the
-        // former takes about 0.87 of a round of the latter), unless the former need a round more: 320 (sequence, KV
-        // head) pairs of 2048 keys take 99.7 us as two rounds of 296 and 59.6 us as one round of 444; 512 pairs 103.9
-        // against 118.4 us (two rounds either way); 640 pairs 150.3 against 122.9 us (three rounds against two).
+        // Unsplit keys: two CTAs per SM with three stages each stream faster than three CTAs with two (a wave of the
+        // former takes about 0.87 of a wave of the latter), unless the former need a wave more: 320 (sequence, KV
+        // head) pairs of 2048 keys take 99.7 us as two waves of 296 and 59.6 us as one wave of 444; 512 pairs 103.9
+        // against 118.4 us (two waves either way); 640 pairs 150.3 against 122.9 us (three waves against two).
         const int sms = decode_sm_count();
         const long long ctas = (long long) ((max_rows + 15) / 16) * p.nkv * S;
-        const long long rounds3 = (ctas + 2 * sms - 1) / (2 * sms), rounds2 = (ctas + 3 * sms - 1) / (3 * sms);
-        deep = g_unsplit_stages != 0 ? g_unsplit_stages == 3 : rounds3 * 100 <= rounds2 * 115;
+        const long long waves3 = (ctas + 2 * sms - 1) / (2 * sms), waves2 = (ctas + 3 * sms - 1) / (3 * sms);
+        deep = g_unsplit_stages != 0 ? g_unsplit_stages == 3 : waves3 * 100 <= waves2 * 115;
     }
     KvMaps maps = {};
     if constexpr (HD == 128) {
@@ -1078,7 +1078,7 @@ using namespace iian;
 // its K/V tiles by TMA where it can (head size 128, pages of 8 to 64 tokens); a wait that gave up leaves {11, tile}
 // there and the output is not valid.  Without one it copies with cp.async as before.
 // iian_attention_decode_stages(3) gives every decode launch three stages; by default launches with split keys have two,
-// and launches with unsplit keys the number that needs fewer rounds of CTAs (iian_attention_unsplit_stages(2 | 3)
+// and launches with unsplit keys the number that needs fewer waves of CTAs (iian_attention_unsplit_stages(2 | 3)
 // fixes it for a measurement, 0 gives the choice back).
 IIAN_API int iian_attention_unsplit_stages(int stages) {
     if (stages != 0 && stages != 2 && stages != 3) return IIAN_ERR_SHAPE;

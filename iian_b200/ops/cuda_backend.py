@@ -660,7 +660,7 @@ class CudaKernels:
     @staticmethod
     def apply_unsplit_stages() -> None:
         """IIAN_DECODE_UNSPLIT_STAGES=2|3 fixes the tiles per CTA of decode attention with unsplit keys (a measurement
-        switch; by default the kernel library chooses by the number of rounds each form needs)."""
+        switch; by default the kernel library chooses by the number of waves of CTAs each form needs)."""
         v = os.environ.get("IIAN_DECODE_UNSPLIT_STAGES")
         if v:
             if _fn("attention_mma", "iian_attention_unsplit_stages", [c_int])(int(v)) != 0:
@@ -683,7 +683,7 @@ class CudaKernels:
     def attention_splits(self, num_seqs: int, num_kv_heads: int, max_ctx: int) -> int:
         """How many parts the keys of a decode step are cut into, so that few long sequences still fill
         the GPU.  Measured on B200 (replayed graphs, 8 KV heads of 128, contexts of 1k to 8k, batches 1 to
-        128): all CTAs of a launch should be resident at once (a second round repeats the whole chain of dependent
+        128): all CTAs of a launch should be resident at once (a second wave repeats the whole chain of dependent
         loads: 24.6 us with 8 parts against 14.7 us with 4 at batch 8), which with split keys means up to 2.7 per SM
         (35.0 us with 2 parts against 51.8 us unsplit at batch 20, 21.9 against 30.7 us with 4 against 2 at batch 10;
         but 65 against 53 us at batch 28, where two parts no longer fit), and a CTA should keep at least two key
